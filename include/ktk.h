@@ -1,0 +1,192 @@
+/*
+ * ktk.h -- C ABI of the block top-k paged decode attention library (libktk.so).
+ *
+ * Hand-written sm_100a CUDA kernels behind plain C entry points: raw device
+ * pointers, explicit sizes, a cudaStream_t passed as void*.  No torch types,
+ * no exceptions.  Every call only enqueues work on `stream`; none of them
+ * synchronises or allocates device memory.
+ *
+ * Each entry point names the interface of the reference project
+ * (Infini-AI-Lab/Kinetics) that it replaces, as file:line inside that project.
+ *
+ * Data model (all row-major, innermost dimension last):
+ *   kv_cache   [num_pages, 2, page_size, Hkv, D]   dtype   (2 = K then V; the
+ *              "NHD" paged layout of benchmark/blocktopk_decoder.py:161-164)
+ *   summaries  [B, Hkv, summary_stride, D]         dtype   per-page mean key,
+ *              indexed by the LOGICAL page number of sequence b
+ *              (benchmark/blocktopk_decoder.py:166-168 `compressed_key_cache`)
+ *   page table in CSR form, exactly as the reference hands it to flashinfer
+ *              (benchmark/blocktopk_decoder.py:141-149):
+ *              kv_indices[int32], kv_indptr[int32, B+1], kv_last_page_len[int32, B]
+ *              sequence b owns physical pages kv_indices[kv_indptr[b] .. kv_indptr[b+1]),
+ *              its last page holds kv_last_page_len[b] in [1, page_size] tokens.
+ *   q, o       [B, Hq, D]                          dtype,  Hq = Hkv * G
+ *
+ * Only D = 128 and page_size = 16 are built; anything else returns
+ * KTK_ERR_UNSUPPORTED.
+ */
+#ifndef KTK_H_
+#define KTK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define KTK_API __attribute__((visibility("default")))
+#else
+#define KTK_API
+#endif
+
+/* element types of q / k / v / kv_cache / summaries / o */
+#define KTK_F32 0
+#define KTK_BF16 1
+
+/* return codes (host side, detected before anything is enqueued) */
+#define KTK_OK 0
+#define KTK_ERR_ARG (-1)         /* null pointer, negative size, bad enum     */
+#define KTK_ERR_UNSUPPORTED (-2) /* head_dim / page_size / group size not built */
+#define KTK_ERR_WORKSPACE (-3)   /* workspace too small for the split count    */
+#define KTK_ERR_CUDA (-4)        /* a CUDA runtime call failed; see ktk_last_error */
+#define KTK_ERR_TOO_LARGE (-5)   /* size beyond a stated maximum                */
+
+/* device-side status word values (written to `status[0]`, first fault wins;
+ * the offending access is skipped, the kernel never traps) */
+#define KTK_STATUS_OK 0
+#define KTK_STATUS_BAD_PAGE 1    /* physical page id outside [0, num_pages)      */
+#define KTK_STATUS_BAD_TABLE 2   /* kv_indptr not monotone / last_page_len out of range */
+
+/* decode kernel variants (ktk_sparse_decode / ktk_dense_decode `variant`) */
+#define KTK_VARIANT_AUTO 0
+#define KTK_VARIANT_SIMT 1       /* fp32 FMA path (the only one for KTK_F32)     */
+#define KTK_VARIANT_MMA 2        /* bf16 tensor-core path with TMA-staged pages  */
+
+typedef struct ktk_shape {
+    int32_t batch;          /* B: sequences in this step                         */
+    int32_t num_kv_heads;   /* Hkv, local to this GPU                            */
+    int32_t group_size;     /* G = Hq / Hkv                                      */
+    int32_t head_dim;       /* D, must be 128                                    */
+    int32_t page_size;      /* P, must be 16                                     */
+    int32_t dtype;          /* KTK_F32 or KTK_BF16                               */
+    int64_t num_pages;      /* physical pages in kv_cache (bounds check)         */
+} ktk_shape;
+
+/* Human-readable text of the last error on the calling thread ("" if none). */
+KTK_API const char* ktk_last_error(void);
+/* Library version, "major.minor". */
+KTK_API const char* ktk_version(void);
+
+/*
+ * Paged KV append + page-summary maintenance (decode, one token per sequence).
+ * Replaces: torch op mylib::update_kv -> flashinfer.append_paged_kv_cache
+ *   (benchmark/blocktopk_decoder.py:23-46, call site :209-213; dense twin
+ *   benchmark/dense_decoder.py:21-44) and LiteSys copy_to_cache
+ *   (LiteSys/litesys/attention/cache_utils.py:5-51, batch_cache.py:76-84).
+ * The page table must already describe the state AFTER the append (flashinfer
+ * convention): the token goes to page kv_indices[kv_indptr[b+1]-1], slot
+ * kv_last_page_len[b]-1.  If `summaries` is non-null the summary of that
+ * (last) logical page is rewritten as the mean of the page's filled keys:
+ * fp32 sequential sum over slots 0..c-1, divided by c, rounded to dtype.
+ *   k, v: [B, Hkv, D]
+ */
+KTK_API int ktk_append(const void* k, const void* v, void* kv_cache, void* summaries,
+               int64_t summary_stride, const int32_t* kv_indices,
+               const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+               const ktk_shape* shape, int32_t* status, void* stream);
+
+/*
+ * Rebuild the summaries of every page of every sequence from the cache (bulk
+ * initialisation after a prefill).  The reference fills `compressed_key_cache`
+ * with random numbers (benchmark/blocktopk_decoder.py:166-168); the mean-of-keys
+ * definition follows LiteSys/litesys/attention/sparsity_utils.py:37.
+ */
+KTK_API int ktk_build_summaries(const void* kv_cache, void* summaries, int64_t summary_stride,
+                        const int32_t* kv_indices, const int32_t* kv_indptr,
+                        const int32_t* kv_last_page_len, const ktk_shape* shape,
+                        int32_t* status, void* stream);
+
+/*
+ * GQA query x page-summary scoring fused with top-k page selection.
+ * Replaces: benchmark/blocktopk_decoder.py:216-221 (einsum + mean, torch.topk,
+ *   logical->physical map, always-on last page, int32 cast) and the selection
+ *   inside LiteSys/litesys/attention/sparsity_utils.py:24-47.
+ * For each (b, kv head): scored pages are the logical pages 0 .. n_pages-2 (every
+ * page but the one being filled); score = dot(mean_g q[b, h*G+g, :], summary) in
+ * fp32 in a fixed summation order; if their number <= topk all are taken in index
+ * order, else the topk largest, descending score, ties to the LOWEST page index;
+ * the last page is appended.  Writes cnt = min(topk, n_pages-1) + 1 entries, the
+ * rest of the row is -1.
+ *   out_pages   [B, Hkv, topk+1] int32  physical page ids        (required)
+ *   out_logical [B, Hkv, topk+1] int32  logical page numbers     (nullable)
+ *   out_scores  [B, Hkv, summary_stride] fp32 raw scores         (nullable)
+ */
+KTK_API int ktk_select(const void* q, const void* summaries, int64_t summary_stride,
+               const int32_t* kv_indices, const int32_t* kv_indptr,
+               const int32_t* kv_last_page_len, int32_t topk, int32_t* out_pages,
+               int32_t* out_logical, float* out_scores, const ktk_shape* shape,
+               int32_t* status, void* stream);
+
+/*
+ * Split count the decode kernels use when the caller passes num_splits = 0, and
+ * the workspace size that count needs.  `max_entries` = largest number of pages
+ * one (sequence, kv head) attends (topk+1 for sparse, max pages per sequence
+ * for dense).  Host-only, no CUDA call except a cached device-attribute query.
+ * flashinfer's analogue is the 128 MB workspace + plan()
+ * (benchmark/blocktopk_decoder.py:152, :255-265).
+ */
+KTK_API int32_t ktk_decode_num_splits(const ktk_shape* shape, int32_t max_entries);
+KTK_API size_t ktk_decode_workspace_bytes(const ktk_shape* shape, int32_t num_splits);
+
+/*
+ * Flash-decode attention over the selected pages only.
+ * Replaces: mylib::decode -> BatchDecodeWithPagedKVCacheWrapper.run
+ *   (benchmark/blocktopk_decoder.py:153-160, :171-184, :223-225) and, restricted
+ *   to the selected pages, LiteSys qk / softmax / sv
+ *   (LiteSys/litesys/attention/cache_utils.py:54-93, :97-130, :135-169).
+ * o[b, h*G+g, :] = softmax_s(q . K_s * sm_scale) . V_s over the tokens of the
+ * pages listed in sel_pages[b, h, 0..cnt), cnt = min(topk, n_pages-1) + 1; the last
+ * listed page is masked to kv_last_page_len[b] tokens.  fp32 accumulation.
+ *   num_splits 0 = ktk_decode_num_splits(); >1 needs `workspace` of
+ *   ktk_decode_workspace_bytes() bytes (partials + a second combine launch).
+ */
+KTK_API int ktk_sparse_decode(const void* q, const void* kv_cache, const int32_t* sel_pages,
+                      int32_t topk, const int32_t* kv_indptr,
+                      const int32_t* kv_last_page_len, float sm_scale, void* o,
+                      void* workspace, size_t workspace_bytes, int32_t num_splits,
+                      int32_t variant, const ktk_shape* shape, int32_t* status,
+                      void* stream);
+
+/*
+ * Dense paged decode over all pages of each sequence (the baseline the sparse
+ * path is compared with).
+ * Replaces: benchmark/dense_decoder.py:149-156, :168-170, :178-189.
+ */
+KTK_API int ktk_dense_decode(const void* q, const void* kv_cache, const int32_t* kv_indices,
+                     const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                     int32_t max_pages_per_seq, float sm_scale, void* o, void* workspace,
+                     size_t workspace_bytes, int32_t num_splits, int32_t variant,
+                     const ktk_shape* shape, int32_t* status, void* stream);
+
+/*
+ * RMSNorm over the last dimension: out = x * rsqrt(mean(x^2) + eps) * w, fp32
+ * arithmetic, result in dtype.  x, out: [rows, cols]; w: [cols].
+ * Replaces: mylib::layer_norm / mylib::qk_norm -> flashinfer.rmsnorm
+ *   (benchmark/model_utils.py:4-25, benchmark/blocktopk_decoder.py:61-85).
+ */
+KTK_API int ktk_rmsnorm(const void* x, const void* w, float eps, void* out, int64_t rows,
+                int32_t cols, int32_t dtype, void* stream);
+
+/*
+ * SwiGLU gate: out = silu(gate) * up, elementwise, fp32 arithmetic.
+ * Replaces the activation + multiply of benchmark/blocktopk_decoder.py:235-236.
+ */
+KTK_API int ktk_silu_mul(const void* gate, const void* up, void* out, int64_t n, int32_t dtype,
+                 void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KTK_H_ */

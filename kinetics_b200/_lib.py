@@ -1,0 +1,78 @@
+"""ctypes binding of libktk.so (the C ABI declared in include/ktk.h).
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, c_char_p, c_float, c_int32, c_int64, c_size_t, c_void_p
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libktk.so"
+
+KTK_F32, KTK_BF16 = 0, 1
+VARIANT_AUTO, VARIANT_SIMT, VARIANT_MMA = 0, 1, 2
+STATUS_TEXT = {0: "ok", 1: "physical page id outside the cache", 2: "malformed page table"}
+
+
+class KtkError(RuntimeError):
+    def __init__(self, code: int, text: str):
+        super().__init__(f"libktk error {code}: {text}")
+        self.code = code
+
+
+class Shape(ctypes.Structure):
+    _fields_ = [
+        ("batch", c_int32), ("num_kv_heads", c_int32), ("group_size", c_int32),
+        ("head_dim", c_int32), ("page_size", c_int32), ("dtype", c_int32),
+        ("num_pages", c_int64),
+    ]
+
+
+_i32p = c_void_p   # device pointers travel as integers
+_SIGNATURES = {
+    "ktk_last_error": (c_char_p, []),
+    "ktk_version": (c_char_p, []),
+    "ktk_append": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, _i32p, _i32p, _i32p,
+                             POINTER(Shape), _i32p, c_void_p]),
+    "ktk_build_summaries": (c_int32, [c_void_p, c_void_p, c_int64, _i32p, _i32p, _i32p, POINTER(Shape),
+                                      _i32p, c_void_p]),
+    "ktk_select": (c_int32, [c_void_p, c_void_p, c_int64, _i32p, _i32p, _i32p, c_int32, _i32p, _i32p,
+                             c_void_p, POINTER(Shape), _i32p, c_void_p]),
+    "ktk_decode_num_splits": (c_int32, [POINTER(Shape), c_int32]),
+    "ktk_decode_workspace_bytes": (c_size_t, [POINTER(Shape), c_int32]),
+    "ktk_sparse_decode": (c_int32, [c_void_p, c_void_p, _i32p, c_int32, _i32p, _i32p, c_float, c_void_p,
+                                    c_void_p, c_size_t, c_int32, c_int32, POINTER(Shape), _i32p, c_void_p]),
+    "ktk_dense_decode": (c_int32, [c_void_p, c_void_p, _i32p, _i32p, _i32p, c_int32, c_float, c_void_p,
+                                   c_void_p, c_size_t, c_int32, c_int32, POINTER(Shape), _i32p, c_void_p]),
+    "ktk_rmsnorm": (c_int32, [c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int32, c_int32, c_void_p]),
+    "ktk_silu_mul": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
+}
+
+#: every symbol include/ktk.h declares
+EXPORTED = tuple(_SIGNATURES)
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load libktk.so, binding argument types.  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python kinetics_b200/build.py` "
+                "(nvcc, sm_100a).  There is no CPU or PyTorch fallback for this path.")
+        lib = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise KtkError(rc, load().ktk_last_error().decode())

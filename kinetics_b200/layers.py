@@ -1,0 +1,248 @@
+"""Decoder layers with block top-k / dense paged decode attention.
+
+Drop-in counterparts of the reference's ``BlockTopkDecoderLayer``
+(benchmark/blocktopk_decoder.py:96-265) and ``DecoderLayer`` (benchmark/dense_decoder.py:94-234):
+same constructor arguments, ``forward(hidden_states[B, 1, H]) -> [B, 1, H]`` and
+``prepare_wrapper``.  Differences, all on purpose:
+
+* the paged append, page selection and attention run hand-written CUDA kernels (libktk.so)
+  instead of flashinfer / ATen; the linear layers stay cuBLAS;
+* ``compressed_key_cache`` holds the mean key of every page (maintained by the append), not
+  random numbers (reference :166-168), for every local kv head (the reference asserts one, :165);
+* the selection computed in ``forward`` is the one the attention consumes (the reference rebinds
+  ``self.topk_page_indices`` at :221 while flashinfer keeps the buffer from :157);
+* ``last_kv_lens`` starts at 1 (the token the step appends) instead of 0 (:149);
+* the torch ops are registered once at import, so dense and sparse layers share a process;
+* with ``process_group`` set, the o_proj partial sums are all-reduced (LiteSys
+  litesys/models/qwen3_dist.py:111-112); the reference benchmark only divides head counts.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import ops
+
+
+def init_weights(m):
+    """Same initialisation as benchmark/blocktopk_decoder.py:88-94."""
+    if isinstance(m, nn.Linear):
+        nn.init.kaiming_uniform_(m.weight, a=math.sqrt(5))
+        if m.bias is not None:
+            fan_in, _ = nn.init._calculate_fan_in_and_fan_out(m.weight)
+            bound = 1 / math.sqrt(fan_in)
+            nn.init.uniform_(m.bias, -bound, bound)
+
+
+def interleaved_page_table(batch_size: int, pages_per_req: int, device) -> torch.Tensor:
+    """[B, pages_per_req] with entry [b, p] = p * B + b (benchmark/blocktopk_decoder.py:141)."""
+    p = torch.arange(pages_per_req, dtype=torch.int32, device=device) * batch_size
+    return (p[None, :] + torch.arange(batch_size, dtype=torch.int32, device=device)[:, None]).contiguous()
+
+
+def random_page_table(batch_size: int, pages_per_req: int, num_pages: int, device, seed: int) -> torch.Tensor:
+    """[B, pages_per_req] drawn from one global random permutation of the physical pages."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    perm = torch.randperm(num_pages, generator=g)[: batch_size * pages_per_req]
+    return perm.to(torch.int32).view(batch_size, pages_per_req).to(device).contiguous()
+
+
+class _PagedDecoderLayer(nn.Module):
+    """Shared body: weights, paged KV state, the non-attention part of forward."""
+
+    def __init__(self, config, world_size, batch_size, prefix_len, max_len, page_size, device, dtype,
+                 page_table: str = "interleaved", process_group=None, seed: int = 0, variant: int = 0):
+        super().__init__()
+        self.num_heads = config.num_attention_heads // world_size
+        self.num_kv_heads = config.num_key_value_heads // world_size
+        self.num_key_value_groups = self.num_heads // self.num_kv_heads
+        self.head_dim = config.head_dim
+        self.dim = config.hidden_size
+        self.intermediate_size = config.intermediate_size // world_size
+        self.max_position_embeddings = config.max_position_embeddings
+        self.rope_theta = getattr(config, "rope_theta", 1e6)
+        eos = getattr(config, "eos_token_id", None)
+        self.eos_tokens = eos if isinstance(eos, list) else [eos]
+        self.hidden_act = getattr(config, "hidden_act", "silu")
+        self.ffn_frac = getattr(config, "ffn_frac", 1.0)
+
+        eps = config.rms_norm_eps
+        self.qnorm_weight = nn.Parameter(torch.ones(self.head_dim))
+        self.qnorm_variance_epsilon = eps
+        self.knorm_weight = nn.Parameter(torch.ones(self.head_dim))
+        self.knorm_variance_epsilon = eps
+        self.input_layernorm_weight = nn.Parameter(torch.ones(self.dim))
+        self.input_layernorm_variance_epsilon = eps
+        self.post_attention_layernorm_weight = nn.Parameter(torch.ones(self.dim))
+        self.post_attention_layernorm_variance_epsilon = eps
+
+        total_head_dim = (self.num_heads + 2 * self.num_kv_heads) * self.head_dim
+        self.wqkv = nn.Linear(self.dim, total_head_dim, bias=True)
+        self.wo = nn.Linear(self.head_dim * self.num_heads, self.dim, bias=False)
+        self.up_proj = nn.Linear(self.dim, self.intermediate_size, bias=False)
+        self.gate_proj = nn.Linear(self.dim, self.intermediate_size, bias=False)
+        self.down_proj = nn.Linear(self.intermediate_size, self.dim, bias=False)
+
+        self.batch_size = batch_size
+        self.prefix_len = prefix_len
+        self.page_size = page_size
+        self.device = device
+        self.dtype = dtype
+        self.process_group = process_group
+        self.variant = variant
+        if page_size != ops.PAGE_SIZE or self.head_dim != ops.HEAD_DIM:
+            raise ValueError(f"only page_size={ops.PAGE_SIZE}, head_dim={ops.HEAD_DIM} are built")
+
+        # paged KV state: prefix fills num_pages_per_req pages, the step appends into one more
+        self.max_num_pages = max_num_pages = max_len // page_size
+        self.num_pages_per_req = n = prefix_len // page_size
+        if n + 1 > max_num_pages:
+            raise ValueError("max_len leaves no page for the decoded token")
+        self.total_pages = max_num_pages * batch_size
+        if page_table == "interleaved":
+            table = interleaved_page_table(batch_size, n + 1, device)
+        elif page_table == "random":
+            table = random_page_table(batch_size, n + 1, self.total_pages, device, seed)
+        else:
+            raise ValueError(f"page_table {page_table!r}: 'interleaved' or 'random'")
+        self.page_table = table                                  # [B, n+1]
+        self.paged_kv_indices = table.view(-1)
+        self.full_kv_indptr = (torch.arange(batch_size + 1, dtype=torch.int32, device=device) * (n + 1))
+        self.last_kv_lens = torch.ones(batch_size, dtype=torch.int32, device=device)
+        self.qkv_indptr = torch.arange(batch_size + 1, dtype=torch.int32, device=device)
+        self.status = ops.new_status(device)
+
+        self.kv_cache = torch.randn(self.total_pages, 2, page_size, self.num_kv_heads, self.head_dim,
+                                    dtype=dtype, device=device)
+        self.decode_run = torch.ops.mylib.decode
+
+    # -- attention-specific parts, provided by the subclasses --
+    def _attention(self, query_states):
+        raise NotImplementedError
+
+    def _mlp(self, hidden_states):
+        up = self.up_proj(hidden_states)
+        gate = self.gate_proj(hidden_states)
+        if self.hidden_act == "silu":
+            hidden_states = ops.silu_mul(gate, up)
+        else:
+            from transformers.activations import ACT2FN
+            hidden_states = ACT2FN[self.hidden_act](gate) * up
+        return self.down_proj(hidden_states)
+
+    @torch.inference_mode()
+    def forward(self, hidden_states):
+        residual = hidden_states
+        hidden_states = torch.ops.mylib.layer_norm(hidden_states, self.input_layernorm_variance_epsilon,
+                                                   self.input_layernorm_weight)
+        bsz, q_len, _ = hidden_states.size()
+        q_dim, kv_dim = self.head_dim * self.num_heads, self.head_dim * self.num_kv_heads
+        proj = self.wqkv(hidden_states)
+        query_states, key_states, value_states = proj.split((q_dim, kv_dim, kv_dim), dim=-1)
+        query_states = query_states.reshape(bsz, q_len, self.num_heads, self.head_dim)
+        key_states = key_states.reshape(bsz, q_len, self.num_kv_heads, self.head_dim)
+        value_states = value_states.reshape(bsz, self.num_kv_heads, self.head_dim).contiguous()
+
+        query_states = torch.ops.mylib.qk_norm(query_states, self.qnorm_variance_epsilon, self.qnorm_weight)
+        key_states = torch.ops.mylib.qk_norm(key_states, self.knorm_variance_epsilon, self.knorm_weight)
+        query_states = query_states.reshape(bsz, self.num_heads, self.head_dim)
+        key_states = key_states.reshape(bsz, self.num_kv_heads, self.head_dim)
+
+        torch.ops.mylib.update_kv(key_states, value_states, self.qkv_indptr, self.kv_cache,
+                                  self.paged_kv_indices, self.full_kv_indptr, self.last_kv_lens)
+        o = self._attention(query_states)
+        o = o.reshape(bsz, q_len, self.head_dim * self.num_heads)
+        hidden_states = self.wo(o)
+        if self.process_group is not None:
+            torch.distributed.all_reduce(hidden_states, group=self.process_group)
+        hidden_states = residual + hidden_states
+        residual = hidden_states
+        hidden_states = torch.ops.mylib.layer_norm(hidden_states, self.post_attention_layernorm_variance_epsilon,
+                                                   self.post_attention_layernorm_weight)
+        hidden_states = self._mlp(hidden_states)
+        return residual + hidden_states
+
+    def check_status(self):
+        """Synchronising check of the device status word."""
+        ops.raise_on_status(self.status)
+
+    def make_graphed(self, example: torch.Tensor, warmup: int = 3):
+        """Capture one forward in a CUDA graph.  Returns (static_input, static_output, graph)."""
+        static_in = example.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self.forward(static_in)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            static_out = self.forward(static_in)
+        return static_in, static_out, graph
+
+
+class BlockTopkDecoderLayer(_PagedDecoderLayer):
+    """benchmark/blocktopk_decoder.py:96 -- block top-k sparse decode attention."""
+
+    def __init__(self, config, world_size, batch_size, prefix_len, max_len, page_size, topk_page, device, dtype,
+                 **kw):
+        super().__init__(config, world_size, batch_size, prefix_len, max_len, page_size, device, dtype, **kw)
+        self.topk_page = topk_page
+        n = self.num_pages_per_req
+        self.topk_page_indices = torch.full((batch_size * self.num_kv_heads * (topk_page + 1),), -1,
+                                            dtype=torch.int32, device=device)
+        # one summary row per (sequence, kv head, logical page); reference: [B, n, D] for one head
+        self.compressed_key_cache = torch.zeros(batch_size, self.num_kv_heads, self.max_num_pages, self.head_dim,
+                                                dtype=dtype, device=device)
+        self.rebuild_summaries()
+        ops.bind_summaries(self.kv_cache, self.compressed_key_cache)
+        self.prepare_wrapper(prefix_len)
+
+    def rebuild_summaries(self):
+        ops.build_summaries(self.kv_cache, self.compressed_key_cache, self.paged_kv_indices, self.full_kv_indptr,
+                            self.last_kv_lens, status=self.status)
+
+    def _sel_view(self):
+        return self.topk_page_indices.view(self.batch_size, self.num_kv_heads, self.topk_page + 1)
+
+    def _attention(self, query_states):
+        # benchmark/blocktopk_decoder.py:216-221, one kernel
+        ops.select_pages(query_states, self.compressed_key_cache, self.paged_kv_indices, self.full_kv_indptr,
+                         self.last_kv_lens, self.topk_page, self.total_pages, out=self._sel_view(),
+                         status=self.status)
+        return self.decode_run(query_states, self.kv_cache)
+
+    def prepare_wrapper(self, prefix_len=None, topk_page_indices=None):
+        """Bind the decode plan (reference: flashinfer wrapper.plan, :243-265).
+
+        `topk_page_indices`, if given, pre-loads the selection buffer ([B * Hkv * (topk+1)] int32
+        physical pages); forward overwrites it with its own selection.
+        """
+        if topk_page_indices is not None:
+            self.topk_page_indices.copy_(topk_page_indices.view(-1).to(torch.int32))
+        plan = ops.DecodePlan(self.kv_cache, self.full_kv_indptr, self.last_kv_lens, sel_pages=self._sel_view(),
+                              sm_scale=1.0 / math.sqrt(self.head_dim), variant=self.variant, status=self.status)
+        ops.bind_decode_plan(plan)
+        self.decode_plan = plan
+
+
+class DecoderLayer(_PagedDecoderLayer):
+    """benchmark/dense_decoder.py:94 -- dense paged decode attention over every page."""
+
+    def __init__(self, config, world_size, batch_size, prefix_len, max_len, page_size, device, dtype, **kw):
+        super().__init__(config, world_size, batch_size, prefix_len, max_len, page_size, device, dtype, **kw)
+        self.prepare_wrapper()
+
+    def _attention(self, query_states):
+        return self.decode_run(query_states, self.kv_cache)
+
+    def prepare_wrapper(self):
+        plan = ops.DecodePlan(self.kv_cache, self.full_kv_indptr, self.last_kv_lens,
+                              kv_indices=self.paged_kv_indices, max_pages_per_seq=self.num_pages_per_req + 1,
+                              sm_scale=1.0 / math.sqrt(self.head_dim), variant=self.variant, status=self.status)
+        ops.bind_decode_plan(plan)
+        self.decode_plan = plan

@@ -1,0 +1,423 @@
+"""Operator surface of the block top-k paged decode path.
+
+Functional wrappers over the C ABI (``include/ktk.h``) on CUDA tensors, and the torch
+custom ops the reference's decoder layers call:
+
+* ``mylib::update_kv``, ``mylib::decode``, ``mylib::qk_norm``, ``mylib::layer_norm`` -- the
+  names and schemas of ``benchmark/blocktopk_decoder.py:23-85,171-184`` (same in
+  ``benchmark/dense_decoder.py:21-83``), registered ONCE at import (the reference defines
+  ``mylib::decode`` inside ``__init__``, so a second layer in one process raises).
+* ``ktk::select_pages``, ``ktk::sparse_decode``, ``ktk::dense_decode``,
+  ``ktk::append_kv_with_summary`` -- explicit-argument forms.
+
+Every op runs a hand-written CUDA kernel from ``libktk.so`` on the current stream.  There is
+no CPU implementation and no PyTorch fallback: a CPU tensor raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import Shape, check
+
+HEAD_DIM = 128
+PAGE_SIZE = 16
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return _lib.KTK_BF16
+    if t.dtype == torch.float32:
+        return _lib.KTK_F32
+    raise TypeError(f"kinetics_b200: dtype {t.dtype} not supported (float32 or bfloat16)")
+
+
+def _cuda(*ts):
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("kinetics_b200 ops need CUDA tensors: this path has no CPU fallback")
+        if not t.is_contiguous():
+            raise RuntimeError("kinetics_b200 ops need contiguous tensors")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _shape(batch: int, kv_cache: torch.Tensor, num_q_heads: int) -> Shape:
+    if kv_cache.dim() != 5 or kv_cache.shape[1] != 2:
+        raise ValueError("kv_cache must be [num_pages, 2, page_size, num_kv_heads, head_dim]")
+    hkv = kv_cache.shape[3]
+    if num_q_heads % hkv:
+        raise ValueError(f"{num_q_heads} query heads do not divide into {hkv} kv heads")
+    return Shape(batch, hkv, num_q_heads // hkv, kv_cache.shape[4], kv_cache.shape[2], _dtype_code(kv_cache),
+                 kv_cache.shape[0])
+
+
+def new_status(device) -> torch.Tensor:
+    """Device status word the kernels report table / page-id faults into (0 = ok)."""
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def raise_on_status(status: torch.Tensor) -> None:
+    """Synchronising check of a status word."""
+    code = int(status.item())
+    if code:
+        raise RuntimeError(f"kinetics_b200 device status {code}: {_lib.STATUS_TEXT.get(code, '?')}")
+
+
+# --------------------------------------------------------------------------------------
+# functional API
+# --------------------------------------------------------------------------------------
+
+def append_kv(k, v, kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len, status=None) -> None:
+    """Write one new token per sequence into the paged cache and refresh its page summary.
+
+    k, v: [B, Hkv, D].  The page table already includes the new token
+    (flashinfer.append_paged_kv_cache convention, benchmark/blocktopk_decoder.py:38-46).
+    """
+    _cuda(k, v, kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len, status)
+    B = kv_indptr.numel() - 1
+    if k.shape != (B, kv_cache.shape[3], kv_cache.shape[4]) or v.shape != k.shape:
+        raise ValueError(f"k/v must be [B={B}, Hkv, D], got {tuple(k.shape)}")
+    if k.dtype != kv_cache.dtype or v.dtype != kv_cache.dtype:
+        raise TypeError("k, v and kv_cache must share a dtype")
+    shp = _shape(B, kv_cache, kv_cache.shape[3])
+    stride = 0
+    if summaries is not None:
+        if summaries.dtype != kv_cache.dtype or summaries.shape[0] < B or summaries.shape[1] != shp.num_kv_heads:
+            raise ValueError("summaries must be [>=B, Hkv, pages, D] in the cache dtype")
+        stride = summaries.shape[2]
+    check(_lib.load().ktk_append(_ptr(k), _ptr(v), _ptr(kv_cache), _ptr(summaries), stride, _ptr(kv_indices),
+                                 _ptr(kv_indptr), _ptr(kv_last_page_len), ctypes.byref(shp), _ptr(status),
+                                 _stream()))
+
+
+def build_summaries(kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len, status=None) -> None:
+    """Recompute the mean-key summary of every page of every sequence."""
+    _cuda(kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len, status)
+    B = kv_indptr.numel() - 1
+    shp = _shape(B, kv_cache, kv_cache.shape[3])
+    if summaries.dtype != kv_cache.dtype or summaries.shape[0] < B or summaries.shape[1] != shp.num_kv_heads:
+        raise ValueError("summaries must be [>=B, Hkv, pages, D] in the cache dtype")
+    check(_lib.load().ktk_build_summaries(_ptr(kv_cache), _ptr(summaries), summaries.shape[2], _ptr(kv_indices),
+                                          _ptr(kv_indptr), _ptr(kv_last_page_len), ctypes.byref(shp),
+                                          _ptr(status), _stream()))
+
+
+def select_pages(q, summaries, kv_indices, kv_indptr, kv_last_page_len, topk: int, num_pages: int,
+                 out=None, out_logical=None, out_scores=None, status=None):
+    """Score every filled page against the query group and pick the top-k pages.
+
+    q [B, Hq, D]; summaries [B, Hkv, n, D].  Returns int32 [B, Hkv, topk+1] physical page ids
+    (descending score, ties to the lowest page, then the page being filled; unused tail -1).
+    Replaces benchmark/blocktopk_decoder.py:216-221.
+    """
+    _cuda(q, summaries, kv_indices, kv_indptr, kv_last_page_len, out, out_logical, out_scores, status)
+    B, Hq, Dh = q.shape
+    Hkv = summaries.shape[1]
+    if q.dtype != summaries.dtype:
+        raise TypeError("q and summaries must share a dtype")
+    if kv_indptr.numel() - 1 != B or summaries.shape[0] < B:
+        raise ValueError("batch mismatch between q, kv_indptr and summaries")
+    if out is None:
+        out = torch.empty(B, Hkv, topk + 1, dtype=torch.int32, device=q.device)
+    shp = Shape(B, Hkv, Hq // Hkv, Dh, PAGE_SIZE, _dtype_code(q), num_pages)
+    check(_lib.load().ktk_select(_ptr(q), _ptr(summaries), summaries.shape[2], _ptr(kv_indices), _ptr(kv_indptr),
+                                 _ptr(kv_last_page_len), topk, _ptr(out), _ptr(out_logical), _ptr(out_scores),
+                                 ctypes.byref(shp), _ptr(status), _stream()))
+    return out
+
+
+def decode_num_splits(batch: int, num_kv_heads: int, group_size: int, max_entries: int, dtype=torch.bfloat16) -> int:
+    shp = Shape(batch, num_kv_heads, group_size, HEAD_DIM, PAGE_SIZE,
+                _lib.KTK_BF16 if dtype == torch.bfloat16 else _lib.KTK_F32, 0)
+    return int(_lib.load().ktk_decode_num_splits(ctypes.byref(shp), max_entries))
+
+
+def decode_workspace_bytes(batch: int, num_kv_heads: int, group_size: int, num_splits: int) -> int:
+    shp = Shape(batch, num_kv_heads, group_size, HEAD_DIM, PAGE_SIZE, _lib.KTK_BF16, 0)
+    return int(_lib.load().ktk_decode_workspace_bytes(ctypes.byref(shp), num_splits))
+
+
+def _decode_args(q, kv_cache, max_entries, workspace, num_splits):
+    B, Hq, _ = q.shape
+    shp = _shape(B, kv_cache, Hq)
+    if q.dtype != kv_cache.dtype:
+        raise TypeError("q and kv_cache must share a dtype")
+    if num_splits == 0:
+        num_splits = int(_lib.load().ktk_decode_num_splits(ctypes.byref(shp), max_entries))
+    need = int(_lib.load().ktk_decode_workspace_bytes(ctypes.byref(shp), num_splits))
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        raise RuntimeError(f"decode with {num_splits} splits needs a {need}-byte workspace "
+                           "(decode_workspace_bytes); pass one, or num_splits=1")
+    return shp, num_splits
+
+
+def sparse_decode(q, kv_cache, sel_pages, kv_indptr, kv_last_page_len, sm_scale: Optional[float] = None,
+                  workspace=None, num_splits: int = 0, variant: int = 0, out=None, status=None):
+    """Attention of q [B, Hq, D] over the pages listed in sel_pages [B, Hkv, topk+1].
+
+    Replaces mylib::decode -> flashinfer BatchDecodeWithPagedKVCacheWrapper.run
+    (benchmark/blocktopk_decoder.py:176-178).
+    """
+    _cuda(q, kv_cache, sel_pages, kv_indptr, kv_last_page_len, workspace, out, status)
+    topk = sel_pages.shape[-1] - 1
+    shp, num_splits = _decode_args(q, kv_cache, topk + 1, workspace, num_splits)
+    if sel_pages.dtype != torch.int32 or sel_pages.numel() != shp.batch * shp.num_kv_heads * (topk + 1):
+        raise ValueError("sel_pages must be int32 [B, Hkv, topk+1]")
+    if out is None:
+        out = torch.empty_like(q)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(q.shape[-1])
+    wsb = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    check(_lib.load().ktk_sparse_decode(_ptr(q), _ptr(kv_cache), _ptr(sel_pages), topk, _ptr(kv_indptr),
+                                        _ptr(kv_last_page_len), sm_scale, _ptr(out), _ptr(workspace), wsb,
+                                        num_splits, variant, ctypes.byref(shp), _ptr(status), _stream()))
+    return out
+
+
+def dense_decode(q, kv_cache, kv_indices, kv_indptr, kv_last_page_len, max_pages_per_seq: int,
+                 sm_scale: Optional[float] = None, workspace=None, num_splits: int = 0, variant: int = 0,
+                 out=None, status=None):
+    """Attention of q over every page of each sequence (benchmark/dense_decoder.py:168-170)."""
+    _cuda(q, kv_cache, kv_indices, kv_indptr, kv_last_page_len, workspace, out, status)
+    shp, num_splits = _decode_args(q, kv_cache, max_pages_per_seq, workspace, num_splits)
+    if out is None:
+        out = torch.empty_like(q)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(q.shape[-1])
+    wsb = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    check(_lib.load().ktk_dense_decode(_ptr(q), _ptr(kv_cache), _ptr(kv_indices), _ptr(kv_indptr),
+                                       _ptr(kv_last_page_len), max_pages_per_seq, sm_scale, _ptr(out),
+                                       _ptr(workspace), wsb, num_splits, variant, ctypes.byref(shp),
+                                       _ptr(status), _stream()))
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm over the last dimension (flashinfer.rmsnorm, benchmark/model_utils.py:12,23)."""
+    _cuda(x, weight)
+    if weight.dtype != x.dtype or weight.numel() != x.shape[-1]:
+        raise ValueError("rmsnorm: weight must be [cols] in the dtype of x")
+    out = torch.empty_like(x)
+    cols = x.shape[-1]
+    check(_lib.load().ktk_rmsnorm(_ptr(x), _ptr(weight), eps, _ptr(out), x.numel() // cols, cols, _dtype_code(x),
+                                  _stream()))
+    return out
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up (benchmark/blocktopk_decoder.py:235-236)."""
+    _cuda(gate, up)
+    if gate.shape != up.shape or gate.dtype != up.dtype:
+        raise ValueError("silu_mul: gate and up must match")
+    out = torch.empty_like(gate)
+    check(_lib.load().ktk_silu_mul(_ptr(gate), _ptr(up), _ptr(out), gate.numel(), _dtype_code(gate), _stream()))
+    return out
+
+
+# --------------------------------------------------------------------------------------
+# decode plans: what flashinfer keeps inside BatchDecodeWithPagedKVCacheWrapper
+# --------------------------------------------------------------------------------------
+
+class DecodePlan:
+    """State `mylib::decode(q, kv_cache)` needs beyond its two tensors.
+
+    The reference's op closes over a flashinfer wrapper holding the page-index buffers
+    (benchmark/blocktopk_decoder.py:153-160, :171-178).  Here a plan is bound to its
+    ``kv_cache`` tensor, so several layers (sparse and dense) coexist in one process.
+    """
+
+    def __init__(self, kv_cache, kv_indptr, kv_last_page_len, *, sel_pages=None, kv_indices=None,
+                 max_pages_per_seq: int = 0, sm_scale: Optional[float] = None, variant: int = 0,
+                 num_splits: int = 0, status=None):
+        if (sel_pages is None) == (kv_indices is None):
+            raise ValueError("a plan is either sparse (sel_pages) or dense (kv_indices)")
+        self.kv_cache, self.kv_indptr, self.kv_last_page_len = kv_cache, kv_indptr, kv_last_page_len
+        self.sel_pages, self.kv_indices = sel_pages, kv_indices
+        self.max_pages_per_seq = max_pages_per_seq
+        self.sm_scale, self.variant, self.status = sm_scale, variant, status
+        self.num_splits = num_splits
+        self.workspace = None
+
+    def _ensure_workspace(self, q):
+        B, Hq, _ = q.shape
+        hkv = self.kv_cache.shape[3]
+        entries = self.sel_pages.shape[-1] if self.sel_pages is not None else self.max_pages_per_seq
+        if self.num_splits == 0:
+            self.num_splits = decode_num_splits(B, hkv, Hq // hkv, entries, q.dtype)
+        need = decode_workspace_bytes(B, hkv, Hq // hkv, self.num_splits)
+        if need and (self.workspace is None or self.workspace.numel() < need):
+            self.workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+
+    def run(self, q):
+        self._ensure_workspace(q)
+        if self.sel_pages is not None:
+            return sparse_decode(q, self.kv_cache, self.sel_pages, self.kv_indptr, self.kv_last_page_len,
+                                 self.sm_scale, self.workspace, self.num_splits, self.variant, status=self.status)
+        return dense_decode(q, self.kv_cache, self.kv_indices, self.kv_indptr, self.kv_last_page_len,
+                            self.max_pages_per_seq, self.sm_scale, self.workspace, self.num_splits, self.variant,
+                            status=self.status)
+
+
+_PLANS: dict[int, DecodePlan] = {}
+_SUMMARIES: dict[int, torch.Tensor] = {}
+
+
+def bind_decode_plan(plan: DecodePlan) -> None:
+    _PLANS[plan.kv_cache.data_ptr()] = plan
+
+
+def bind_summaries(kv_cache: torch.Tensor, summaries: Optional[torch.Tensor]) -> None:
+    """Make `mylib::update_kv` on this cache also maintain `summaries`."""
+    if summaries is None:
+        _SUMMARIES.pop(kv_cache.data_ptr(), None)
+    else:
+        _SUMMARIES[kv_cache.data_ptr()] = summaries
+
+
+def unbind(kv_cache: torch.Tensor) -> None:
+    _PLANS.pop(kv_cache.data_ptr(), None)
+    _SUMMARIES.pop(kv_cache.data_ptr(), None)
+
+
+# --------------------------------------------------------------------------------------
+# torch custom ops (reference names and schemas)
+# --------------------------------------------------------------------------------------
+
+torch.library.define(
+    "mylib::update_kv",
+    "(Tensor k, Tensor v, Tensor kv_append_indptr, Tensor(a!) kv_cache, Tensor kv_page_indices, "
+    "Tensor kv_page_indptr, Tensor cachelen) -> ()",
+)
+
+
+@torch.library.impl("mylib::update_kv", "cuda")
+def _update_kv(k, v, kv_append_indptr, kv_cache, kv_page_indices, kv_page_indptr, kv_page_last_len):
+    # kv_append_indptr is arange(B+1) at decode (one token per sequence) and is not read
+    append_kv(k, v, kv_cache, _SUMMARIES.get(kv_cache.data_ptr()), kv_page_indices, kv_page_indptr,
+              kv_page_last_len)
+
+
+@torch.library.register_fake("mylib::update_kv")
+def _update_kv_fake(k, v, kv_append_indptr, kv_cache, kv_page_indices, kv_page_indptr, kv_page_last_len):
+    return None
+
+
+torch.library.define("mylib::decode", "(Tensor q, Tensor kv_cache) -> Tensor")
+
+
+@torch.library.impl("mylib::decode", "cuda")
+def _decode(q, kv_cache):
+    plan = _PLANS.get(kv_cache.data_ptr())
+    if plan is None:
+        raise RuntimeError("mylib::decode: no DecodePlan bound to this kv_cache (bind_decode_plan)")
+    return plan.run(q)
+
+
+@torch.library.register_fake("mylib::decode")
+def _decode_fake(q, kv_cache):
+    return torch.empty_like(q)
+
+
+torch.library.define("mylib::qk_norm", "(Tensor q, float variance_epsilon, Tensor weight) -> Tensor")
+
+
+@torch.library.impl("mylib::qk_norm", "cuda")
+def _qk_norm(q, variance_epsilon, weight):
+    return rmsnorm(q.contiguous(), weight, variance_epsilon)
+
+
+@torch.library.register_fake("mylib::qk_norm")
+def _qk_norm_fake(q, variance_epsilon, weight):
+    return torch.empty_like(q)
+
+
+torch.library.define("mylib::layer_norm", "(Tensor input, float variance_epsilon, Tensor weight) -> Tensor")
+
+
+@torch.library.impl("mylib::layer_norm", "cuda")
+def _layer_norm(input, variance_epsilon, weight):
+    return rmsnorm(input.contiguous(), weight, variance_epsilon)
+
+
+@torch.library.register_fake("mylib::layer_norm")
+def _layer_norm_fake(input, variance_epsilon, weight):
+    return torch.empty_like(input)
+
+
+torch.library.define(
+    "ktk::select_pages",
+    "(Tensor q, Tensor summaries, Tensor kv_indices, Tensor kv_indptr, Tensor kv_last_page_len, int topk, "
+    "int num_pages) -> Tensor",
+)
+
+
+@torch.library.impl("ktk::select_pages", "cuda")
+def _select_pages(q, summaries, kv_indices, kv_indptr, kv_last_page_len, topk, num_pages):
+    return select_pages(q, summaries, kv_indices, kv_indptr, kv_last_page_len, topk, num_pages)
+
+
+@torch.library.register_fake("ktk::select_pages")
+def _select_pages_fake(q, summaries, kv_indices, kv_indptr, kv_last_page_len, topk, num_pages):
+    return torch.empty(q.shape[0], summaries.shape[1], topk + 1, dtype=torch.int32, device=q.device)
+
+
+torch.library.define(
+    "ktk::sparse_decode",
+    "(Tensor q, Tensor kv_cache, Tensor sel_pages, Tensor kv_indptr, Tensor kv_last_page_len) -> Tensor",
+)
+
+
+@torch.library.impl("ktk::sparse_decode", "cuda")
+def _sparse_decode(q, kv_cache, sel_pages, kv_indptr, kv_last_page_len):
+    return sparse_decode(q, kv_cache, sel_pages, kv_indptr, kv_last_page_len, num_splits=1)
+
+
+@torch.library.register_fake("ktk::sparse_decode")
+def _sparse_decode_fake(q, kv_cache, sel_pages, kv_indptr, kv_last_page_len):
+    return torch.empty_like(q)
+
+
+torch.library.define(
+    "ktk::dense_decode",
+    "(Tensor q, Tensor kv_cache, Tensor kv_indices, Tensor kv_indptr, Tensor kv_last_page_len) -> Tensor",
+)
+
+
+@torch.library.impl("ktk::dense_decode", "cuda")
+def _dense_decode(q, kv_cache, kv_indices, kv_indptr, kv_last_page_len):
+    return dense_decode(q, kv_cache, kv_indices, kv_indptr, kv_last_page_len, 1, num_splits=1)
+
+
+@torch.library.register_fake("ktk::dense_decode")
+def _dense_decode_fake(q, kv_cache, kv_indices, kv_indptr, kv_last_page_len):
+    return torch.empty_like(q)
+
+
+torch.library.define(
+    "ktk::append_kv_with_summary",
+    "(Tensor k, Tensor v, Tensor(a!) kv_cache, Tensor(b!) summaries, Tensor kv_indices, Tensor kv_indptr, "
+    "Tensor kv_last_page_len) -> ()",
+)
+
+
+@torch.library.impl("ktk::append_kv_with_summary", "cuda")
+def _append_kv_with_summary(k, v, kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len):
+    append_kv(k, v, kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len)
+
+
+@torch.library.register_fake("ktk::append_kv_with_summary")
+def _append_kv_with_summary_fake(k, v, kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len):
+    return None
