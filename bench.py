@@ -1,0 +1,413 @@
+#!/usr/bin/env python
+"""Benchmark of the block top-k decode layer (one JSON line on stdout).
+
+    python bench.py --gpus N --steps K --warmup W            # this repository's CUDA path
+    python bench.py --impl reference --steps K --warmup W    # the reference's path on host cores
+
+Workload (default ``cfg3-shard``): one Qwen3-8B-shaped decoder layer at the paper's throughput shape
+-- batch 4096, 32768-token context, page size 16, block top-k budget of 128 pages, bf16 -- sharded
+8-way by KV head the way the reference benchmark does it (``--world_size 8``: one KV head, four
+query heads and 1/8 of the MLP per GPU, benchmark/blocktopk_decoder.py:101-106).  Every rank of an
+N-GPU run holds one such shard (weak scaling) and all-reduces the o_proj partial sums over NCCL.
+A step is one forward of the layer: RMSNorm, QKV projection, q/k-norm, paged append (+ page
+summary), page scoring + top-k selection, attention over the selected pages, o_proj (+ all-reduce),
+MLP.  The reported value is decode tokens/s in full-layer equivalents, ``batch * N / 8 / t_step``:
+with 8 ranks it is the throughput of the whole layer, with one rank it is the number the
+reference prints times its layer count (benchmark/blocktopk.py:82).
+
+Synthetic data: KV cache and hidden states N(0,1), weights N(0, 0.02), seeded.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # BASELINE.json configs[2] as one 8-way KV-head shard per GPU (68.2 GB of KV per GPU)
+    "cfg3-shard": dict(model="Qwen3-8B", tp=8, batch=4096, ctx=32768, topk=128),
+    # configs[1] at TP=8 and TP=1
+    "cfg2-shard": dict(model="Qwen3-8B", tp=8, batch=256, ctx=8192, topk=64),
+    "cfg2-tp1": dict(model="Qwen3-8B", tp=1, batch=256, ctx=8192, topk=64),
+    # configs[3] shape with uniform context (ragged contexts are covered by the parity tests)
+    "cfg4-shard": dict(model="Qwen3-32B", tp=8, batch=1024, ctx=8192, topk=64),
+    "tiny": dict(model="Qwen3-8B", tp=8, batch=64, ctx=2048, topk=16),
+}
+PAGE = 16
+HEAD_DIM = 128
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg3-shard", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=0, help="override the workload's batch size")
+    ap.add_argument("--variant", type=int, default=0, help="decode kernel: 0 auto, 1 fp32-FMA, 2 tensor-core")
+    ap.add_argument("--no-dense", action="store_true", help="skip the dense paged decode comparison")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--page-table", default="interleaved", choices=["interleaved", "random"])
+    ap.add_argument("--seed", type=int, default=1236)
+    ap.add_argument("--cpu-sample", type=int, default=32, help="sequences in the CPU sample")
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------------------------
+# clocks (read-only NVML sampling during the timed regions)
+# ------------------------------------------------------------------------------------------
+
+class ClockSampler:
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.index, self.period = index, period_s
+        self.sm, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    _NAMES = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+              0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+              0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.sm.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for bit, name in self._NAMES.items():
+                    if mask & bit and name != "gpu_idle":
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+            self._thread = None
+        return False
+
+    def summary(self):
+        if not self.sm:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        s = sorted(self.sm)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU baseline: the reference's layer forward on host cores, bounded sample of the workload
+# ------------------------------------------------------------------------------------------
+
+def cpu_reference_run(wl, sample_batch: int, steps: int, warmup: int, seed: int, budget_s: float = 20.0):
+    """Times oracle/reference_layer.py (torch on CPU, all host threads) on `sample_batch` sequences of the
+    workload's shape.  Returns (tokens_per_s in full-layer equivalents, ms_per_step, threads, steps_run)."""
+    from kinetics_b200.config import get_config
+    from oracle.reference_layer import ReferenceLayerCPU
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    cfg = get_config(wl["model"])
+    tp = wl["tp"]
+    hq, hkv, inter, hid = cfg.num_attention_heads // tp, cfg.num_key_value_heads // tp, cfg.intermediate_size // tp, cfg.hidden_size
+    n = wl["ctx"] // PAGE
+    B = sample_batch
+    g = torch.Generator().manual_seed(seed)
+    dt = torch.float32
+
+    def w(*shape):
+        return torch.empty(*shape, dtype=dt).normal_(0, 0.02, generator=g)
+
+    weights = {
+        "wqkv.weight": w((hq + 2 * hkv) * HEAD_DIM, hid), "wqkv.bias": w((hq + 2 * hkv) * HEAD_DIM),
+        "wo.weight": w(hid, hq * HEAD_DIM), "up_proj.weight": w(inter, hid), "gate_proj.weight": w(inter, hid),
+        "down_proj.weight": w(hid, inter), "qnorm_weight": torch.ones(HEAD_DIM), "knorm_weight": torch.ones(HEAD_DIM),
+        "input_layernorm_weight": torch.ones(hid), "post_attention_layernorm_weight": torch.ones(hid),
+    }
+    pages = B * (n + 1)
+    kv = torch.empty(pages, 2, PAGE, hkv, HEAD_DIM, dtype=dt).normal_(generator=g)
+    table = (torch.arange(n + 1)[None, :] * B + torch.arange(B)[:, None])
+    summ = kv[table[:, :n], 0].mean(2).permute(0, 2, 1, 3).contiguous()          # [B, Hkv, n, D]
+    layer = ReferenceLayerCPU(weights, kv, table, summ, hq, hkv, HEAD_DIM, cfg.rms_norm_eps, wl["topk"])
+    x = torch.empty(B, 1, hid, dtype=dt).normal_(generator=g)
+    for _ in range(max(1, warmup)):
+        layer.forward(x)
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(steps):
+        layer.forward(x)
+        done += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    dt_s = (time.perf_counter() - t0) / done
+    return B / tp / dt_s, dt_s * 1e3, threads, done
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wl = dict(WORKLOADS[args.workload])
+    if args.batch:
+        wl["batch"] = args.batch
+    value, ms, threads, done = cpu_reference_run(wl, args.cpu_sample, args.steps, args.warmup, args.seed,
+                                                 budget_s=120.0)
+    sample = (f"{args.cpu_sample} of {wl['batch']} sequences of the workload per step, fp32, "
+              f"torch on {threads} host threads")
+    line = {
+        "impl": "reference", "metric": "block-top-k decode tokens/s (Qwen3-8B layer, B=4096, 32K ctx)",
+        "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": done, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(args, wl, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, wl, n_gpus):
+    return {
+        "workload": (f"{args.workload}: {wl['model']} decoder layer, 8-way KV-head shard per GPU "
+                     f"(tp={wl['tp']}), batch {wl['batch']}, context {wl['ctx']}, page {PAGE}, "
+                     f"top-k {wl['topk']} pages, one decode step"),
+        "batch": wl["batch"], "context": wl["ctx"], "page_size": PAGE, "topk_pages": wl["topk"],
+        "tp_shards_total": wl["tp"], "shards_resident": n_gpus, "page_table": args.page_table,
+        "l2": "per-step traffic (summaries + selected pages) exceeds the 126 MB L2; no flush needed",
+        "parallelism": f"tp{wl['tp']} by KV head, {n_gpus} shard(s) resident, o_proj all-reduce over NCCL"
+                       if n_gpus > 1 else f"tp{wl['tp']} by KV head, 1 shard resident",
+    }
+
+
+# ------------------------------------------------------------------------------------------
+# this repository's path
+# ------------------------------------------------------------------------------------------
+
+def mean_ms(pairs):
+    return sum(a.elapsed_time(b) for a, b in pairs) / max(len(pairs), 1)
+
+
+def run_ours(args):
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this path has no CPU fallback (use --impl reference)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    pg = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        pg = dist.group.WORLD
+
+    import kinetics_b200 as kb
+    from kinetics_b200 import ops
+
+    wl = dict(WORKLOADS[args.workload])
+    if args.batch:
+        wl["batch"] = args.batch
+    cfg = kb.get_config(wl["model"])
+    tp, B, ctx, topk = wl["tp"], wl["batch"], wl["ctx"], wl["topk"]
+    dtype = torch.bfloat16
+    torch.manual_seed(args.seed * 1000 + rank)
+
+    def make(cls, **kw):
+        layer = cls(config=cfg, world_size=tp, batch_size=B, prefix_len=ctx, max_len=ctx + 512, page_size=PAGE,
+                    device=device, dtype=dtype, page_table=args.page_table, process_group=pg,
+                    seed=args.seed + rank, variant=args.variant, **kw)
+        for m in layer.modules():
+            if isinstance(m, torch.nn.Linear):
+                torch.nn.init.normal_(m.weight, 0.0, 0.02)
+                if m.bias is not None:
+                    torch.nn.init.normal_(m.bias, 0.0, 0.02)
+        layer.eval()
+        layer.to(device, dtype=dtype)
+        return layer
+
+    sparse = make(kb.BlockTopkDecoderLayer, topk_page=topk)
+    hidden = torch.randn(B, 1, cfg.hidden_size, device=device, dtype=dtype)
+    static_in, static_out, graph = sparse.make_graphed(hidden)
+    sparse.check_status()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local)
+
+    # ---- timed region: K graph replays, inputs resident in HBM ----
+    for _ in range(args.warmup):
+        graph.replay()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with sampler:
+        e0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record()
+        barrier()
+    ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    value = B * world / tp / (ms_step * 1e-3)
+
+    # ---- per-kernel durations, CUDA events around each of our kernels in an eager pass ----
+    sparse.timers = {}
+    ksteps = max(5, min(args.steps, 50))
+    launches0 = ops.launch_count()
+    with sampler:
+        for _ in range(ksteps):
+            sparse.forward(static_in)
+        torch.cuda.synchronize()
+    launches_per_step = (ops.launch_count() - launches0) // ksteps
+    timers, sparse.timers = sparse.timers, None
+    t_select = mean_ms(timers["select"][2:])
+    t_decode = mean_ms(timers["decode"][2:])
+    t_append = mean_ms(timers["append"][2:])
+    hkv = cfg.num_key_value_heads // tp
+    esz = 2
+    bytes_select = B * hkv * (ctx // PAGE) * HEAD_DIM * esz
+    bytes_decode = B * hkv * (min(topk, ctx // PAGE) + 1) * PAGE * HEAD_DIM * 2 * esz
+    peaks = {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except Exception:
+        pass
+    peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
+    peak_kind = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+    ach_decode = bytes_decode / (t_decode * 1e-3) / 1e9
+    ach_select = bytes_select / (t_select * 1e-3) / 1e9
+    ach_attn = (bytes_decode + bytes_select) / ((t_decode + t_select) * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "sparse decode (selected K/V pages)", "achieved": ach_decode,
+                "peak": peak_gbs, "unit": "GB/s", "frac": ach_decode / peak_gbs, "traffic": None,
+                "peak_kind": peak_kind, "ms": t_decode, "algorithmic_bytes": bytes_decode}
+    kernels = {
+        "select": {"ms": t_select, "algorithmic_bytes": bytes_select, "achieved_gbs": ach_select,
+                   "frac": ach_select / peak_gbs},
+        "decode": {"ms": t_decode, "algorithmic_bytes": bytes_decode, "achieved_gbs": ach_decode,
+                   "frac": ach_decode / peak_gbs},
+        "append": {"ms": t_append},
+        "attention_total": {"ms": t_select + t_decode, "achieved_gbs": ach_attn, "frac": ach_attn / peak_gbs,
+                            "frac_of_8TBs_nominal": ach_attn / 8000.0},
+    }
+
+    # ---- end to end: host buffers in, host buffers out, every step ----
+    e2e = None
+    if not args.no_e2e:
+        host_in = torch.randn(B, 1, cfg.hidden_size, dtype=dtype).pin_memory()
+        host_out = torch.empty(B, 1, cfg.hidden_size, dtype=dtype).pin_memory()
+        for _ in range(3):
+            static_in.copy_(host_in, non_blocking=True)
+            graph.replay()
+            host_out.copy_(static_out, non_blocking=True)
+        barrier()
+        with sampler:
+            e0.record()
+            for _ in range(args.steps):
+                static_in.copy_(host_in, non_blocking=True)
+                graph.replay()
+                host_out.copy_(static_out, non_blocking=True)
+            e1.record()
+            barrier()
+        ms_e2e = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+        nbytes = host_in.numel() * host_in.element_size()
+        e2e = {"value": B * world / tp / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
+    sparse.check_status()
+
+    # ---- the repository's dense paged decode at the same shape, sharing the KV cache ----
+    dense_info = None
+    if not args.no_dense:
+        dense = make(kb.DecoderLayer, kv_cache=sparse.kv_cache)
+        dense.timers = {}
+        dsteps = 4
+        for _ in range(2):
+            dense.forward(static_in)
+        barrier()
+        e0.record()
+        for _ in range(dsteps):
+            dense.forward(static_in)
+        e1.record()
+        barrier()
+        ms_dense = max_over_ranks(e0.elapsed_time(e1) / dsteps)
+        t_dd = mean_ms(dense.timers["decode"][2:])
+        dense.timers = None
+        bytes_dense = B * hkv * (ctx // PAGE + 1) * PAGE * HEAD_DIM * 2 * esz
+        dense_info = {"tokens_per_s": B * world / tp / (ms_dense * 1e-3), "ms_per_step": ms_dense,
+                      "decode_ms": t_dd, "decode_gbs": bytes_dense / (t_dd * 1e-3) / 1e9,
+                      "sparse_over_dense": ms_dense / ms_step}
+        dense.check_status()
+        del dense
+
+    # ---- CPU baseline (rank 0, single-GPU run only) ----
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        sys.path.insert(0, ROOT)
+        v, ms, threads, done = cpu_reference_run(wl, args.cpu_sample, 1000, 1, args.seed, budget_s=15.0)
+        cpu = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "ms_per_step": ms,
+               "sample": f"{args.cpu_sample} of {B} sequences of the workload per step, {done} steps, fp32, "
+                         f"torch on {threads} host threads (oracle/reference_layer.py)"}
+
+    if rank == 0:
+        line = {
+            "metric": "block-top-k decode tokens/s (Qwen3-8B layer, B=4096, 32K ctx)", "value": value,
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(args, wl, world), "roofline": roofline, "kernels": kernels,
+            "cpu_baseline": cpu, "e2e": e2e, "dense": dense_info,
+            "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
+            "clocks": sampler.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

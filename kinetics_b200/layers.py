@@ -51,11 +51,31 @@ def random_page_table(batch_size: int, pages_per_req: int, num_pages: int, devic
     return perm.to(torch.int32).view(batch_size, pages_per_req).to(device).contiguous()
 
 
+class _EventPair:
+    """Brackets a kernel with CUDA events on the current stream when timing is switched on."""
+
+    def __init__(self, sink, name):
+        self.sink, self.name = sink, name
+
+    def __enter__(self):
+        if self.sink is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+
+    def __exit__(self, *exc):
+        if self.sink is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            self.sink.setdefault(self.name, []).append((self.start, end))
+        return False
+
+
 class _PagedDecoderLayer(nn.Module):
     """Shared body: weights, paged KV state, the non-attention part of forward."""
 
     def __init__(self, config, world_size, batch_size, prefix_len, max_len, page_size, device, dtype,
-                 page_table: str = "interleaved", process_group=None, seed: int = 0, variant: int = 0):
+                 page_table: str = "interleaved", process_group=None, seed: int = 0, variant: int = 0,
+                 kv_cache: Optional[torch.Tensor] = None):
         super().__init__()
         self.num_heads = config.num_attention_heads // world_size
         self.num_kv_heads = config.num_key_value_heads // world_size
@@ -116,12 +136,21 @@ class _PagedDecoderLayer(nn.Module):
         self.qkv_indptr = torch.arange(batch_size + 1, dtype=torch.int32, device=device)
         self.status = ops.new_status(device)
 
-        self.kv_cache = torch.randn(self.total_pages, 2, page_size, self.num_kv_heads, self.head_dim,
-                                    dtype=dtype, device=device)
+        shape = (self.total_pages, 2, page_size, self.num_kv_heads, self.head_dim)
+        if kv_cache is None:
+            kv_cache = torch.randn(*shape, dtype=dtype, device=device)
+        elif tuple(kv_cache.shape) != shape or kv_cache.dtype != dtype:
+            raise ValueError(f"kv_cache must be {shape} {dtype}")
+        self.kv_cache = kv_cache          # may be shared with another layer (dense next to sparse)
         self.decode_run = torch.ops.mylib.decode
+        self.capture = None               # set to a dict to keep q / k / v of the last forward (tests)
+        self.timers = None                # set to a dict name -> list of (start, end) CUDA events
 
     # -- attention-specific parts, provided by the subclasses --
     def _attention(self, query_states):
+        raise NotImplementedError
+
+    def _bind(self):
         raise NotImplementedError
 
     def _mlp(self, hidden_states):
@@ -136,6 +165,7 @@ class _PagedDecoderLayer(nn.Module):
 
     @torch.inference_mode()
     def forward(self, hidden_states):
+        self._bind()      # the torch ops find this layer's page state through its kv_cache
         residual = hidden_states
         hidden_states = torch.ops.mylib.layer_norm(hidden_states, self.input_layernorm_variance_epsilon,
                                                    self.input_layernorm_weight)
@@ -152,8 +182,11 @@ class _PagedDecoderLayer(nn.Module):
         query_states = query_states.reshape(bsz, self.num_heads, self.head_dim)
         key_states = key_states.reshape(bsz, self.num_kv_heads, self.head_dim)
 
-        torch.ops.mylib.update_kv(key_states, value_states, self.qkv_indptr, self.kv_cache,
-                                  self.paged_kv_indices, self.full_kv_indptr, self.last_kv_lens)
+        if self.capture is not None:
+            self.capture.update(q=query_states.clone(), k=key_states.clone(), v=value_states.clone())
+        with self._timed("append"):
+            torch.ops.mylib.update_kv(key_states, value_states, self.qkv_indptr, self.kv_cache,
+                                      self.paged_kv_indices, self.full_kv_indptr, self.last_kv_lens)
         o = self._attention(query_states)
         o = o.reshape(bsz, q_len, self.head_dim * self.num_heads)
         hidden_states = self.wo(o)
@@ -165,6 +198,9 @@ class _PagedDecoderLayer(nn.Module):
                                                    self.post_attention_layernorm_weight)
         hidden_states = self._mlp(hidden_states)
         return residual + hidden_states
+
+    def _timed(self, name):
+        return _EventPair(self.timers, name)
 
     def check_status(self):
         """Synchronising check of the device status word."""
@@ -211,10 +247,16 @@ class BlockTopkDecoderLayer(_PagedDecoderLayer):
 
     def _attention(self, query_states):
         # benchmark/blocktopk_decoder.py:216-221, one kernel
-        ops.select_pages(query_states, self.compressed_key_cache, self.paged_kv_indices, self.full_kv_indptr,
-                         self.last_kv_lens, self.topk_page, self.total_pages, out=self._sel_view(),
-                         status=self.status)
-        return self.decode_run(query_states, self.kv_cache)
+        with self._timed("select"):
+            ops.select_pages(query_states, self.compressed_key_cache, self.paged_kv_indices, self.full_kv_indptr,
+                             self.last_kv_lens, self.topk_page, self.total_pages, out=self._sel_view(),
+                             status=self.status)
+        with self._timed("decode"):
+            return self.decode_run(query_states, self.kv_cache)
+
+    def _bind(self):
+        ops.bind_summaries(self.kv_cache, self.compressed_key_cache)
+        ops.bind_decode_plan(self.decode_plan)
 
     def prepare_wrapper(self, prefix_len=None, topk_page_indices=None):
         """Bind the decode plan (reference: flashinfer wrapper.plan, :243-265).
@@ -238,7 +280,11 @@ class DecoderLayer(_PagedDecoderLayer):
         self.prepare_wrapper()
 
     def _attention(self, query_states):
-        return self.decode_run(query_states, self.kv_cache)
+        with self._timed("decode"):
+            return self.decode_run(query_states, self.kv_cache)
+
+    def _bind(self):
+        ops.bind_decode_plan(self.decode_plan)
 
     def prepare_wrapper(self):
         plan = ops.DecodePlan(self.kv_cache, self.full_kv_indptr, self.last_kv_lens,

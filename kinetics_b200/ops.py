@@ -27,6 +27,18 @@ from ._lib import Shape, check
 HEAD_DIM = 128
 PAGE_SIZE = 16
 
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Kernels of libktk.so launched from this process so far."""
+    return _LAUNCHES
+
+
+def _launched(n: int = 1) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
 
 def _dtype_code(t: torch.Tensor) -> int:
     if t.dtype == torch.bfloat16:
@@ -101,6 +113,7 @@ def append_kv(k, v, kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len
     check(_lib.load().ktk_append(_ptr(k), _ptr(v), _ptr(kv_cache), _ptr(summaries), stride, _ptr(kv_indices),
                                  _ptr(kv_indptr), _ptr(kv_last_page_len), ctypes.byref(shp), _ptr(status),
                                  _stream()))
+    _launched()
 
 
 def build_summaries(kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len, status=None) -> None:
@@ -113,6 +126,7 @@ def build_summaries(kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len
     check(_lib.load().ktk_build_summaries(_ptr(kv_cache), _ptr(summaries), summaries.shape[2], _ptr(kv_indices),
                                           _ptr(kv_indptr), _ptr(kv_last_page_len), ctypes.byref(shp),
                                           _ptr(status), _stream()))
+    _launched()
 
 
 def select_pages(q, summaries, kv_indices, kv_indptr, kv_last_page_len, topk: int, num_pages: int,
@@ -136,6 +150,7 @@ def select_pages(q, summaries, kv_indices, kv_indptr, kv_last_page_len, topk: in
     check(_lib.load().ktk_select(_ptr(q), _ptr(summaries), summaries.shape[2], _ptr(kv_indices), _ptr(kv_indptr),
                                  _ptr(kv_last_page_len), topk, _ptr(out), _ptr(out_logical), _ptr(out_scores),
                                  ctypes.byref(shp), _ptr(status), _stream()))
+    _launched()
     return out
 
 
@@ -184,6 +199,7 @@ def sparse_decode(q, kv_cache, sel_pages, kv_indptr, kv_last_page_len, sm_scale:
     check(_lib.load().ktk_sparse_decode(_ptr(q), _ptr(kv_cache), _ptr(sel_pages), topk, _ptr(kv_indptr),
                                         _ptr(kv_last_page_len), sm_scale, _ptr(out), _ptr(workspace), wsb,
                                         num_splits, variant, ctypes.byref(shp), _ptr(status), _stream()))
+    _launched(2 if num_splits > 1 else 1)
     return out
 
 
@@ -214,6 +230,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     cols = x.shape[-1]
     check(_lib.load().ktk_rmsnorm(_ptr(x), _ptr(weight), eps, _ptr(out), x.numel() // cols, cols, _dtype_code(x),
                                   _stream()))
+    _launched()
     return out
 
 
@@ -224,6 +241,7 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
         raise ValueError("silu_mul: gate and up must match")
     out = torch.empty_like(gate)
     check(_lib.load().ktk_silu_mul(_ptr(gate), _ptr(up), _ptr(out), gate.numel(), _dtype_code(gate), _stream()))
+    _launched()
     return out
 
 

@@ -1,0 +1,292 @@
+"""CUDA kernels (through the C ABI) against the CPU oracle on the same seeded inputs."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import CASES, P, case_state, load_golden, paged_state, random_case, to_dev
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _bits(t):
+    return t.view(torch.int16 if t.dtype == torch.bfloat16 else torch.int32)
+
+
+def _ops():
+    from kinetics_b200 import ops
+    return ops
+
+
+def _tol(dtype):
+    # north-star tolerances: 1e-4 abs/rel in fp32, 2e-2 in bf16
+    return 1e-4 if dtype == torch.float32 else 2e-2
+
+
+# ---------------------------------------------------------------- append + summaries
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_append_and_summaries_bit_exact(cuda_device, dtype):
+    ops = _ops()
+    torch.manual_seed(7)
+    B, Hkv, npg_max, steps = 5, 2, 4, 50
+    total = B * npg_max + 3
+    table = torch.randperm(total)[: B * npg_max].view(B, npg_max).to(torch.int32)
+    cache_c = torch.zeros(total, 2, P, Hkv, 128, dtype=dtype)
+    summ_c = torch.zeros(B, Hkv, npg_max, 128, dtype=dtype)
+    cache_g, summ_g = cache_c.to(cuda_device), summ_c.to(cuda_device)
+    status = ops.new_status(cuda_device)
+    for s in range(steps):
+        npg = s // P + 1
+        indices = table[:, :npg].contiguous().view(-1)
+        indptr = (torch.arange(B + 1) * npg).to(torch.int32)
+        last = torch.full((B,), s % P + 1, dtype=torch.int32)
+        k = torch.randn(B, Hkv, 128).to(dtype)
+        v = torch.randn(B, Hkv, 128).to(dtype)
+        oracle.append(k, v, cache_c, summ_c, indices, indptr, last)
+        ops.append_kv(k.to(cuda_device), v.to(cuda_device), cache_g, summ_g, indices.to(cuda_device),
+                      indptr.to(cuda_device), last.to(cuda_device), status=status)
+    ops.raise_on_status(status)
+    assert torch.equal(_bits(cache_g.cpu()), _bits(cache_c))
+    assert torch.equal(_bits(summ_g.cpu()), _bits(summ_c))
+    # bulk rebuild gives the same summaries
+    rebuilt = torch.zeros_like(summ_g)
+    ops.build_summaries(cache_g, rebuilt, indices.to(cuda_device), indptr.to(cuda_device), last.to(cuda_device),
+                        status=status)
+    ops.raise_on_status(status)
+    assert torch.equal(_bits(rebuilt.cpu()), _bits(summ_c))
+
+
+def test_append_ragged_and_empty(cuda_device):
+    ops = _ops()
+    dtype = torch.bfloat16
+    lens = [0, 17, 1, 32]                      # an empty slot, mid-page, first token, page just filled
+    q, k, v = random_case(3, 4, 2, 2, lens, dtype)
+    st = paged_state(k, v, lens, dtype, seed=1, fill=0.0)
+    # drop the newest token from the cache, append it back with the kernel
+    want = st["kv_cache"].clone()
+    cache = st["kv_cache"].clone()
+    knew = torch.zeros(4, 2, 128, dtype=dtype)
+    vnew = torch.zeros(4, 2, 128, dtype=dtype)
+    for b, n in enumerate(lens):
+        if n == 0:
+            continue
+        page = int(st["kv_indices"][st["kv_indptr"][b + 1] - 1])
+        slot = int(st["kv_last_page_len"][b]) - 1
+        knew[b], vnew[b] = cache[page, 0, slot], cache[page, 1, slot]
+        cache[page, :, slot] = 0
+    summ = torch.zeros(4, 2, st["summary_stride"], 128, dtype=dtype)
+    d = to_dev(st, cuda_device)
+    cache_g, summ_g = cache.to(cuda_device), summ.to(cuda_device)
+    status = ops.new_status(cuda_device)
+    ops.append_kv(knew.to(cuda_device), vnew.to(cuda_device), cache_g, summ_g, d["kv_indices"], d["kv_indptr"],
+                  d["kv_last_page_len"], status=status)
+    ops.raise_on_status(status)
+    assert torch.equal(_bits(cache_g.cpu()), _bits(want))
+    ref = oracle.summaries(want, st["kv_indices"], st["kv_indptr"], st["kv_last_page_len"], st["summary_stride"])
+    for b, n in enumerate(lens):
+        if n:
+            lastp = st["npages"][b] - 1
+            assert torch.equal(_bits(summ_g.cpu()[b, :, lastp]), _bits(ref[b, :, lastp]))
+
+
+# ---------------------------------------------------------------- selection
+
+def _select_both(ops, q, st, topk, device):
+    summ = oracle.summaries(st["kv_cache"], st["kv_indices"], st["kv_indptr"], st["kv_last_page_len"],
+                            st["summary_stride"])
+    sc = oracle.scores(q, summ, st["kv_indptr"])
+    phys, logical = oracle.select_from_scores(sc, st["kv_indices"], st["kv_indptr"], topk)
+    d = to_dev(st, device)
+    summ_g = torch.zeros_like(summ, device=device)
+    status = ops.new_status(device)
+    ops.build_summaries(d["kv_cache"], summ_g, d["kv_indices"], d["kv_indptr"], d["kv_last_page_len"], status=status)
+    assert torch.equal(_bits(summ_g.cpu()), _bits(summ))
+    B, Hkv = summ.shape[:2]
+    out_l = torch.empty(B, Hkv, topk + 1, dtype=torch.int32, device=device)
+    out_s = torch.full((B, Hkv, st["summary_stride"]), float("nan"), device=device)
+    out_p = ops.select_pages(q.to(device), summ_g, d["kv_indices"], d["kv_indptr"], d["kv_last_page_len"], topk,
+                             st["num_pages"], out_logical=out_l, out_scores=out_s, status=status)
+    ops.raise_on_status(status)
+    return (phys, logical, sc), (out_p.cpu(), out_l.cpu(), out_s.cpu()), d, summ_g
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_select_bit_exact_on_golden_cases(cuda_device, name):
+    ops = _ops()
+    case, st, q = case_state(name, seed=4)
+    (phys, logical, sc), (gp, gl, gs), _, _ = _select_both(ops, q, st, case["topk"], cuda_device)
+    assert torch.equal(gl, logical)
+    assert torch.equal(gp, phys)
+    for b, npg in enumerate(st["npages"]):
+        assert torch.equal(gs[b, :, : npg - 1].view(torch.int32), sc[b, :, : npg - 1].view(torch.int32))
+    # and the reference's own kept sets
+    gold = load_golden(name)
+    for b, npg in enumerate(st["npages"]):
+        cnt = min(case["topk"], npg - 1)
+        for h in range(gl.shape[1]):
+            ref = gold["kept"][b, h][gold["kept"][b, h] >= 0]
+            assert np.array_equal(np.sort(gl[b, h, :cnt].numpy()), ref)
+
+
+@pytest.mark.parametrize("dtype,G,Hkv,topk,lens", [
+    (torch.bfloat16, 4, 1, 128, [32769, 32768, 20000]),      # 2048 scored pages, the headline shape
+    (torch.bfloat16, 8, 2, 64, [16385, 1025, 4000, 9999]),
+    (torch.float32, 4, 1, 16, [2049, 2049]),
+    (torch.bfloat16, 2, 3, 32, [513, 1, 16, 17, 5000]),
+    (torch.float32, 1, 2, 1, [100, 33]),
+    (torch.bfloat16, 4, 1, 1024, [20001]),                   # largest budget
+])
+def test_select_bit_exact_random(cuda_device, dtype, G, Hkv, topk, lens):
+    ops = _ops()
+    q, k, v = random_case(99, len(lens), Hkv, G, lens, dtype)
+    st = paged_state(k, v, lens, dtype, seed=8)
+    (phys, logical, sc), (gp, gl, gs), _, _ = _select_both(ops, q, st, topk, cuda_device)
+    assert torch.equal(gl, logical)
+    assert torch.equal(gp, phys)
+
+
+def test_select_ties_go_to_lowest_page(cuda_device):
+    ops = _ops()
+    dtype = torch.bfloat16
+    lens = [16 * 300 + 3, 16 * 40 + 16]
+    q, k, v = random_case(5, 2, 2, 4, lens, dtype)
+    k[0] = 0.0                                   # all scores equal (+0)
+    k[1, :, : 16 * 20] = k[1, :, 16 * 20: 16 * 40]   # every score appears twice
+    st = paged_state(k, v, lens, dtype, seed=3)
+    (phys, logical, sc), (gp, gl, gs), _, _ = _select_both(ops, q, st, 24, cuda_device)
+    assert gl[0, 0, :24].tolist() == list(range(24))
+    assert torch.equal(gl, logical) and torch.equal(gp, phys)
+
+
+def test_select_reports_bad_page_id(cuda_device):
+    ops = _ops()
+    dtype = torch.float32
+    lens = [200]
+    q, k, v = random_case(6, 1, 1, 4, lens, dtype)
+    st = paged_state(k, v, lens, dtype, seed=3)
+    d = to_dev(st, cuda_device)
+    summ = oracle.summaries(st["kv_cache"], st["kv_indices"], st["kv_indptr"], st["kv_last_page_len"],
+                            st["summary_stride"]).to(cuda_device)
+    bad = d["kv_indices"].clone()
+    bad[:] = st["num_pages"] + 5
+    status = ops.new_status(cuda_device)
+    ops.select_pages(q.to(cuda_device), summ, bad, d["kv_indptr"], d["kv_last_page_len"], 4, st["num_pages"],
+                     status=status)
+    assert int(status.item()) == 1
+    # the decode kernel skips such pages instead of reading them
+    sel = torch.full((1, 1, 5), st["num_pages"] + 5, dtype=torch.int32, device=cuda_device)
+    status.zero_()
+    out = ops.sparse_decode(q.to(cuda_device), d["kv_cache"], sel, d["kv_indptr"], d["kv_last_page_len"],
+                            num_splits=1, variant=1, status=status)
+    assert int(status.item()) == 1
+    assert torch.isfinite(out).all()
+
+
+# ---------------------------------------------------------------- decode
+
+VARIANTS = {torch.float32: [1], torch.bfloat16: [1]}
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_sparse_decode_on_golden_cases(cuda_device, name):
+    ops = _ops()
+    case, st, q = case_state(name, seed=4)
+    dtype = q.dtype
+    topk = case["topk"]
+    (phys, logical, sc), (gp, gl, gs), d, _ = _select_both(ops, q, st, topk, cuda_device)
+    ref = oracle.decode(q, st["kv_cache"], phys, topk, st["kv_indptr"], st["kv_last_page_len"],
+                        oracle.default_scale())
+    gold = load_golden(name)
+    tol = _tol(dtype)
+    B, Hq = q.shape[:2]
+    for variant in VARIANTS[dtype]:
+        for splits in (1, 2, 5):
+            ws = torch.empty(max(ops.decode_workspace_bytes(B, gp.shape[1], Hq // gp.shape[1], splits), 1),
+                             dtype=torch.uint8, device=cuda_device)
+            out = ops.sparse_decode(q.to(cuda_device), d["kv_cache"], gp.to(cuda_device), d["kv_indptr"],
+                                    d["kv_last_page_len"], workspace=ws, num_splits=splits, variant=variant)
+            np.testing.assert_allclose(out.float().cpu().numpy(), ref.numpy(), rtol=tol, atol=tol)
+            np.testing.assert_allclose(out.float().cpu().numpy(), gold["out"], rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("dtype,G,Hkv,lens", [
+    (torch.bfloat16, 4, 1, [2049, 100, 16, 1]),
+    (torch.bfloat16, 8, 2, [777, 1300]),
+    (torch.float32, 4, 2, [300, 45]),
+    (torch.float32, 1, 1, [64, 65]),
+    (torch.bfloat16, 2, 4, [31, 32, 33]),
+])
+def test_dense_decode_vs_oracle(cuda_device, dtype, G, Hkv, lens):
+    ops = _ops()
+    q, k, v = random_case(21, len(lens), Hkv, G, lens, dtype)
+    st = paged_state(k, v, lens, dtype, seed=9)
+    d = to_dev(st, cuda_device)
+    ref = oracle.decode(q, st["kv_cache"], st["kv_indices"], -1, st["kv_indptr"], st["kv_last_page_len"],
+                        oracle.default_scale())
+    tol = _tol(dtype)
+    B, Hq = q.shape[:2]
+    for variant in VARIANTS[dtype]:
+        for splits in (1, 3, 0):
+            s_eff = splits or ops.decode_num_splits(B, Hkv, G, max(st["npages"]), dtype)
+            ws = torch.empty(max(ops.decode_workspace_bytes(B, Hkv, G, s_eff), 1), dtype=torch.uint8,
+                             device=cuda_device)
+            out = ops.dense_decode(q.to(cuda_device), d["kv_cache"], d["kv_indices"], d["kv_indptr"],
+                                   d["kv_last_page_len"], max(st["npages"]), workspace=ws, num_splits=splits,
+                                   variant=variant)
+            np.testing.assert_allclose(out.float().cpu().numpy(), ref.numpy(), rtol=tol, atol=tol)
+
+
+def test_sparse_equals_dense_when_budget_covers_everything(cuda_device):
+    ops = _ops()
+    dtype = torch.bfloat16
+    lens = [500, 129]
+    q, k, v = random_case(22, 2, 2, 4, lens, dtype)
+    st = paged_state(k, v, lens, dtype, seed=9)
+    (phys, *_), (gp, *_), d, _ = _select_both(ops, q, st, 40, cuda_device)
+    a = ops.sparse_decode(q.to(cuda_device), d["kv_cache"], gp.to(cuda_device), d["kv_indptr"],
+                          d["kv_last_page_len"], num_splits=1, variant=1)
+    b = ops.dense_decode(q.to(cuda_device), d["kv_cache"], d["kv_indices"], d["kv_indptr"], d["kv_last_page_len"],
+                         max(st["npages"]), num_splits=1, variant=1)
+    assert torch.equal(a, b)
+
+
+def test_large_logits_do_not_overflow(cuda_device):
+    ops = _ops()
+    dtype = torch.bfloat16
+    lens = [400]
+    q, k, v = random_case(23, 1, 1, 4, lens, dtype, scale=6.0)   # logits of a few hundred
+    st = paged_state(k, v, lens, dtype, seed=9)
+    d = to_dev(st, cuda_device)
+    ref = oracle.decode(q, st["kv_cache"], st["kv_indices"], -1, st["kv_indptr"], st["kv_last_page_len"],
+                        oracle.default_scale())
+    out = ops.dense_decode(q.to(cuda_device), d["kv_cache"], d["kv_indices"], d["kv_indptr"],
+                           d["kv_last_page_len"], 25, num_splits=1, variant=1)
+    assert torch.isfinite(out).all()
+    np.testing.assert_allclose(out.float().cpu().numpy(), ref.numpy(), rtol=3e-2, atol=3e-2)
+
+
+# ---------------------------------------------------------------- small ops
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("cols", [128, 4096, 1000])
+def test_rmsnorm(cuda_device, dtype, cols):
+    ops = _ops()
+    torch.manual_seed(1)
+    x = torch.randn(37, cols).to(dtype)
+    w = (torch.rand(cols) + 0.5).to(dtype)
+    ref = (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6) * w.float())
+    out = ops.rmsnorm(x.to(cuda_device), w.to(cuda_device), 1e-6)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(cuda_device, dtype):
+    ops = _ops()
+    torch.manual_seed(2)
+    g, u = torch.randn(3, 1, 1536).to(dtype), torch.randn(3, 1, 1536).to(dtype)
+    ref = torch.nn.functional.silu(g.float()) * u.float()
+    out = ops.silu_mul(g.to(cuda_device), u.to(cuda_device))
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=tol, atol=tol)
