@@ -54,6 +54,7 @@ def parse():
     ap.add_argument("--workload", default="cfg3-shard", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch size")
     ap.add_argument("--variant", type=int, default=0, help="decode kernel: 0 auto, 1 fp32-FMA, 2 tensor-core")
+    ap.add_argument("--splits", type=int, default=0, help="decode split count (0 = library policy)")
     ap.add_argument("--no-dense", action="store_true", help="skip the dense paged decode comparison")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     ap.add_argument("--no-e2e", action="store_true")
@@ -256,6 +257,7 @@ def run_ours(args):
         return layer
 
     sparse = make(kb.BlockTopkDecoderLayer, topk_page=topk)
+    sparse.decode_plan.num_splits = args.splits
     hidden = torch.randn(B, 1, cfg.hidden_size, device=device, dtype=dtype)
     static_in, static_out, graph = sparse.make_graphed(hidden)
     sparse.check_status()

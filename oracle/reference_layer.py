@@ -39,6 +39,7 @@ class ReferenceLayerCPU:
         self.kv_cache, self.page_table, self.summaries = kv_cache, page_table.long(), summaries
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
         self.eps, self.topk, self.last_page_len = eps, topk, last_page_len
+        self.forced_pages = None      # [B, Hkv, m] physical pages to attend instead of the own selection
 
     def _append(self, k, v):
         # flashinfer.append_paged_kv_cache (benchmark/blocktopk_decoder.py:38-46): newest token
@@ -95,7 +96,9 @@ class ReferenceLayerCPU:
         query_states = rmsnorm(query_states, w["qnorm_weight"], self.eps).reshape(bsz, self.num_heads, self.head_dim)
         key_states = rmsnorm(key_states, w["knorm_weight"], self.eps).reshape(bsz, self.num_kv_heads, self.head_dim)
         self._append(key_states, value_states)
-        if self.summaries is not None:
+        if self.forced_pages is not None:
+            pages = self.forced_pages
+        elif self.summaries is not None:
             pages = self._select(query_states)
         else:
             pages = self.page_table[:, None, :].expand(bsz, self.num_kv_heads, self.page_table.shape[1])
