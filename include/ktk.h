@@ -58,6 +58,8 @@ extern "C" {
 #define KTK_STATUS_OK 0
 #define KTK_STATUS_BAD_PAGE 1    /* physical page id outside [0, num_pages)      */
 #define KTK_STATUS_BAD_TABLE 2   /* kv_indptr not monotone / last_page_len out of range */
+#define KTK_STATUS_TIMEOUT 3     /* a bounded wait on an asynchronous copy gave up       */
+#define KTK_STATUS_INTERNAL 4    /* a kernel's own consistency check failed              */
 
 /* decode kernel variants (ktk_sparse_decode / ktk_dense_decode `variant`) */
 #define KTK_VARIANT_AUTO 0

@@ -13,7 +13,9 @@ LIB_PATH = _PKG / "libktk.so"
 
 KTK_F32, KTK_BF16 = 0, 1
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_MMA = 0, 1, 2
-STATUS_TEXT = {0: "ok", 1: "physical page id outside the cache", 2: "malformed page table"}
+STATUS_TEXT = {0: "ok", 1: "physical page id outside the cache", 2: "malformed page table",
+               3: "a bounded wait on an asynchronous copy gave up",
+               4: "a kernel's own consistency check failed"}
 
 
 class KtkError(RuntimeError):

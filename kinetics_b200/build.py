@@ -63,7 +63,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     rebuilt = any(log is not None for _, log in results)
     if rebuilt or force or not OUT.exists():
         cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(OUT),
-               *map(str, objs), "-lcuda"]
+               *map(str, objs)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

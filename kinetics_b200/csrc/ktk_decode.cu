@@ -318,7 +318,8 @@ static int decode_common(const char* who, const void* q, const void* cache, cons
         p.ws_o = (float*)workspace + rows * 2;
     }
     cudaStream_t st = (cudaStream_t)stream;
-    if (variant == KTK_VARIANT_AUTO) variant = KTK_VARIANT_SIMT;
+    if (variant == KTK_VARIANT_AUTO)
+        variant = (s->dtype == KTK_BF16) ? KTK_VARIANT_MMA : KTK_VARIANT_SIMT;
     if (variant == KTK_VARIANT_MMA)
         rc = launch_decode_mma(p, s->group_size, st);
     else

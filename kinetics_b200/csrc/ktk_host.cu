@@ -3,6 +3,7 @@
 #include <stdio.h>
 
 #include "ktk_common.cuh"
+#include "ktk_pipeline.cuh"
 
 namespace ktk {
 
@@ -56,6 +57,42 @@ int sm_count() {
         cached_dev = dev;
     }
     return cached;
+}
+
+// cuTensorMapEncodeTiled is a driver entry point; it is looked up through the runtime so that
+// the library carries no link-time dependency on libcuda (it must load on machines without a GPU).
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                    CUtensorMapFloatOOBfill);
+
+int make_tensor_map_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, const uint64_t dims[3],
+                       const uint64_t strides_bytes[2], const uint32_t box[3], CUtensorMapSwizzle swizzle,
+                       const char* who) {
+    static encode_tiled_fn encode = nullptr;
+    if (encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess) return cuda_fail(e, who);
+        if (qres != cudaDriverEntryPointSuccess || fn == nullptr) {
+            set_error("%s: the driver does not provide cuTensorMapEncodeTiled", who);
+            return KTK_ERR_CUDA;
+        }
+        encode = (encode_tiled_fn)fn;
+    }
+    cuuint64_t gdim[3] = {dims[0], dims[1], dims[2]};
+    cuuint64_t gstr[2] = {strides_bytes[0], strides_bytes[1]};
+    cuuint32_t bx[3] = {box[0], box[1], box[2]};
+    cuuint32_t es[3] = {1, 1, 1};
+    CUresult r = encode(out, dt, 3, const_cast<void*>(base), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("%s: cuTensorMapEncodeTiled failed with %d (base %p, dims %llu x %llu x %llu)", who, (int)r,
+                  base, (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2]);
+        return KTK_ERR_CUDA;
+    }
+    return KTK_OK;
 }
 
 }  // namespace ktk

@@ -183,9 +183,32 @@ def test_select_reports_bad_page_id(cuda_device):
     assert torch.isfinite(out).all()
 
 
+def test_tensor_core_decode_skips_bad_pages(cuda_device):
+    ops = _ops()
+    dtype = torch.bfloat16
+    lens = [200, 90]
+    q, k, v = random_case(6, 2, 2, 4, lens, dtype)
+    st = paged_state(k, v, lens, dtype, seed=3)
+    d = to_dev(st, cuda_device)
+    # a list whose middle entries are out of range: they are skipped, the rest is attended
+    good = oracle.select(q, oracle.summaries(st["kv_cache"], st["kv_indices"], st["kv_indptr"],
+                                             st["kv_last_page_len"], st["summary_stride"]),
+                         st["kv_indices"], st["kv_indptr"], 6)[0]
+    bad = good.clone()
+    bad[:, :, 2] = st["num_pages"] + 9
+    bad[:, :, 3] = -4
+    status = ops.new_status(cuda_device)
+    out = ops.sparse_decode(q.to(cuda_device), d["kv_cache"], bad.to(cuda_device), d["kv_indptr"],
+                            d["kv_last_page_len"], num_splits=1, variant=2, status=status)
+    assert int(status.item()) == 1
+    ref = ops.sparse_decode(q.to(cuda_device), d["kv_cache"], bad.to(cuda_device), d["kv_indptr"],
+                            d["kv_last_page_len"], num_splits=1, variant=1)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
 # ---------------------------------------------------------------- decode
 
-VARIANTS = {torch.float32: [1], torch.bfloat16: [1]}
+VARIANTS = {torch.float32: [1], torch.bfloat16: [1, 2]}   # 1 = fp32 FMA kernel, 2 = tensor-core kernel
 
 
 @pytest.mark.parametrize("name", sorted(CASES))
@@ -244,11 +267,12 @@ def test_sparse_equals_dense_when_budget_covers_everything(cuda_device):
     q, k, v = random_case(22, 2, 2, 4, lens, dtype)
     st = paged_state(k, v, lens, dtype, seed=9)
     (phys, *_), (gp, *_), d, _ = _select_both(ops, q, st, 40, cuda_device)
-    a = ops.sparse_decode(q.to(cuda_device), d["kv_cache"], gp.to(cuda_device), d["kv_indptr"],
-                          d["kv_last_page_len"], num_splits=1, variant=1)
-    b = ops.dense_decode(q.to(cuda_device), d["kv_cache"], d["kv_indices"], d["kv_indptr"], d["kv_last_page_len"],
-                         max(st["npages"]), num_splits=1, variant=1)
-    assert torch.equal(a, b)
+    for variant in (1, 2):
+        a = ops.sparse_decode(q.to(cuda_device), d["kv_cache"], gp.to(cuda_device), d["kv_indptr"],
+                              d["kv_last_page_len"], num_splits=1, variant=variant)
+        b = ops.dense_decode(q.to(cuda_device), d["kv_cache"], d["kv_indices"], d["kv_indptr"],
+                             d["kv_last_page_len"], max(st["npages"]), num_splits=1, variant=variant)
+        assert torch.equal(a, b)
 
 
 def test_large_logits_do_not_overflow(cuda_device):
@@ -260,10 +284,11 @@ def test_large_logits_do_not_overflow(cuda_device):
     d = to_dev(st, cuda_device)
     ref = oracle.decode(q, st["kv_cache"], st["kv_indices"], -1, st["kv_indptr"], st["kv_last_page_len"],
                         oracle.default_scale())
-    out = ops.dense_decode(q.to(cuda_device), d["kv_cache"], d["kv_indices"], d["kv_indptr"],
-                           d["kv_last_page_len"], 25, num_splits=1, variant=1)
-    assert torch.isfinite(out).all()
-    np.testing.assert_allclose(out.float().cpu().numpy(), ref.numpy(), rtol=3e-2, atol=3e-2)
+    for variant in (1, 2):
+        out = ops.dense_decode(q.to(cuda_device), d["kv_cache"], d["kv_indices"], d["kv_indptr"],
+                               d["kv_last_page_len"], 25, num_splits=1, variant=variant)
+        assert torch.isfinite(out).all()
+        np.testing.assert_allclose(out.float().cpu().numpy(), ref.numpy(), rtol=3e-2, atol=3e-2)
 
 
 # ---------------------------------------------------------------- small ops

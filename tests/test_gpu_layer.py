@@ -78,6 +78,9 @@ def test_dense_and_sparse_layers_share_a_process_and_a_cache(cuda_device):
     sparse = _build("BlockTopkDecoderLayer", cuda_device, dtype, topk_page=64)       # budget >= pages: dense
     dense = _build("DecoderLayer", cuda_device, dtype, kv_cache=sparse.kv_cache)
     dense.load_state_dict(sparse.state_dict())
+    # same page list, same split count => the two paths run the very same arithmetic
+    sparse.decode_plan.num_splits = 1
+    dense.decode_plan.num_splits = 1
     x = torch.randn(6, 1, Cfg.hidden_size, device=cuda_device, dtype=dtype)
     a = sparse(x)
     b = dense(x)
