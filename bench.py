@@ -332,27 +332,51 @@ def run_ours(args):
     }
 
     # ---- end to end: host buffers in, host buffers out, every step ----
+    # Three streams: the next step's input is copied in and the previous step's output is copied
+    # out while the current step computes; two captured graphs alternate so that each has its own
+    # input and output buffer.
     e2e = None
     if not args.no_e2e:
-        host_in = torch.randn(B, 1, cfg.hidden_size, dtype=dtype).pin_memory()
-        host_out = torch.empty(B, 1, cfg.hidden_size, dtype=dtype).pin_memory()
-        for _ in range(3):
-            static_in.copy_(host_in, non_blocking=True)
-            graph.replay()
-            host_out.copy_(static_out, non_blocking=True)
+        sets = [(static_in, static_out, graph), sparse.make_graphed(hidden)]
+        host_in = [torch.randn(B, 1, cfg.hidden_size, dtype=dtype).pin_memory() for _ in range(2)]
+        host_out = [torch.empty(B, 1, cfg.hidden_size, dtype=dtype).pin_memory() for _ in range(2)]
+        s_in, s_out, s_comp = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+
+        def run_steps(n):
+            ev_in = [None, None]; ev_comp = [None, None]; ev_out = [None, None]
+            for i in range(n):
+                j = i & 1
+                buf_in, buf_out, g = sets[j]
+                with torch.cuda.stream(s_in):
+                    if ev_comp[j] is not None:
+                        s_in.wait_event(ev_comp[j])          # the graph that read this buffer has finished
+                    buf_in.copy_(host_in[j], non_blocking=True)
+                    ev_in[j] = torch.cuda.Event(); ev_in[j].record(s_in)
+                s_comp.wait_event(ev_in[j])
+                if ev_out[j] is not None:
+                    s_comp.wait_event(ev_out[j])             # its previous output has left the device
+                g.replay()
+                ev_comp[j] = torch.cuda.Event(); ev_comp[j].record(s_comp)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_comp[j])
+                    host_out[j].copy_(buf_out, non_blocking=True)
+                    ev_out[j] = torch.cuda.Event(); ev_out[j].record(s_out)
+            s_comp.wait_stream(s_out)
+            s_comp.wait_stream(s_in)
+
+        run_steps(4)
         barrier()
         with sampler:
             e0.record()
-            for _ in range(args.steps):
-                static_in.copy_(host_in, non_blocking=True)
-                graph.replay()
-                host_out.copy_(static_out, non_blocking=True)
+            run_steps(args.steps)
             e1.record()
             barrier()
         ms_e2e = max_over_ranks(e0.elapsed_time(e1) / args.steps)
-        nbytes = host_in.numel() * host_in.element_size()
+        nbytes = host_in[0].numel() * host_in[0].element_size()
         e2e = {"value": B * world / tp / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
+               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
+               "how": "pinned host input -> device, layer step, output -> pinned host, every step; copies of "
+                      "neighbouring steps overlap the compute on separate streams"}
     sparse.check_status()
 
     # ---- the repository's dense paged decode at the same shape, sharing the KV cache ----

@@ -13,192 +13,326 @@
 // which is unique per page: the k largest composites are "largest score first, ties
 // to the lowest page number".
 #include "ktk_common.cuh"
+#include "ktk_pipeline.cuh"
 
 namespace ktk {
 
-constexpr int kSelThreads = 256;
-constexpr int kSelUnroll = 8;
+constexpr int kSelWarps = 8;                        // consumer warps
+constexpr int kSelThreads = kSelWarps * 32;         // threads that score and select
+constexpr int kSelCtaThreads = kSelThreads + 32;    // + one producer warp
+constexpr int kSelStages = 8;                       // one stage per consumer warp
+template <typename T> struct SelStage;              // rows per stage: a multiple of the 8 rows a warp scores per step
+template <> struct SelStage<__nv_bfloat16> { static constexpr int kRows = 24; };   // 6 KiB
+template <> struct SelStage<float> { static constexpr int kRows = 16; };           // 8 KiB
+constexpr int kSelCtasPerSm = 3;
 constexpr int kMaxTopk = 1024;
+static_assert(kSelStages % kSelWarps == 0, "a stage must belong to one consumer warp");
 
 __device__ __forceinline__ unsigned long long composite(uint32_t key, int page) {
     return ((unsigned long long)key << 16) | (unsigned long long)(0xFFFFu - (unsigned)page);
 }
 
+__device__ __forceinline__ void consumer_sync() {
+    asm volatile("bar.sync 1, %0;" ::"n"(kSelThreads) : "memory");
+}
+
+// eight consecutive elements (one chunk) of a staged row as fp32
+__device__ __forceinline__ void lds8(const float* p, float (&out)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *(reinterpret_cast<const float4*>(p) + 1);
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+    out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+}
+__device__ __forceinline__ void lds8(const __nv_bfloat16* p, float (&out)[8]) {
+    unpack8(*reinterpret_cast<const uint4*>(p), out);
+}
+
+// What both the producer and the consumers derive for a work item (sequence b, kv head h).
+struct SelItem {
+    int beg, n_pages, n_scored, n_stages;
+    bool bad, need_select, scan;
+};
+
+template <int kRowsPerStage>
+__device__ __forceinline__ SelItem sel_item(int b, const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                                            int64_t summary_stride, int key_cap, int topk, bool want_scores) {
+    SelItem it;
+    it.beg = kv_indptr[b];
+    it.n_pages = kv_indptr[b + 1] - it.beg;
+    const int last = (it.n_pages > 0) ? kv_last_page_len[b] : 1;
+    it.n_scored = it.n_pages - 1;
+    it.bad = it.n_pages > 0 && (last < 1 || last > kPageSize || it.n_scored > summary_stride ||
+                                it.n_scored > key_cap);
+    it.need_select = !it.bad && it.n_scored > topk;
+    it.scan = it.n_pages > 0 && !it.bad && (it.need_select || want_scores) && it.n_scored > 0;
+    it.n_stages = it.scan ? (it.n_scored + kRowsPerStage - 1) / kRowsPerStage : 0;
+    return it;
+}
+
+// Persistent kernel: CTA c handles the (sequence, kv head) items c, c + gridDim.x, ...
+// A producer warp streams the summaries of its items, one after the other without a gap,
+// through a ring of shared-memory stages with bulk asynchronous copies (the rows of one item
+// are contiguous); stage i of the stream is scored by consumer warp i mod 8, sixteen lanes per
+// row.  While the consumers run the selection of one item, the producer is already filling the
+// ring with the rows of the next.  The first radix pass is histogrammed while scoring.
 template <typename T, int G>
-__global__ void __launch_bounds__(kSelThreads, 2)
+__global__ void __launch_bounds__(kSelCtaThreads, kSelCtasPerSm)
 select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t summary_stride,
               const int32_t* __restrict__ kv_indices, const int32_t* __restrict__ kv_indptr,
-              const int32_t* __restrict__ kv_last_page_len, int topk, int key_cap,
+              const int32_t* __restrict__ kv_last_page_len, int topk, int key_cap, int kp,
               int32_t* __restrict__ out_pages, int32_t* __restrict__ out_logical,
-              float* __restrict__ out_scores, int Hkv, int64_t num_pages, int32_t* status) {
-    extern __shared__ uint32_t keys[];                 // one key per scored page
+              float* __restrict__ out_scores, int64_t n_items, int Hkv, int64_t num_pages,
+              int32_t* status) {
+    // [stages][6 KiB] | one key per scored page | kp selected composites
+    extern __shared__ __align__(128) uint8_t sel_smem[];
+    __shared__ __align__(8) uint64_t full_bar[kSelStages];
+    __shared__ __align__(8) uint64_t empty_bar[kSelStages];
     __shared__ float qbar[kHeadDim];
     __shared__ unsigned int hist[256];
-    __shared__ unsigned long long sel[kMaxTopk];
     __shared__ int s_digit, s_greater, s_bincount, s_count;
+    __shared__ int abort_flag, issued_total;
+
+    constexpr int kRowBytes = kHeadDim * (int)sizeof(T);
+    constexpr int kRowsPerStage = SelStage<T>::kRows;
+    constexpr int kSelStageBytes = kRowsPerStage * kRowBytes;
+    static_assert(kRowsPerStage % 8 == 0, "eight rows per warp step");
+    unsigned long long* sel = reinterpret_cast<unsigned long long*>(sel_smem + kSelStages * kSelStageBytes);
+    uint32_t* keys = reinterpret_cast<uint32_t*>(sel + kp);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int hl = lane & 15;       // lane inside its 16-lane group
-    const int grp = tid >> 4;       // 16-lane group inside the CTA
-    const int64_t bh = blockIdx.x;
-    const int b = (int)(bh / Hkv), h = (int)(bh % Hkv);
     const int stride_out = topk + 1;
-    int32_t* row_pages = out_pages + bh * stride_out;
-    int32_t* row_logical = out_logical ? out_logical + bh * stride_out : nullptr;
+    const bool want_scores = out_scores != nullptr;
 
-    const int beg = kv_indptr[b], end = kv_indptr[b + 1];
-    const int n_pages = end - beg;
-    const int last = (n_pages > 0) ? kv_last_page_len[b] : 1;
-    const int n_scored = n_pages - 1;
-    const bool bad = n_pages > 0 && (last < 1 || last > kPageSize || n_scored > summary_stride ||
-                                     n_scored > key_cap);
-    if (n_pages <= 0 || bad) {
-        if (bad && tid == 0) report(status, KTK_STATUS_BAD_TABLE);
-        for (int i = tid; i < stride_out; i += kSelThreads) {
-            row_pages[i] = -1;
-            if (row_logical) row_logical[i] = -1;
+    if (tid == 0) {
+        for (int s = 0; s < kSelStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
         }
-        return;
+        abort_flag = 0;
+        issued_total = 0;
+        mbar_init_fence();
     }
-
-    const bool need_select = n_scored > topk;
-    if (need_select || out_scores != nullptr) {
-        if (tid < kHeadDim) {
-            const T* qp = q + ((int64_t)b * Hkv * G + (int64_t)h * G) * kHeadDim + tid;
-            float acc = 0.0f;
-#pragma unroll
-            for (int g = 0; g < G; ++g) acc = __fadd_rn(acc, to_f32(qp[g * kHeadDim]));
-            qbar[tid] = __fmul_rn(acc, 1.0f / (float)G);
-        }
-        __syncthreads();
-        float qr[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) qr[e] = qbar[8 * hl + e];
-
-        const T* sbase = summaries + bh * summary_stride * kHeadDim + hl * 8;
-        float* score_row = out_scores ? out_scores + bh * summary_stride : nullptr;
-        constexpr int kRowsPerIt = kSelThreads / 16;
-        for (int r0 = 0; r0 < n_scored; r0 += kRowsPerIt * kSelUnroll) {
-            float x[kSelUnroll][8];
-#pragma unroll
-            for (int u = 0; u < kSelUnroll; ++u) {
-                const int r = r0 + u * kRowsPerIt + grp;
-                if (r < n_scored) {
-                    load8(sbase + (int64_t)r * kHeadDim, x[u]);
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) x[u][e] = 0.0f;
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < kSelUnroll; ++u) {
-                const int r = r0 + u * kRowsPerIt + grp;
-                float acc = 0.0f;
-#pragma unroll
-                for (int e = 0; e < 8; ++e) acc = __fmaf_rn(qr[e], x[u][e], acc);
-#pragma unroll
-                for (int off = 8; off > 0; off >>= 1)
-                    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, off));
-                acc = __fadd_rn(acc, 0.0f);
-                if (hl == 0 && r < n_scored) {
-                    keys[r] = score_to_key(acc);
-                    if (score_row) score_row[r] = acc;
-                }
-            }
-        }
-    }
-
-    if (!need_select) {
-        // every scored page is taken, in page order, then the page being filled
-        for (int i = tid; i < stride_out; i += kSelThreads) {
-            int logical = -1, phys = -1;
-            if (i <= n_scored) {
-                logical = i;
-                phys = kv_indices[beg + i];
-                if (phys < 0 || phys >= num_pages) report(status, KTK_STATUS_BAD_PAGE);
-            }
-            row_pages[i] = phys;
-            if (row_logical) row_logical[i] = logical;
-        }
-        return;
-    }
-
-    // ---- radix select of the topk-th largest 48-bit composite, 8 bits per pass ----
-    unsigned long long prefix = 0, mask = 0;
-    int need = topk;
-    if (tid == 0) s_count = 0;
-    for (int shift = 40; shift >= 0; shift -= 8) {
-        if (tid < 256) hist[tid] = 0;
-        __syncthreads();
-        for (int i = tid; i < n_scored; i += kSelThreads) {
-            const unsigned long long c = composite(keys[i], i);
-            if ((c & mask) == prefix) atomicAdd(&hist[(unsigned)(c >> shift) & 255u], 1u);
-        }
-        __syncthreads();
-        if (warp == 0) {
-            // lane l owns bins 255-8l .. 248-8l, walked from the largest digit down
-            unsigned cnt[8];
-            unsigned mine = 0;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                cnt[j] = hist[255 - 8 * lane - j];
-                mine += cnt[j];
-            }
-            unsigned incl = mine;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const unsigned up = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += up;
-            }
-            unsigned running = incl - mine;   // elements in strictly larger bins
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (running < (unsigned)need && (unsigned)need <= running + cnt[j]) {
-                    s_digit = 255 - 8 * lane - j;
-                    s_greater = (int)running;
-                    s_bincount = (int)cnt[j];
-                }
-                running += cnt[j];
-            }
-        }
-        __syncthreads();
-        need -= s_greater;
-        prefix |= (unsigned long long)s_digit << shift;
-        mask |= 0xFFull << shift;
-        if (s_bincount == need) break;   // the whole bin is taken: threshold found
-    }
-
-    // ---- gather the topk composites >= threshold, sort them descending ----
-    int kp = 1;
-    while (kp < topk) kp <<= 1;
-    for (int i = tid; i < n_scored; i += kSelThreads) {
-        const unsigned long long c = composite(keys[i], i);
-        if ((c & mask) >= prefix) {
-            const int pos = atomicAdd(&s_count, 1);
-            if (pos < kMaxTopk) sel[pos] = c;
-        }
-    }
-    for (int i = topk + tid; i < kp; i += kSelThreads) sel[i] = 0ull;
     __syncthreads();
-    for (int k2 = 2; k2 <= kp; k2 <<= 1) {
-        for (int j = k2 >> 1; j > 0; j >>= 1) {
-            for (int i = tid; i < kp; i += kSelThreads) {
-                const int ixj = i ^ j;
-                if (ixj > i) {
-                    const unsigned long long a = sel[i], c = sel[ixj];
-                    const bool desc = (i & k2) == 0;
-                    if (desc ? (a < c) : (a > c)) { sel[i] = c; sel[ixj] = a; }
+
+    if (warp == kSelWarps) {
+        // ---------------- producer warp: one lane issues the bulk copies ----------------
+        if (lane == 0) {
+            int i = 0;           // stages issued so far, over all items of this CTA
+            bool alive = true;
+            for (int64_t bh = blockIdx.x; bh < n_items && alive; bh += gridDim.x) {
+                const int b = (int)(bh / Hkv);
+                const SelItem it = sel_item<kRowsPerStage>(b, kv_indptr, kv_last_page_len, summary_stride,
+                                                           key_cap, topk, want_scores);
+                const T* sbase = summaries + bh * summary_stride * kHeadDim;
+                for (int st = 0; st < it.n_stages; ++st, ++i) {
+                    const int s = i % kSelStages;
+                    if (i >= kSelStages && !mbar_wait(&empty_bar[s], ((i / kSelStages) - 1) & 1, &abort_flag)) {
+                        alive = false;
+                        break;
+                    }
+                    const int r0 = st * kRowsPerStage;
+                    const int rows = (it.n_scored - r0 < kRowsPerStage) ? it.n_scored - r0 : kRowsPerStage;
+                    const uint32_t bytes = (uint32_t)rows * kRowBytes;
+                    mbar_arrive_expect_tx(&full_bar[s], bytes);
+                    bulk_load(sel_smem + s * kSelStageBytes, sbase + (int64_t)r0 * kHeadDim, bytes, &full_bar[s]);
                 }
             }
-            __syncthreads();
+            issued_total = i;
+        }
+    } else {
+        // ---------------- consumer warps ----------------
+        int ibase = 0;           // stream position of the current item's first stage
+        for (int64_t bh = blockIdx.x; bh < n_items; bh += gridDim.x) {
+            const int b = (int)(bh / Hkv), h = (int)(bh % Hkv);
+            int32_t* row_pages = out_pages + bh * stride_out;
+            int32_t* row_logical = out_logical ? out_logical + bh * stride_out : nullptr;
+            const SelItem it = sel_item<kRowsPerStage>(b, kv_indptr, kv_last_page_len, summary_stride, key_cap,
+                                                       topk, want_scores);
+            if (it.n_pages <= 0 || it.bad) {
+                if (it.bad && tid == 0) report(status, KTK_STATUS_BAD_TABLE);
+                for (int i = tid; i < stride_out; i += kSelThreads) {
+                    row_pages[i] = -1;
+                    if (row_logical) row_logical[i] = -1;
+                }
+                continue;
+            }
+
+            if (it.scan) {
+                hist[tid] = 0;
+                if (tid == 0) s_count = 0;
+                if (tid < kHeadDim) {
+                    const T* qp = q + ((int64_t)b * Hkv * G + (int64_t)h * G) * kHeadDim + tid;
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int g = 0; g < G; ++g) acc = __fadd_rn(acc, to_f32(qp[g * kHeadDim]));
+                    qbar[tid] = __fmul_rn(acc, 1.0f / (float)G);
+                }
+                consumer_sync();
+                // Four lanes per row: lane j of a row owns the 8-element chunks j, j+4, j+8, j+12, i.e. the
+                // chunks whose partial sums meet in the first two levels of the contract's butterfly, so
+                // those two levels are plain in-lane adds and only two shuffles per row remain.  Odd rows
+                // visit their chunks rotated by one (bank conflicts); every add involved is commutative,
+                // so the value is the same bit for bit.  Two chunk chains run in one packed fp32x2 FMA.
+                const int rw = lane >> 2, j4 = lane & 3, rot = rw & 1;
+                float2 q01[8], q23[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    q01[e] = make_float2(qbar[8 * (j4 + 4 * ((0 + rot) & 3)) + e], qbar[8 * (j4 + 4 * ((1 + rot) & 3)) + e]);
+                    q23[e] = make_float2(qbar[8 * (j4 + 4 * ((2 + rot) & 3)) + e], qbar[8 * (j4 + 4 * ((3 + rot) & 3)) + e]);
+                }
+                const int c0 = (j4 + 4 * ((0 + rot) & 3)) * 8, c1 = (j4 + 4 * ((1 + rot) & 3)) * 8;
+                const int c2 = (j4 + 4 * ((2 + rot) & 3)) * 8, c3 = (j4 + 4 * ((3 + rot) & 3)) * 8;
+                float* score_row = want_scores ? out_scores + bh * summary_stride : nullptr;
+                // this warp's stages of the item: stream positions i = warp (mod 8) inside [ibase, ibase + n_stages)
+                int i = ibase + ((warp - ibase) & (kSelWarps - 1));
+                bool ok = true;
+                for (; i < ibase + it.n_stages; i += kSelWarps) {
+                    const int s = i % kSelStages;
+                    if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], (i / kSelStages) & 1, &abort_flag))) {
+                        ok = false;
+                        break;
+                    }
+                    const T* stage = reinterpret_cast<const T*>(sel_smem + s * kSelStageBytes);
+                    const int r0 = (i - ibase) * kRowsPerStage;
+#pragma unroll
+                    for (int step = 0; step < kRowsPerStage / 8; ++step) {
+                        const int lr = step * 8 + rw;                 // row inside the stage
+                        const int r = r0 + lr;
+                        const T* rowp = stage + lr * kHeadDim;        // rows past the item's last hold stale data: unused
+                        float x0[8], x1[8], x2[8], x3[8];
+                        lds8(rowp + c0, x0);
+                        lds8(rowp + c1, x1);
+                        lds8(rowp + c2, x2);
+                        lds8(rowp + c3, x3);
+                        float2 a01 = make_float2(0.0f, 0.0f), a23 = make_float2(0.0f, 0.0f);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            a01 = __ffma2_rn(q01[e], make_float2(x0[e], x1[e]), a01);
+                            a23 = __ffma2_rn(q23[e], make_float2(x2[e], x3[e]), a23);
+                        }
+                        const float2 t = __fadd2_rn(a01, a23);        // butterfly level "xor 8"
+                        float acc = __fadd_rn(t.x, t.y);              // level "xor 4"
+                        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+                        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+                        acc = __fadd_rn(acc, 0.0f);
+                        if (j4 == 0 && r < it.n_scored) {
+                            const uint32_t key = score_to_key(acc);
+                            keys[r] = key;
+                            if (it.need_select) atomicAdd(&hist[key >> 24], 1u);
+                            if (score_row) score_row[r] = acc;
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty_bar[s]);
+                }
+                ibase += it.n_stages;
+                consumer_sync();            // every key of the item is in shared memory (or the CTA gave up)
+                if (!ok || abort_flag) break;
+            }
+
+            if (!it.need_select) {
+                // every scored page is taken, in page order, then the page being filled
+                for (int i = tid; i < stride_out; i += kSelThreads) {
+                    int logical = -1, phys = -1;
+                    if (i <= it.n_scored) {
+                        logical = i;
+                        phys = kv_indices[it.beg + i];
+                        if (phys < 0 || phys >= num_pages) report(status, KTK_STATUS_BAD_PAGE);
+                    }
+                    row_pages[i] = phys;
+                    if (row_logical) row_logical[i] = logical;
+                }
+                continue;
+            }
+
+            // ---- radix select of the topk-th largest 48-bit composite, 8 bits per pass; the
+            //      histogram of the first pass (top byte of the key) was filled while scoring ----
+            unsigned long long prefix = 0, mask = 0;
+            int need = topk;
+            for (int shift = 40; shift >= 0; shift -= 8) {
+                if (shift != 40) {
+                    hist[tid] = 0;
+                    consumer_sync();
+                    for (int i = tid; i < it.n_scored; i += kSelThreads) {
+                        const unsigned long long c = composite(keys[i], i);
+                        if ((c & mask) == prefix) atomicAdd(&hist[(unsigned)(c >> shift) & 255u], 1u);
+                    }
+                    consumer_sync();
+                }
+                if (warp == 0) {
+                    // lane l owns bins 255-8l .. 248-8l, walked from the largest digit down
+                    unsigned cnt[8];
+                    unsigned mine = 0;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        cnt[j] = hist[255 - 8 * lane - j];
+                        mine += cnt[j];
+                    }
+                    unsigned incl = mine;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const unsigned up = __shfl_up_sync(0xffffffffu, incl, o);
+                        if (lane >= o) incl += up;
+                    }
+                    unsigned running = incl - mine;   // elements in strictly larger bins
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (running < (unsigned)need && (unsigned)need <= running + cnt[j]) {
+                            s_digit = 255 - 8 * lane - j;
+                            s_greater = (int)running;
+                            s_bincount = (int)cnt[j];
+                        }
+                        running += cnt[j];
+                    }
+                }
+                consumer_sync();
+                need -= s_greater;
+                prefix |= (unsigned long long)s_digit << shift;
+                mask |= 0xFFull << shift;
+                if (s_bincount == need) break;   // the whole bin is taken: threshold found
+            }
+
+            // ---- gather the topk composites >= threshold, sort them descending ----
+            for (int i = tid; i < it.n_scored; i += kSelThreads) {
+                const unsigned long long c = composite(keys[i], i);
+                if ((c & mask) >= prefix) {
+                    const int pos = atomicAdd(&s_count, 1);
+                    if (pos < kp) sel[pos] = c;
+                }
+            }
+            for (int i = topk + tid; i < kp; i += kSelThreads) sel[i] = 0ull;
+            consumer_sync();
+            for (int k2 = 2; k2 <= kp; k2 <<= 1) {
+                for (int j = k2 >> 1; j > 0; j >>= 1) {
+                    for (int i = tid; i < kp; i += kSelThreads) {
+                        const int ixj = i ^ j;
+                        if (ixj > i) {
+                            const unsigned long long a = sel[i], c = sel[ixj];
+                            const bool desc = (i & k2) == 0;
+                            if (desc ? (a < c) : (a > c)) { sel[i] = c; sel[ixj] = a; }
+                        }
+                    }
+                    consumer_sync();
+                }
+            }
+            for (int i = tid; i < stride_out; i += kSelThreads) {
+                const int logical = (i < topk) ? (int)(0xFFFFu - (unsigned)(sel[i] & 0xFFFFull)) : it.n_pages - 1;
+                const int phys = kv_indices[it.beg + logical];
+                if (phys < 0 || phys >= num_pages) report(status, KTK_STATUS_BAD_PAGE);
+                row_pages[i] = phys;
+                if (row_logical) row_logical[i] = logical;
+            }
+            consumer_sync();                // sel / keys / hist are reused by the next item
         }
     }
-    for (int i = tid; i < stride_out; i += kSelThreads) {
-        const int logical = (i < topk) ? (int)(0xFFFFu - (unsigned)(sel[i] & 0xFFFFull)) : n_pages - 1;
-        const int phys = kv_indices[beg + logical];
-        if (phys < 0 || phys >= num_pages) report(status, KTK_STATUS_BAD_PAGE);
-        row_pages[i] = phys;
-        if (row_logical) row_logical[i] = logical;
+
+    __syncthreads();
+    if (abort_flag && tid == 0) {
+        report(status, KTK_STATUS_TIMEOUT);
+        volatile int never = 0;   // copies still in flight must land before the shared memory is released
+        const int total = issued_total;
+        for (int i = (total > kSelStages ? total - kSelStages : 0); i < total; ++i)
+            mbar_wait(&full_bar[i % kSelStages], (i / kSelStages) & 1, &never);
     }
 }
 
@@ -209,16 +343,20 @@ static int select_launch(const void* q, const void* summaries, int64_t summary_s
                          int32_t* out_logical, float* out_scores, const ktk_shape* s,
                          int32_t* status, cudaStream_t st) {
     int key_cap = (int)(summary_stride < kMaxScoredPages ? summary_stride : kMaxScoredPages);
-    const size_t smem = (size_t)key_cap * sizeof(uint32_t);
+    int kp = 1;
+    while (kp < topk) kp <<= 1;
+    const size_t smem = (size_t)kSelStages * SelStage<T>::kRows * kHeadDim * sizeof(T) + (size_t)kp * 8 +
+                        (size_t)key_cap * sizeof(uint32_t);
     auto kern = select_kernel<T, G>;
-    if (smem > 40 * 1024) {
-        KTK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                     "ktk_select");
-    }
-    const int64_t bh = (int64_t)s->batch * s->num_kv_heads;
-    kern<<<(unsigned)bh, kSelThreads, smem, st>>>(
+    KTK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                 "ktk_select");
+    const int64_t items = (int64_t)s->batch * s->num_kv_heads;
+    int64_t grid = (int64_t)sm_count() * kSelCtasPerSm;
+    if (grid > items) grid = items;
+    kern<<<(unsigned)grid, kSelCtaThreads, smem, st>>>(
         (const T*)q, (const T*)summaries, summary_stride, kv_indices, kv_indptr, kv_last_page_len,
-        topk, key_cap, out_pages, out_logical, out_scores, s->num_kv_heads, s->num_pages, status);
+        topk, key_cap, kp, out_pages, out_logical, out_scores, items, s->num_kv_heads, s->num_pages,
+        status);
     KTK_CUDA_TRY(cudaGetLastError(), "ktk_select");
     return KTK_OK;
 }
@@ -255,6 +393,10 @@ extern "C" int ktk_select(const void* q, const void* summaries, int64_t summary_
     }
     if (summary_stride <= 0) {
         set_error("ktk_select: summary_stride must be positive");
+        return KTK_ERR_ARG;
+    }
+    if (((uintptr_t)summaries & 15u) != 0) {
+        set_error("ktk_select: summaries must be 16-byte aligned (bulk asynchronous copies)");
         return KTK_ERR_ARG;
     }
     if ((int64_t)shape->batch * shape->num_kv_heads > 2147483647LL) {
