@@ -61,6 +61,9 @@ def parse():
     ap.add_argument("--page-table", default="interleaved", choices=["interleaved", "random"])
     ap.add_argument("--seed", type=int, default=1236)
     ap.add_argument("--cpu-sample", type=int, default=32, help="sequences in the CPU sample")
+    ap.add_argument("--micro", default="", choices=["", "select"],
+                    help="time one kernel alone on the workload's shapes (select: only the page summaries are "
+                         "allocated, so the full batch fits in a few GB)")
     return ap.parse_args()
 
 
@@ -427,8 +430,49 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_micro_select(args):
+    """The scoring + selection kernel alone at the workload's shape (no KV cache is needed for it)."""
+    from kinetics_b200 import ops
+    import kinetics_b200 as kb
+    wl = dict(WORKLOADS[args.workload])
+    if args.batch:
+        wl["batch"] = args.batch
+    cfg = kb.get_config(wl["model"])
+    tp, B, ctx, topk = wl["tp"], wl["batch"], wl["ctx"], wl["topk"]
+    hkv, hq = cfg.num_key_value_heads // tp, cfg.num_attention_heads // tp
+    n = ctx // PAGE
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(args.seed)
+    dtype = torch.bfloat16
+    summ = torch.randn(B, hkv, n + 32, HEAD_DIM, device=dev, dtype=dtype)
+    q = torch.randn(B, hq, HEAD_DIM, device=dev, dtype=dtype)
+    table = (torch.arange(n + 1, dtype=torch.int32, device=dev)[None, :] * B
+             + torch.arange(B, dtype=torch.int32, device=dev)[:, None]).contiguous().view(-1)
+    indptr = torch.arange(B + 1, dtype=torch.int32, device=dev) * (n + 1)
+    last = torch.ones(B, dtype=torch.int32, device=dev)
+    out = torch.empty(B, hkv, topk + 1, dtype=torch.int32, device=dev)
+    status = ops.new_status(dev)
+    run = lambda: ops.select_pages(q, summ, table, indptr, last, topk, B * (n + 1), out=out, status=status)
+    for _ in range(args.warmup):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ops.raise_on_status(status)
+    ms = e0.elapsed_time(e1) / args.steps
+    nbytes = B * hkv * n * HEAD_DIM * 2
+    print(json.dumps({"micro": "select", "batch": B, "pages_scored": n, "topk": topk, "ms": ms,
+                      "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / (ms * 1e-3) / 1e9}), flush=True)
+
+
 def main():
     args = parse()
+    if args.micro == "select":
+        return run_micro_select(args)
     if args.impl == "reference":
         run_reference(args)
     else:

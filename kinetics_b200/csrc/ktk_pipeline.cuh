@@ -1,6 +1,6 @@
 // sm_100a building blocks for the staged kernels: mbarrier ring, TMA / bulk
 // asynchronous copies into shared memory, ldmatrix / mma.sync fragments.
-// Every wait is bounded: after kSpinCap polls it gives up and the caller leaves
+// Every wait is bounded: after kTryCap suspended tries it gives up and the caller leaves
 // the kernel with KTK_STATUS_TIMEOUT in the status word.
 #pragma once
 
@@ -10,7 +10,8 @@
 
 namespace ktk {
 
-constexpr uint32_t kSpinCap = 1u << 22;   // polls with a ~40 ns back-off each: a fraction of a second
+constexpr uint32_t kTryCap = 1u << 17;       // bounded waits: this many suspended tries ...
+constexpr uint32_t kTryHintNs = 8000;        // ... of at most this long each (about a second in all)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -30,24 +31,25 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+// One try: the warp is suspended by the hardware until the phase completes or the time hint
+// runs out, so a waiting warp issues next to no instructions.
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kTryHintNs)
         : "memory");
     return ok != 0;
 }
 // Bounded wait for the phase with the given parity.  Returns false if it gave up
 // (and raises *abort so that the rest of the CTA stops waiting too).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
-    for (uint32_t i = 0; i < kSpinCap; ++i) {
-        if (mbar_test(bar, parity)) return true;
-        if (i > 32) __nanosleep(40);
-        if ((i & 255u) == 255u && *abort) return false;
+    for (uint32_t i = 0; i < kTryCap; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort) return false;
     }
     *abort = 1;
     return false;

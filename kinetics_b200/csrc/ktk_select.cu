@@ -172,16 +172,15 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
                 // chunks whose partial sums meet in the first two levels of the contract's butterfly, so
                 // those two levels are plain in-lane adds and only two shuffles per row remain.  Odd rows
                 // visit their chunks rotated by one (bank conflicts); every add involved is commutative,
-                // so the value is the same bit for bit.  Two chunk chains run in one packed fp32x2 FMA.
+                // so the value is the same bit for bit.
                 const int rw = lane >> 2, j4 = lane & 3, rot = rw & 1;
-                float2 q01[8], q23[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    q01[e] = make_float2(qbar[8 * (j4 + 4 * ((0 + rot) & 3)) + e], qbar[8 * (j4 + 4 * ((1 + rot) & 3)) + e]);
-                    q23[e] = make_float2(qbar[8 * (j4 + 4 * ((2 + rot) & 3)) + e], qbar[8 * (j4 + 4 * ((3 + rot) & 3)) + e]);
-                }
                 const int c0 = (j4 + 4 * ((0 + rot) & 3)) * 8, c1 = (j4 + 4 * ((1 + rot) & 3)) * 8;
                 const int c2 = (j4 + 4 * ((2 + rot) & 3)) * 8, c3 = (j4 + 4 * ((3 + rot) & 3)) * 8;
+                float q0[8], q1[8], q2[8], q3[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    q0[e] = qbar[c0 + e]; q1[e] = qbar[c1 + e]; q2[e] = qbar[c2 + e]; q3[e] = qbar[c3 + e];
+                }
                 float* score_row = want_scores ? out_scores + bh * summary_stride : nullptr;
                 // this warp's stages of the item: stream positions i = warp (mod 8) inside [ibase, ibase + n_stages)
                 int i = ibase + ((warp - ibase) & (kSelWarps - 1));
@@ -204,14 +203,16 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
                         lds8(rowp + c1, x1);
                         lds8(rowp + c2, x2);
                         lds8(rowp + c3, x3);
-                        float2 a01 = make_float2(0.0f, 0.0f), a23 = make_float2(0.0f, 0.0f);
+                        float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;   // the lane's four chunk chains
 #pragma unroll
                         for (int e = 0; e < 8; ++e) {
-                            a01 = __ffma2_rn(q01[e], make_float2(x0[e], x1[e]), a01);
-                            a23 = __ffma2_rn(q23[e], make_float2(x2[e], x3[e]), a23);
+                            p0 = __fmaf_rn(q0[e], x0[e], p0);
+                            p1 = __fmaf_rn(q1[e], x1[e], p1);
+                            p2 = __fmaf_rn(q2[e], x2[e], p2);
+                            p3 = __fmaf_rn(q3[e], x3[e], p3);
                         }
-                        const float2 t = __fadd2_rn(a01, a23);        // butterfly level "xor 8"
-                        float acc = __fadd_rn(t.x, t.y);              // level "xor 4"
+                        // butterfly levels "xor 8" (p0 + p2, p1 + p3) and "xor 4", in the lane
+                        float acc = __fadd_rn(__fadd_rn(p0, p2), __fadd_rn(p1, p3));
                         acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
                         acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
                         acc = __fadd_rn(acc, 0.0f);
