@@ -162,6 +162,35 @@ KTK_API int ktk_sparse_decode(const void* q, const void* kv_cache, const int32_t
                       void* stream);
 
 /*
+ * ktk_sparse_decode for callers that can neither pass a workspace nor let the library
+ * allocate one.  No counterpart in the reference: flashinfer takes a caller-allocated
+ * 128 MB workspace, and nothing in the reference runs without one.
+ *
+ * Who needs it: an engine that gave all device memory to its own page pool when it
+ * started, so that an allocation made on its behalf would fail or shrink the pool; or a
+ * decode loop in which the device-wide synchronisation of cudaMalloc is not acceptable.
+ *
+ * Same arguments and results as ktk_sparse_decode, minus `workspace`.  The partial
+ * results of a split decode go to a 16 MiB array that is part of the library image
+ * (ktk_noalloc_scratch_bytes()); every GPU that loads the library keeps that array until
+ * the process ends.  A call whose splits need more (batch * Hq * num_splits * 520 bytes)
+ * returns KTK_ERR_TOO_LARGE and launches nothing.  The call itself performs no
+ * cudaMalloc / cudaFree and uses no allocating library routine.
+ *
+ * The first call on a device looks up the array's device address (one runtime query, no
+ * allocation); make that first call outside any stream capture.  All calls on a device
+ * share the one array: two calls whose kernels may overlap on the GPU (different
+ * streams) race on it -- keep them on one stream or order them with events.  Nothing in
+ * the array has to be cleared between calls.
+ */
+KTK_API size_t ktk_noalloc_scratch_bytes(void);
+KTK_API int ktk_sparse_decode_noalloc(const void* q, const void* kv_cache, const int32_t* sel_pages,
+                                      int32_t topk, const int32_t* kv_indptr,
+                                      const int32_t* kv_last_page_len, float sm_scale, void* o,
+                                      int32_t num_splits, int32_t variant, const ktk_shape* shape,
+                                      int32_t* status, void* stream);
+
+/*
  * Dense paged decode over all pages of each sequence (the baseline the sparse
  * path is compared with).
  * Replaces: benchmark/dense_decoder.py:149-156, :168-170, :178-189.

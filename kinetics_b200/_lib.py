@@ -46,6 +46,9 @@ _SIGNATURES = {
     "ktk_decode_workspace_bytes": (c_size_t, [POINTER(Shape), c_int32]),
     "ktk_sparse_decode": (c_int32, [c_void_p, c_void_p, _i32p, c_int32, _i32p, _i32p, c_float, c_void_p,
                                     c_void_p, c_size_t, c_int32, c_int32, POINTER(Shape), _i32p, c_void_p]),
+    "ktk_noalloc_scratch_bytes": (c_size_t, []),
+    "ktk_sparse_decode_noalloc": (c_int32, [c_void_p, c_void_p, _i32p, c_int32, _i32p, _i32p, c_float, c_void_p,
+                                            c_int32, c_int32, POINTER(Shape), _i32p, c_void_p]),
     "ktk_dense_decode": (c_int32, [c_void_p, c_void_p, _i32p, _i32p, _i32p, c_int32, c_float, c_void_p,
                                    c_void_p, c_size_t, c_int32, c_int32, POINTER(Shape), _i32p, c_void_p]),
     "ktk_rmsnorm": (c_int32, [c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int32, c_int32, c_void_p]),

@@ -377,3 +377,84 @@ extern "C" int ktk_dense_decode(const void* q, const void* kv_cache, const int32
                          kv_indptr, kv_last_page_len, sm_scale, o, workspace, workspace_bytes,
                          num_splits, variant, shape, status, stream);
 }
+
+// ---------------------------------------------------------------------------
+// Split decode without a caller-provided workspace and without any allocation.
+//
+// Some hosts of this library cannot hand it scratch memory and must not see it
+// allocate: a serving engine that claimed all of HBM for its own KV-page pool at
+// start-up (a cudaMalloc would fail or eat into that pool), or a decode loop that
+// cannot afford the device-wide synchronisation an allocation implies.  For them
+// the split partials live in the array below, which is part of the library image:
+// every GPU that loads the library carries these 16 MiB until the process exits.
+//
+// g_noalloc_scratch is a device symbol.  Host code may not use its name as an
+// address; ktk_noalloc_scratch() asks the runtime for the real device address, once
+// per device, with that device current, and that address is what the kernels get.
+// ---------------------------------------------------------------------------
+#include <mutex>
+
+namespace ktk {
+
+constexpr size_t kNoAllocScratchBytes = 16u << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kMaxDevices = 64;
+
+static int ktk_noalloc_scratch(void** out) {
+    static std::mutex mu;
+    static void* addr[kMaxDevices] = {};
+    int dev = -1;
+    KTK_CUDA_TRY(cudaGetDevice(&dev), "ktk_sparse_decode_noalloc");
+    if (dev < 0 || dev >= kMaxDevices) {
+        set_error("ktk_sparse_decode_noalloc: device ordinal %d outside [0, %d)", dev, kMaxDevices);
+        return KTK_ERR_UNSUPPORTED;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (addr[dev] == nullptr) {
+        void* p = nullptr;
+        KTK_CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_scratch), "ktk_sparse_decode_noalloc (scratch address)");
+        addr[dev] = p;
+    }
+    *out = addr[dev];
+    return KTK_OK;
+}
+
+}  // namespace ktk
+
+extern "C" size_t ktk_noalloc_scratch_bytes(void) { return ktk::kNoAllocScratchBytes; }
+
+extern "C" int ktk_sparse_decode_noalloc(const void* q, const void* kv_cache, const int32_t* sel_pages,
+                                         int32_t topk, const int32_t* kv_indptr,
+                                         const int32_t* kv_last_page_len, float sm_scale, void* o,
+                                         int32_t num_splits, int32_t variant, const ktk_shape* shape,
+                                         int32_t* status, void* stream) {
+    if (topk < 1) {
+        set_error("ktk_sparse_decode_noalloc: topk must be >= 1 (got %d)", topk);
+        return KTK_ERR_ARG;
+    }
+    int rc = check_shape(shape, "ktk_sparse_decode_noalloc");
+    if (rc != KTK_OK) return rc;
+    if (num_splits < 0 || num_splits > 256) {
+        set_error("ktk_sparse_decode_noalloc: num_splits %d outside [0, 256]", num_splits);
+        return KTK_ERR_ARG;
+    }
+    if (num_splits == 0) num_splits = ktk_decode_num_splits(shape, topk + 1);
+    const size_t need = ktk_decode_workspace_bytes(shape, num_splits);
+    if (need > kNoAllocScratchBytes) {
+        set_error("ktk_sparse_decode_noalloc: %d splits of this batch need %zu bytes of scratch, the built-in "
+                  "array holds %zu; use fewer splits, or ktk_sparse_decode with a workspace of your own",
+                  num_splits, need, (size_t)kNoAllocScratchBytes);
+        return KTK_ERR_TOO_LARGE;
+    }
+    void* scratch = nullptr;
+    if (need > 0) {
+        rc = ktk_noalloc_scratch(&scratch);
+        if (rc != KTK_OK) return rc;
+    }
+    // Every partial slot a launch later reads is written by that same launch (an empty split
+    // writes "nothing seen"), so the array needs no clearing between calls.
+    return decode_common("ktk_sparse_decode_noalloc", q, kv_cache, sel_pages, topk, topk + 1, kv_indptr,
+                         kv_last_page_len, sm_scale, o, scratch, need, num_splits, variant, shape, status,
+                         stream);
+}
