@@ -427,7 +427,14 @@ def run_ours(args):
         }
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Leave without tearing the communicator down: the captured graphs still reference its kernels,
+        # and destroy_process_group() has been seen to wait forever in that state.  Every rank has
+        # finished its work once it passes this barrier.
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def run_micro_select(args):
