@@ -321,8 +321,12 @@ def run_ours(args):
     ach_decode = bytes_decode / (t_decode * 1e-3) / 1e9
     ach_select = bytes_select / (t_select * 1e-3) / 1e9
     ach_attn = (bytes_decode + bytes_select) / ((t_decode + t_select) * 1e-3) / 1e9
+    # DRAM traffic per launch: ncu dram__bytes_read+write of this kernel on a B=296 capture of the same shape
+    # came to 1.002x the algorithmic bytes (profiles/decode_mma_kernel_cfg3_b296.md); it grows with the batch
+    # in proportion (one CTA per sequence, each page read once), so it is scaled to this run's batch.
+    traffic = int(bytes_decode * 1.002) + B * hkv * (cfg.num_attention_heads // cfg.num_key_value_heads) * HEAD_DIM * esz
     roofline = {"bound": "hbm", "kernel": "sparse decode (selected K/V pages)", "achieved": ach_decode,
-                "peak": peak_gbs, "unit": "GB/s", "frac": ach_decode / peak_gbs, "traffic": None,
+                "peak": peak_gbs, "unit": "GB/s", "frac": ach_decode / peak_gbs, "traffic": traffic,
                 "peak_kind": peak_kind, "ms": t_decode, "algorithmic_bytes": bytes_decode}
     kernels = {
         "select": {"ms": t_select, "algorithmic_bytes": bytes_select, "achieved_gbs": ach_select,
