@@ -76,6 +76,36 @@ typedef struct ktk_shape {
     int64_t num_pages;      /* physical pages in kv_cache (bounds check)         */
 } ktk_shape;
 
+/*
+ * Optional view of a sequence's pages, for callers whose block grid does not start at token 0
+ * or who keep more than the newest page always attended -- the LiteSys semantics of
+ * LiteSys/litesys/attention/sparsity_utils.py:24-47 (sink = 4 tokens, `attn_local` newest tokens,
+ * 16-token blocks counted from the end of the sink).  A null view means {0, 1, NULL, NULL}: the
+ * semantics of benchmark/blocktopk_decoder.py (every full page before the one being filled is
+ * scored, that last page is always attended).
+ *   sink_tokens  0..15.  When > 0, logical page 0 of every sequence holds only the first
+ *                sink_tokens tokens (slots 0..sink_tokens-1); it is never scored and always
+ *                attended.  Token t >= sink_tokens lives in logical page 1 + (t - sink_tokens) / 16.
+ *   local_tokens L >= 0.  Scored pages are the full pages whose tokens all lie more than L tokens
+ *                behind the end: n_dyn = max(0, tokens_after_sink - L) / 16 pages, right after
+ *                the sink page; every later page is always attended.
+ *   page_count   nullable int32[B]: number of pages of sequence b.  kv_indptr[b] is then only
+ *                the start of its list in kv_indices (lists need not be packed), and kv_indptr
+ *                needs B entries.
+ *   slot_index   nullable int32[B]: row of `summaries` that belongs to sequence b (default b).
+ * Selected-page rows then hold [sink page][<= topk picks][always-attended tail pages], at most
+ * ktk_view_row_width(topk, view) entries.
+ */
+typedef struct ktk_view {
+    int32_t sink_tokens;
+    int32_t local_tokens;
+    const int32_t* page_count;
+    const int32_t* slot_index;
+} ktk_view;
+
+/* Entries per (sequence, kv head) row of a selected-page table under `view` (topk + 1 for a null view). */
+KTK_API int32_t ktk_view_row_width(int32_t topk, const ktk_view* view);
+
 /* Human-readable text of the last error on the calling thread ("" if none). */
 KTK_API const char* ktk_last_error(void);
 /* Library version, "major.minor". */
@@ -216,6 +246,40 @@ KTK_API int ktk_rmsnorm(const void* x, const void* w, float eps, void* out, int6
  */
 KTK_API int ktk_silu_mul(const void* gate, const void* up, void* out, int64_t n, int32_t dtype,
                  void* stream);
+
+/*
+ * The same four operations under a ktk_view (null view = the plain entry points above).
+ * Replace, in the LiteSys decode path: copy_to_cache + kv_offset update
+ * (LiteSys/litesys/attention/batch_cache.py:76-84), the selection inside blockwise_topk_sparsity
+ * (sparsity_utils.py:24-47, reached through attn_logits_processor :217-249), and qk / softmax / sv
+ * (cache_utils.py:173-226) restricted to the kept tokens; dense when the view keeps everything
+ * (layers listed in attn_layer_skip, sparsity_utils.py:211,221-222).
+ * `out_pages` / `sel_pages` rows are `row_width` ints wide (>= ktk_view_row_width()).
+ */
+KTK_API int ktk_append_v(const void* k, const void* v, void* kv_cache, void* summaries,
+                         int64_t summary_stride, const int32_t* kv_indices, const int32_t* kv_indptr,
+                         const int32_t* kv_last_page_len, const ktk_view* view, const ktk_shape* shape,
+                         int32_t* status, void* stream);
+KTK_API int ktk_build_summaries_v(const void* kv_cache, void* summaries, int64_t summary_stride,
+                                  const int32_t* kv_indices, const int32_t* kv_indptr,
+                                  const int32_t* kv_last_page_len, const ktk_view* view,
+                                  const ktk_shape* shape, int32_t* status, void* stream);
+KTK_API int ktk_select_v(const void* q, const void* summaries, int64_t summary_stride,
+                         const int32_t* kv_indices, const int32_t* kv_indptr,
+                         const int32_t* kv_last_page_len, int32_t topk, const ktk_view* view,
+                         int32_t row_width, int32_t* out_pages, int32_t* out_logical, float* out_scores,
+                         const ktk_shape* shape, int32_t* status, void* stream);
+KTK_API int ktk_sparse_decode_v(const void* q, const void* kv_cache, const int32_t* sel_pages,
+                                int32_t topk, const ktk_view* view, int32_t row_width,
+                                const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                                float sm_scale, void* o, void* workspace, size_t workspace_bytes,
+                                int32_t num_splits, int32_t variant, const ktk_shape* shape,
+                                int32_t* status, void* stream);
+KTK_API int ktk_dense_decode_v(const void* q, const void* kv_cache, const int32_t* kv_indices,
+                               const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                               const ktk_view* view, int32_t max_pages_per_seq, float sm_scale, void* o,
+                               void* workspace, size_t workspace_bytes, int32_t num_splits,
+                               int32_t variant, const ktk_shape* shape, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -12,5 +12,6 @@ _lib.load()   # no fallback: a missing library is an ImportError
 from . import ops  # noqa: E402  (registers the torch ops)
 from .config import LayerConfig, get_config  # noqa: E402
 from .layers import BlockTopkDecoderLayer, DecoderLayer, init_weights  # noqa: E402
+from .batch_cache import BatchKVManager  # noqa: E402
 
-__all__ = ["ops", "LayerConfig", "get_config", "BlockTopkDecoderLayer", "DecoderLayer", "init_weights"]
+__all__ = ["ops", "LayerConfig", "get_config", "BlockTopkDecoderLayer", "DecoderLayer", "init_weights", "BatchKVManager"]

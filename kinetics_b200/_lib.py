@@ -32,6 +32,11 @@ class Shape(ctypes.Structure):
     ]
 
 
+class View(ctypes.Structure):
+    _fields_ = [("sink_tokens", c_int32), ("local_tokens", c_int32), ("page_count", c_void_p),
+                ("slot_index", c_void_p)]
+
+
 _i32p = c_void_p   # device pointers travel as integers
 _SIGNATURES = {
     "ktk_last_error": (c_char_p, []),
@@ -51,6 +56,19 @@ _SIGNATURES = {
                                             c_int32, c_int32, POINTER(Shape), _i32p, c_void_p]),
     "ktk_dense_decode": (c_int32, [c_void_p, c_void_p, _i32p, _i32p, _i32p, c_int32, c_float, c_void_p,
                                    c_void_p, c_size_t, c_int32, c_int32, POINTER(Shape), _i32p, c_void_p]),
+    "ktk_view_row_width": (c_int32, [c_int32, POINTER(View)]),
+    "ktk_append_v": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, _i32p, _i32p, _i32p, POINTER(View),
+                               POINTER(Shape), _i32p, c_void_p]),
+    "ktk_build_summaries_v": (c_int32, [c_void_p, c_void_p, c_int64, _i32p, _i32p, _i32p, POINTER(View),
+                                        POINTER(Shape), _i32p, c_void_p]),
+    "ktk_select_v": (c_int32, [c_void_p, c_void_p, c_int64, _i32p, _i32p, _i32p, c_int32, POINTER(View), c_int32,
+                               _i32p, _i32p, c_void_p, POINTER(Shape), _i32p, c_void_p]),
+    "ktk_sparse_decode_v": (c_int32, [c_void_p, c_void_p, _i32p, c_int32, POINTER(View), c_int32, _i32p, _i32p,
+                                      c_float, c_void_p, c_void_p, c_size_t, c_int32, c_int32, POINTER(Shape),
+                                      _i32p, c_void_p]),
+    "ktk_dense_decode_v": (c_int32, [c_void_p, c_void_p, _i32p, _i32p, _i32p, POINTER(View), c_int32, c_float,
+                                     c_void_p, c_void_p, c_size_t, c_int32, c_int32, POINTER(Shape), _i32p,
+                                     c_void_p]),
     "ktk_rmsnorm": (c_int32, [c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int32, c_int32, c_void_p]),
     "ktk_silu_mul": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
 }

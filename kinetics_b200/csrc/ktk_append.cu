@@ -13,11 +13,13 @@ __global__ void __launch_bounds__(kHeadDim)
 append_kernel(const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ cache,
               T* __restrict__ summaries, int64_t summary_stride,
               const int32_t* __restrict__ kv_indices, const int32_t* __restrict__ kv_indptr,
-              const int32_t* __restrict__ kv_last_page_len, int Hkv, int64_t num_pages,
-              int32_t* status) {
+              const int32_t* __restrict__ kv_last_page_len, const int32_t* __restrict__ page_count,
+              const int32_t* __restrict__ slot_index, int Hkv, int64_t num_pages, int32_t* status) {
     const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
-    const int beg = kv_indptr[b], end = kv_indptr[b + 1];
-    const int n_pages = end - beg;
+    const int beg = kv_indptr[b];
+    const int n_pages = page_count ? page_count[b] : kv_indptr[b + 1] - beg;
+    const int end = beg + n_pages;
+    const int srow_b = slot_index ? slot_index[b] : b;
     if (n_pages <= 0) return;  // empty slot: nothing to append
     const int last = kv_last_page_len[b];
     if (last < 1 || last > kPageSize || (summaries != nullptr && n_pages > summary_stride)) {
@@ -41,7 +43,7 @@ append_kernel(const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ 
         float acc = 0.0f;
         for (int t = 0; t < slot; ++t) acc = __fadd_rn(acc, to_f32(kpage[t * row]));
         acc = __fadd_rn(acc, to_f32(kn));
-        T* srow = summaries + (((int64_t)b * Hkv + h) * summary_stride + (n_pages - 1)) * kHeadDim;
+        T* srow = summaries + (((int64_t)srow_b * Hkv + h) * summary_stride + (n_pages - 1)) * kHeadDim;
         srow[d] = from_f32<T>(__fdiv_rn(acc, (float)last));
     }
 }
@@ -52,11 +54,13 @@ __global__ void __launch_bounds__(kHeadDim)
 build_summaries_kernel(const T* __restrict__ cache, T* __restrict__ summaries,
                        int64_t summary_stride, const int32_t* __restrict__ kv_indices,
                        const int32_t* __restrict__ kv_indptr,
-                       const int32_t* __restrict__ kv_last_page_len, int Hkv, int64_t num_pages,
+                       const int32_t* __restrict__ kv_last_page_len, const int32_t* __restrict__ page_count,
+                       const int32_t* __restrict__ slot_index, int sink_tokens, int Hkv, int64_t num_pages,
                        int32_t* status) {
     const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
-    const int beg = kv_indptr[b], end = kv_indptr[b + 1];
-    const int n_pages = end - beg;
+    const int beg = kv_indptr[b];
+    const int n_pages = page_count ? page_count[b] : kv_indptr[b + 1] - beg;
+    const int srow_b = slot_index ? slot_index[b] : b;
     if (n_pages <= 0) return;
     const int last = kv_last_page_len[b];
     if (last < 1 || last > kPageSize || n_pages > summary_stride) {
@@ -64,14 +68,15 @@ build_summaries_kernel(const T* __restrict__ cache, T* __restrict__ summaries,
         return;
     }
     const int64_t row = (int64_t)Hkv * kHeadDim;
-    T* sbase = summaries + ((int64_t)b * Hkv + h) * summary_stride * kHeadDim + d;
+    T* sbase = summaries + ((int64_t)srow_b * Hkv + h) * summary_stride * kHeadDim + d;
     for (int p = blockIdx.z; p < n_pages; p += gridDim.z) {
         const int64_t page = kv_indices[beg + p];
         if (page < 0 || page >= num_pages) {
             if (d == 0) report(status, KTK_STATUS_BAD_PAGE);
             continue;
         }
-        const int c = (p == n_pages - 1) ? last : kPageSize;
+        // a sink page (logical 0 under a view) holds sink_tokens keys unless it is also the last page
+        const int c = (p == n_pages - 1) ? last : ((p == 0 && sink_tokens > 0) ? sink_tokens : kPageSize);
         const T* kpage = cache + (page * 2) * kPageSize * row + (int64_t)h * kHeadDim + d;
         float x[kPageSize];
 #pragma unroll
@@ -150,12 +155,12 @@ silu_mul_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restr
 template <typename T>
 static int append_impl(const void* k, const void* v, void* cache, void* summaries,
                        int64_t summary_stride, const int32_t* kv_indices,
-                       const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                       const int32_t* kv_indptr, const int32_t* kv_last_page_len, const View& view,
                        const ktk_shape* s, int32_t* status, cudaStream_t st) {
     dim3 grid(s->batch, s->num_kv_heads);
     append_kernel<T><<<grid, kHeadDim, 0, st>>>(
         (const T*)k, (const T*)v, (T*)cache, (T*)summaries, summary_stride, kv_indices, kv_indptr,
-        kv_last_page_len, s->num_kv_heads, s->num_pages, status);
+        kv_last_page_len, view.page_count, view.slot_index, s->num_kv_heads, s->num_pages, status);
     KTK_CUDA_TRY(cudaGetLastError(), "ktk_append");
     return KTK_OK;
 }
@@ -163,7 +168,7 @@ static int append_impl(const void* k, const void* v, void* cache, void* summarie
 template <typename T>
 static int build_impl(const void* cache, void* summaries, int64_t summary_stride,
                       const int32_t* kv_indices, const int32_t* kv_indptr,
-                      const int32_t* kv_last_page_len, const ktk_shape* s, int32_t* status,
+                      const int32_t* kv_last_page_len, const View& view, const ktk_shape* s, int32_t* status,
                       cudaStream_t st) {
     const int64_t bh = (int64_t)s->batch * s->num_kv_heads;
     int z = (int)((8LL * sm_count() + bh - 1) / bh);
@@ -172,7 +177,7 @@ static int build_impl(const void* cache, void* summaries, int64_t summary_stride
     dim3 grid(s->batch, s->num_kv_heads, z);
     build_summaries_kernel<T><<<grid, kHeadDim, 0, st>>>(
         (const T*)cache, (T*)summaries, summary_stride, kv_indices, kv_indptr, kv_last_page_len,
-        s->num_kv_heads, s->num_pages, status);
+        view.page_count, view.slot_index, view.sink_tokens, s->num_kv_heads, s->num_pages, status);
     KTK_CUDA_TRY(cudaGetLastError(), "ktk_build_summaries");
     return KTK_OK;
 }
@@ -181,11 +186,13 @@ static int build_impl(const void* cache, void* summaries, int64_t summary_stride
 
 using namespace ktk;
 
-extern "C" int ktk_append(const void* k, const void* v, void* kv_cache, void* summaries,
-                          int64_t summary_stride, const int32_t* kv_indices,
-                          const int32_t* kv_indptr, const int32_t* kv_last_page_len,
-                          const ktk_shape* shape, int32_t* status, void* stream) {
+extern "C" int ktk_append_v(const void* k, const void* v, void* kv_cache, void* summaries,
+                            int64_t summary_stride, const int32_t* kv_indices,
+                            const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                            const ktk_view* view_in, const ktk_shape* shape, int32_t* status, void* stream) {
     int rc = check_shape(shape, "ktk_append");
+    if (rc != KTK_OK) return rc;
+    rc = check_view(view_in, "ktk_append");
     if (rc != KTK_OK) return rc;
     if (shape->batch == 0) return KTK_OK;
     if (!k || !v || !kv_cache || !kv_indices || !kv_indptr || !kv_last_page_len) {
@@ -196,19 +203,30 @@ extern "C" int ktk_append(const void* k, const void* v, void* kv_cache, void* su
         set_error("ktk_append: summary_stride must be positive (got %lld)", (long long)summary_stride);
         return KTK_ERR_ARG;
     }
+    const View view = make_view(view_in);
     cudaStream_t st = (cudaStream_t)stream;
     if (shape->dtype == KTK_F32)
         return append_impl<float>(k, v, kv_cache, summaries, summary_stride, kv_indices, kv_indptr,
-                                  kv_last_page_len, shape, status, st);
+                                  kv_last_page_len, view, shape, status, st);
     return append_impl<__nv_bfloat16>(k, v, kv_cache, summaries, summary_stride, kv_indices,
-                                      kv_indptr, kv_last_page_len, shape, status, st);
+                                      kv_indptr, kv_last_page_len, view, shape, status, st);
 }
 
-extern "C" int ktk_build_summaries(const void* kv_cache, void* summaries, int64_t summary_stride,
-                                   const int32_t* kv_indices, const int32_t* kv_indptr,
-                                   const int32_t* kv_last_page_len, const ktk_shape* shape,
-                                   int32_t* status, void* stream) {
+extern "C" int ktk_append(const void* k, const void* v, void* kv_cache, void* summaries,
+                          int64_t summary_stride, const int32_t* kv_indices,
+                          const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                          const ktk_shape* shape, int32_t* status, void* stream) {
+    return ktk_append_v(k, v, kv_cache, summaries, summary_stride, kv_indices, kv_indptr, kv_last_page_len,
+                        nullptr, shape, status, stream);
+}
+
+extern "C" int ktk_build_summaries_v(const void* kv_cache, void* summaries, int64_t summary_stride,
+                                     const int32_t* kv_indices, const int32_t* kv_indptr,
+                                     const int32_t* kv_last_page_len, const ktk_view* view_in,
+                                     const ktk_shape* shape, int32_t* status, void* stream) {
     int rc = check_shape(shape, "ktk_build_summaries");
+    if (rc != KTK_OK) return rc;
+    rc = check_view(view_in, "ktk_build_summaries");
     if (rc != KTK_OK) return rc;
     if (shape->batch == 0) return KTK_OK;
     if (!kv_cache || !summaries || !kv_indices || !kv_indptr || !kv_last_page_len) {
@@ -219,12 +237,21 @@ extern "C" int ktk_build_summaries(const void* kv_cache, void* summaries, int64_
         set_error("ktk_build_summaries: summary_stride must be positive");
         return KTK_ERR_ARG;
     }
+    const View view = make_view(view_in);
     cudaStream_t st = (cudaStream_t)stream;
     if (shape->dtype == KTK_F32)
         return build_impl<float>(kv_cache, summaries, summary_stride, kv_indices, kv_indptr,
-                                 kv_last_page_len, shape, status, st);
+                                 kv_last_page_len, view, shape, status, st);
     return build_impl<__nv_bfloat16>(kv_cache, summaries, summary_stride, kv_indices, kv_indptr,
-                                     kv_last_page_len, shape, status, st);
+                                     kv_last_page_len, view, shape, status, st);
+}
+
+extern "C" int ktk_build_summaries(const void* kv_cache, void* summaries, int64_t summary_stride,
+                                   const int32_t* kv_indices, const int32_t* kv_indptr,
+                                   const int32_t* kv_last_page_len, const ktk_shape* shape,
+                                   int32_t* status, void* stream) {
+    return ktk_build_summaries_v(kv_cache, summaries, summary_stride, kv_indices, kv_indptr, kv_last_page_len,
+                                 nullptr, shape, status, stream);
 }
 
 extern "C" int ktk_rmsnorm(const void* x, const void* w, float eps, void* out, int64_t rows,

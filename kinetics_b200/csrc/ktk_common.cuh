@@ -18,6 +18,32 @@ void set_error(const char* fmt, ...);
 int check_shape(const ktk_shape* s, const char* who);
 int cuda_fail(cudaError_t e, const char* who);
 int sm_count();
+int check_view(const ktk_view* v, const char* who);
+
+// a ktk_view with the defaults filled in
+struct View {
+    int sink_tokens = 0;
+    int local_tokens = 1;
+    const int32_t* page_count = nullptr;
+    const int32_t* slot_index = nullptr;
+};
+inline View make_view(const ktk_view* v) {
+    View r;
+    if (v != nullptr) {
+        r.sink_tokens = v->sink_tokens;
+        r.local_tokens = v->local_tokens;
+        r.page_count = v->page_count;
+        r.slot_index = v->slot_index;
+    }
+    return r;
+}
+// most always-attended pages behind the scored ones: 1 + ceil((L - 1) / 16), and 1 for L = 0
+inline int view_back_max(int local_tokens) {
+    return local_tokens <= 1 ? 1 : 1 + (local_tokens - 1 + kPageSize - 1) / kPageSize;
+}
+inline int view_row_width(int topk, const View& v) {
+    return (v.sink_tokens > 0 ? 1 : 0) + topk + view_back_max(v.local_tokens);
+}
 
 #define KTK_CUDA_TRY(expr, who)                        \
     do {                                               \

@@ -102,7 +102,7 @@ decode_simt_kernel(const DecodeParams p) {
 
     // one page of the warp: scores, online softmax, weighted values
     auto consume = [&](int e, const R (&kr)[kPageSize], const R (&vr)[kPageSize]) {
-        const int ntok = (e == el.cnt - 1) ? el.last : kPageSize;
+        const int ntok = entry_tokens(el, e);
         const int tok = lane >> 1;               // the token this lane ends up holding
         float s[G];
 #pragma unroll
@@ -274,9 +274,21 @@ static int decode_common(const char* who, const void* q, const void* cache, cons
                          int topk, int max_entries, const int32_t* kv_indptr,
                          const int32_t* kv_last_page_len, float sm_scale, void* o, void* workspace,
                          size_t workspace_bytes, int num_splits, int variant, const ktk_shape* s,
-                         int32_t* status, void* stream) {
+                         int32_t* status, void* stream, const ktk_view* view_in = nullptr,
+                         int row_width = 0) {
     int rc = check_shape(s, who);
     if (rc != KTK_OK) return rc;
+    rc = check_view(view_in, who);
+    if (rc != KTK_OK) return rc;
+    const View view = make_view(view_in);
+    if (topk >= 0) {
+        const int need_width = view_row_width(topk, view);
+        if (row_width == 0) row_width = need_width;
+        if (row_width < need_width) {
+            set_error("%s: selected-page rows of %d entries, this view needs %d", who, row_width, need_width);
+            return KTK_ERR_ARG;
+        }
+    }
     if (s->batch == 0) return KTK_OK;
     if (!q || !cache || !entries || !kv_indptr || !kv_last_page_len || !o) {
         set_error("%s: null pointer argument", who);
@@ -303,6 +315,8 @@ static int decode_common(const char* who, const void* q, const void* cache, cons
     DecodeParams p;
     p.q = q; p.cache = cache; p.o = o; p.entries = entries;
     p.kv_indptr = kv_indptr; p.kv_last_page_len = kv_last_page_len;
+    p.sink_tokens = view.sink_tokens; p.local_tokens = view.local_tokens; p.page_count = view.page_count;
+    p.entry_stride = row_width;
     p.topk = topk; p.batch = s->batch; p.Hkv = s->num_kv_heads; p.num_pages = s->num_pages;
     p.scale_log2 = sm_scale * kLog2e;
     p.num_splits = num_splits; p.ws_ml = nullptr; p.ws_o = nullptr; p.status = status;
@@ -457,4 +471,32 @@ extern "C" int ktk_sparse_decode_noalloc(const void* q, const void* kv_cache, co
     return decode_common("ktk_sparse_decode_noalloc", q, kv_cache, sel_pages, topk, topk + 1, kv_indptr,
                          kv_last_page_len, sm_scale, o, scratch, need, num_splits, variant, shape, status,
                          stream);
+}
+
+extern "C" int ktk_sparse_decode_v(const void* q, const void* kv_cache, const int32_t* sel_pages,
+                                   int32_t topk, const ktk_view* view, int32_t row_width,
+                                   const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                                   float sm_scale, void* o, void* workspace, size_t workspace_bytes,
+                                   int32_t num_splits, int32_t variant, const ktk_shape* shape,
+                                   int32_t* status, void* stream) {
+    if (topk < 1) {
+        set_error("ktk_sparse_decode_v: topk must be >= 1 (got %d)", topk);
+        return KTK_ERR_ARG;
+    }
+    if (check_view(view, "ktk_sparse_decode_v") != KTK_OK) return KTK_ERR_ARG;
+    return decode_common("ktk_sparse_decode_v", q, kv_cache, sel_pages, topk,
+                         view_row_width(topk, make_view(view)), kv_indptr, kv_last_page_len, sm_scale, o,
+                         workspace, workspace_bytes, num_splits, variant, shape, status, stream, view,
+                         row_width);
+}
+
+extern "C" int ktk_dense_decode_v(const void* q, const void* kv_cache, const int32_t* kv_indices,
+                                  const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                                  const ktk_view* view, int32_t max_pages_per_seq, float sm_scale, void* o,
+                                  void* workspace, size_t workspace_bytes, int32_t num_splits,
+                                  int32_t variant, const ktk_shape* shape, int32_t* status, void* stream) {
+    if (max_pages_per_seq < 1) max_pages_per_seq = 1;
+    return decode_common("ktk_dense_decode_v", q, kv_cache, kv_indices, -1, max_pages_per_seq, kv_indptr,
+                         kv_last_page_len, sm_scale, o, workspace, workspace_bytes, num_splits, variant,
+                         shape, status, stream, view, 0);
 }

@@ -158,7 +158,7 @@ decode_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap kv_map)
             }
             if (tag > 0) {
                 const int e = e0 + i;
-                const int ntok = (e == el.cnt - 1) ? el.last : kPageSize;
+                const int ntok = entry_tokens(el, e);
                 const uint32_t kt = stage_base + s * kStageBytes;
                 const uint32_t vt = kt + 2 * kHalfTile;
                 if (ntok < kPageSize) {

@@ -44,6 +44,16 @@ int check_shape(const ktk_shape* s, const char* who) {
     return KTK_OK;
 }
 
+int check_view(const ktk_view* v, const char* who) {
+    if (v == nullptr) return KTK_OK;
+    if (v->sink_tokens < 0 || v->sink_tokens >= kPageSize || v->local_tokens < 0 || v->local_tokens > (1 << 24)) {
+        set_error("%s: view with sink_tokens=%d (0..%d), local_tokens=%d (>= 0)", who, v->sink_tokens,
+                  kPageSize - 1, v->local_tokens);
+        return KTK_ERR_ARG;
+    }
+    return KTK_OK;
+}
+
 int sm_count() {
     static thread_local int cached_dev = -1;
     static thread_local int cached = 0;
@@ -98,4 +108,8 @@ int make_tensor_map_3d(CUtensorMap* out, const void* base, CUtensorMapDataType d
 }  // namespace ktk
 
 extern "C" const char* ktk_last_error(void) { return ktk::g_err; }
-extern "C" const char* ktk_version(void) { return "0.1"; }
+extern "C" const char* ktk_version(void) { return "0.2"; }
+extern "C" int32_t ktk_view_row_width(int32_t topk, const ktk_view* view) {
+    if (ktk::check_view(view, "ktk_view_row_width") != KTK_OK || topk < 0) return -1;
+    return ktk::view_row_width(topk, ktk::make_view(view));
+}

@@ -13,6 +13,7 @@
 // which is unique per page: the k largest composites are "largest score first, ties
 // to the lowest page number".
 #include "ktk_common.cuh"
+#include "ktk_decode.cuh"
 #include "ktk_pipeline.cuh"
 
 namespace ktk {
@@ -47,22 +48,36 @@ __device__ __forceinline__ void lds8(const __nv_bfloat16* p, float (&out)[8]) {
     unpack8(*reinterpret_cast<const uint4*>(p), out);
 }
 
+// The view of the page table a launch works under (ktk_view with defaults filled in) and the
+// width of an output row.
+struct SelView {
+    int sink_tokens, local_tokens, row_width;
+    const int32_t* page_count;
+    const int32_t* slot_index;
+};
+
 // What both the producer and the consumers derive for a work item (sequence b, kv head h).
+// Scored page r (0 <= r < n_scored) is logical page front + r of the sequence.
 struct SelItem {
-    int beg, n_pages, n_scored, n_stages;
+    int beg, n_pages, front, n_scored, back, n_stages, slot;
     bool bad, need_select, scan;
 };
 
 template <int kRowsPerStage>
 __device__ __forceinline__ SelItem sel_item(int b, const int32_t* kv_indptr, const int32_t* kv_last_page_len,
-                                            int64_t summary_stride, int key_cap, int topk, bool want_scores) {
+                                            const SelView& view, int64_t summary_stride, int key_cap, int topk,
+                                            bool want_scores) {
     SelItem it;
+    const PageSplit ps = page_split(kv_indptr, view.page_count, kv_last_page_len, b, view.sink_tokens,
+                                    view.local_tokens);
     it.beg = kv_indptr[b];
-    it.n_pages = kv_indptr[b + 1] - it.beg;
-    const int last = (it.n_pages > 0) ? kv_last_page_len[b] : 1;
-    it.n_scored = it.n_pages - 1;
-    it.bad = it.n_pages > 0 && (last < 1 || last > kPageSize || it.n_scored > summary_stride ||
-                                it.n_scored > key_cap);
+    it.slot = view.slot_index ? view.slot_index[b] : b;
+    it.n_pages = ps.n_pages;
+    it.front = ps.front;
+    it.n_scored = ps.n_dyn;
+    it.back = ps.back;
+    it.bad = ps.bad || (ps.n_pages > 0 && (it.front + it.n_scored > summary_stride || it.n_scored > key_cap ||
+                                           it.slot < 0));
     it.need_select = !it.bad && it.n_scored > topk;
     it.scan = it.n_pages > 0 && !it.bad && (it.need_select || want_scores) && it.n_scored > 0;
     it.n_stages = it.scan ? (it.n_scored + kRowsPerStage - 1) / kRowsPerStage : 0;
@@ -79,7 +94,7 @@ template <typename T, int G>
 __global__ void __launch_bounds__(kSelCtaThreads, kSelCtasPerSm)
 select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t summary_stride,
               const int32_t* __restrict__ kv_indices, const int32_t* __restrict__ kv_indptr,
-              const int32_t* __restrict__ kv_last_page_len, int topk, int key_cap, int kp,
+              const int32_t* __restrict__ kv_last_page_len, int topk, int key_cap, int kp, const SelView view,
               int32_t* __restrict__ out_pages, int32_t* __restrict__ out_logical,
               float* __restrict__ out_scores, int64_t n_items, int Hkv, int64_t num_pages,
               int32_t* status) {
@@ -100,7 +115,7 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
     uint32_t* keys = reinterpret_cast<uint32_t*>(sel + kp);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int stride_out = topk + 1;
+    const int stride_out = view.row_width;
     const bool want_scores = out_scores != nullptr;
 
     if (tid == 0) {
@@ -121,9 +136,10 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
             bool alive = true;
             for (int64_t bh = blockIdx.x; bh < n_items && alive; bh += gridDim.x) {
                 const int b = (int)(bh / Hkv);
-                const SelItem it = sel_item<kRowsPerStage>(b, kv_indptr, kv_last_page_len, summary_stride,
+                const int h = (int)(bh % Hkv);
+                const SelItem it = sel_item<kRowsPerStage>(b, kv_indptr, kv_last_page_len, view, summary_stride,
                                                            key_cap, topk, want_scores);
-                const T* sbase = summaries + bh * summary_stride * kHeadDim;
+                const T* sbase = summaries + (((int64_t)it.slot * Hkv + h) * summary_stride + it.front) * kHeadDim;
                 for (int st = 0; st < it.n_stages; ++st, ++i) {
                     const int s = i % kSelStages;
                     if (i >= kSelStages && !mbar_wait(&empty_bar[s], ((i / kSelStages) - 1) & 1, &abort_flag)) {
@@ -146,7 +162,7 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
             const int b = (int)(bh / Hkv), h = (int)(bh % Hkv);
             int32_t* row_pages = out_pages + bh * stride_out;
             int32_t* row_logical = out_logical ? out_logical + bh * stride_out : nullptr;
-            const SelItem it = sel_item<kRowsPerStage>(b, kv_indptr, kv_last_page_len, summary_stride, key_cap,
+            const SelItem it = sel_item<kRowsPerStage>(b, kv_indptr, kv_last_page_len, view, summary_stride, key_cap,
                                                        topk, want_scores);
             if (it.n_pages <= 0 || it.bad) {
                 if (it.bad && tid == 0) report(status, KTK_STATUS_BAD_TABLE);
@@ -181,7 +197,7 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
                 for (int e = 0; e < 8; ++e) {
                     q0[e] = qbar[c0 + e]; q1[e] = qbar[c1 + e]; q2[e] = qbar[c2 + e]; q3[e] = qbar[c3 + e];
                 }
-                float* score_row = want_scores ? out_scores + bh * summary_stride : nullptr;
+                float* score_row = want_scores ? out_scores + bh * summary_stride + it.front : nullptr;
                 // this warp's stages of the item: stream positions i = warp (mod 8) inside [ibase, ibase + n_stages)
                 int i = ibase + ((warp - ibase) & (kSelWarps - 1));
                 bool ok = true;
@@ -235,7 +251,7 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
                 // every scored page is taken, in page order, then the page being filled
                 for (int i = tid; i < stride_out; i += kSelThreads) {
                     int logical = -1, phys = -1;
-                    if (i <= it.n_scored) {
+                    if (i < it.n_pages) {
                         logical = i;
                         phys = kv_indices[it.beg + i];
                         if (phys < 0 || phys >= num_pages) report(status, KTK_STATUS_BAD_PAGE);
@@ -317,9 +333,15 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
                 }
             }
             for (int i = tid; i < stride_out; i += kSelThreads) {
-                const int logical = (i < topk) ? (int)(0xFFFFu - (unsigned)(sel[i] & 0xFFFFull)) : it.n_pages - 1;
-                const int phys = kv_indices[it.beg + logical];
-                if (phys < 0 || phys >= num_pages) report(status, KTK_STATUS_BAD_PAGE);
+                // [sink page][picks, best first][always-attended tail pages], then -1
+                int logical = -1, phys = -1;
+                if (i < it.front) logical = 0;
+                else if (i < it.front + topk) logical = it.front + (int)(0xFFFFu - (unsigned)(sel[i - it.front] & 0xFFFFull));
+                else if (i < it.front + topk + it.back) logical = it.front + it.n_scored + (i - it.front - topk);
+                if (logical >= 0) {
+                    phys = kv_indices[it.beg + logical];
+                    if (phys < 0 || phys >= num_pages) report(status, KTK_STATUS_BAD_PAGE);
+                }
                 row_pages[i] = phys;
                 if (row_logical) row_logical[i] = logical;
             }
@@ -340,7 +362,7 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
 template <typename T, int G>
 static int select_launch(const void* q, const void* summaries, int64_t summary_stride,
                          const int32_t* kv_indices, const int32_t* kv_indptr,
-                         const int32_t* kv_last_page_len, int topk, int32_t* out_pages,
+                         const int32_t* kv_last_page_len, int topk, SelView view, int32_t* out_pages,
                          int32_t* out_logical, float* out_scores, const ktk_shape* s,
                          int32_t* status, cudaStream_t st) {
     int key_cap = (int)(summary_stride < kMaxScoredPages ? summary_stride : kMaxScoredPages);
@@ -356,7 +378,7 @@ static int select_launch(const void* q, const void* summaries, int64_t summary_s
     if (grid > items) grid = items;
     kern<<<(unsigned)grid, kSelCtaThreads, smem, st>>>(
         (const T*)q, (const T*)summaries, summary_stride, kv_indices, kv_indptr, kv_last_page_len,
-        topk, key_cap, kp, out_pages, out_logical, out_scores, items, s->num_kv_heads, s->num_pages,
+        topk, key_cap, kp, view, out_pages, out_logical, out_scores, items, s->num_kv_heads, s->num_pages,
         status);
     KTK_CUDA_TRY(cudaGetLastError(), "ktk_select");
     return KTK_OK;
@@ -376,16 +398,25 @@ static int select_group(int G, A... a) {
 
 using namespace ktk;
 
-extern "C" int ktk_select(const void* q, const void* summaries, int64_t summary_stride,
-                          const int32_t* kv_indices, const int32_t* kv_indptr,
-                          const int32_t* kv_last_page_len, int32_t topk, int32_t* out_pages,
-                          int32_t* out_logical, float* out_scores, const ktk_shape* shape,
-                          int32_t* status, void* stream) {
+extern "C" int ktk_select_v(const void* q, const void* summaries, int64_t summary_stride,
+                            const int32_t* kv_indices, const int32_t* kv_indptr,
+                            const int32_t* kv_last_page_len, int32_t topk, const ktk_view* view_in,
+                            int32_t row_width, int32_t* out_pages, int32_t* out_logical, float* out_scores,
+                            const ktk_shape* shape, int32_t* status, void* stream) {
     int rc = check_shape(shape, "ktk_select");
+    if (rc != KTK_OK) return rc;
+    rc = check_view(view_in, "ktk_select");
     if (rc != KTK_OK) return rc;
     if (topk < 1 || topk > kMaxTopk) {
         set_error("ktk_select: topk %d outside [1, %d]", topk, kMaxTopk);
         return topk < 1 ? KTK_ERR_ARG : KTK_ERR_TOO_LARGE;
+    }
+    const View v = make_view(view_in);
+    const int need_width = view_row_width(topk, v);
+    if (row_width == 0) row_width = need_width;
+    if (row_width < need_width) {
+        set_error("ktk_select: output rows of %d entries, this view needs %d", row_width, need_width);
+        return KTK_ERR_ARG;
     }
     if (shape->batch == 0) return KTK_OK;
     if (!q || !summaries || !kv_indices || !kv_indptr || !kv_last_page_len || !out_pages) {
@@ -404,12 +435,24 @@ extern "C" int ktk_select(const void* q, const void* summaries, int64_t summary_
         set_error("ktk_select: batch * num_kv_heads exceeds the grid limit");
         return KTK_ERR_TOO_LARGE;
     }
+    SelView sv;
+    sv.sink_tokens = v.sink_tokens; sv.local_tokens = v.local_tokens; sv.row_width = row_width;
+    sv.page_count = v.page_count; sv.slot_index = v.slot_index;
     cudaStream_t st = (cudaStream_t)stream;
     if (shape->dtype == KTK_F32)
         return select_group<float>(shape->group_size, q, summaries, summary_stride, kv_indices,
-                                   kv_indptr, kv_last_page_len, (int)topk, out_pages, out_logical,
+                                   kv_indptr, kv_last_page_len, (int)topk, sv, out_pages, out_logical,
                                    out_scores, shape, status, st);
     return select_group<__nv_bfloat16>(shape->group_size, q, summaries, summary_stride, kv_indices,
-                                       kv_indptr, kv_last_page_len, (int)topk, out_pages,
+                                       kv_indptr, kv_last_page_len, (int)topk, sv, out_pages,
                                        out_logical, out_scores, shape, status, st);
+}
+
+extern "C" int ktk_select(const void* q, const void* summaries, int64_t summary_stride,
+                          const int32_t* kv_indices, const int32_t* kv_indptr,
+                          const int32_t* kv_last_page_len, int32_t topk, int32_t* out_pages,
+                          int32_t* out_logical, float* out_scores, const ktk_shape* shape,
+                          int32_t* status, void* stream) {
+    return ktk_select_v(q, summaries, summary_stride, kv_indices, kv_indptr, kv_last_page_len, topk, nullptr, 0,
+                        out_pages, out_logical, out_scores, shape, status, stream);
 }

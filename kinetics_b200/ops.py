@@ -76,6 +76,50 @@ def _shape(batch: int, kv_cache: torch.Tensor, num_q_heads: int) -> Shape:
                  kv_cache.shape[0])
 
 
+class PageView:
+    """How the pages of a sequence split into always-attended and scored ones (`ktk_view` in ktk.h).
+
+    The default (no view) is the reference benchmark's: every full page in front of the page being
+    filled is scored, that last page is always attended.  LiteSys semantics
+    (litesys/attention/sparsity_utils.py:24-47) are ``PageView(sink_tokens=4, local_tokens=attn_local)``
+    over a page table whose logical page 0 holds the 4 sink tokens.
+    """
+
+    def __init__(self, sink_tokens: int = 0, local_tokens: int = 1, page_count=None, slot_index=None):
+        self.sink_tokens, self.local_tokens = int(sink_tokens), int(local_tokens)
+        self.page_count, self.slot_index = page_count, slot_index
+        for t in (page_count, slot_index):
+            if t is not None and (t.dtype != torch.int32 or not t.is_cuda or not t.is_contiguous()):
+                raise ValueError("PageView: page_count / slot_index must be contiguous int32 CUDA tensors")
+
+    def c(self):
+        return _lib.View(self.sink_tokens, self.local_tokens,
+                         0 if self.page_count is None else self.page_count.data_ptr(),
+                         0 if self.slot_index is None else self.slot_index.data_ptr())
+
+    def row_width(self, topk: int) -> int:
+        v = self.c()
+        w = int(_lib.load().ktk_view_row_width(topk, ctypes.byref(v)))
+        if w < 0:
+            raise ValueError(_lib.load().ktk_last_error().decode())
+        return w
+
+    def batch(self, kv_indptr) -> int:
+        return kv_indptr.numel() if self.page_count is not None else kv_indptr.numel() - 1
+
+
+def _view_ref(view):
+    """(ctypes pointer or None, keep-alive object)"""
+    if view is None:
+        return None, None
+    cv = view.c()
+    return ctypes.byref(cv), cv
+
+
+def _batch_of(kv_indptr, view) -> int:
+    return view.batch(kv_indptr) if view is not None else kv_indptr.numel() - 1
+
+
 def new_status(device) -> torch.Tensor:
     """Device status word the kernels report table / page-id faults into (0 = ok)."""
     return torch.zeros(1, dtype=torch.int32, device=device)
@@ -92,14 +136,14 @@ def raise_on_status(status: torch.Tensor) -> None:
 # functional API
 # --------------------------------------------------------------------------------------
 
-def append_kv(k, v, kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len, status=None) -> None:
+def append_kv(k, v, kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len, status=None, view=None) -> None:
     """Write one new token per sequence into the paged cache and refresh its page summary.
 
     k, v: [B, Hkv, D].  The page table already includes the new token
     (flashinfer.append_paged_kv_cache convention, benchmark/blocktopk_decoder.py:38-46).
     """
     _cuda(k, v, kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len, status)
-    B = kv_indptr.numel() - 1
+    B = _batch_of(kv_indptr, view)
     if k.shape != (B, kv_cache.shape[3], kv_cache.shape[4]) or v.shape != k.shape:
         raise ValueError(f"k/v must be [B={B}, Hkv, D], got {tuple(k.shape)}")
     if k.dtype != kv_cache.dtype or v.dtype != kv_cache.dtype:
@@ -107,30 +151,32 @@ def append_kv(k, v, kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len
     shp = _shape(B, kv_cache, kv_cache.shape[3])
     stride = 0
     if summaries is not None:
-        if summaries.dtype != kv_cache.dtype or summaries.shape[0] < B or summaries.shape[1] != shp.num_kv_heads:
-            raise ValueError("summaries must be [>=B, Hkv, pages, D] in the cache dtype")
+        if summaries.dtype != kv_cache.dtype or summaries.shape[1] != shp.num_kv_heads:
+            raise ValueError("summaries must be [rows, Hkv, pages, D] in the cache dtype")
         stride = summaries.shape[2]
-    check(_lib.load().ktk_append(_ptr(k), _ptr(v), _ptr(kv_cache), _ptr(summaries), stride, _ptr(kv_indices),
-                                 _ptr(kv_indptr), _ptr(kv_last_page_len), ctypes.byref(shp), _ptr(status),
-                                 _stream()))
+    vp, _keep = _view_ref(view)
+    check(_lib.load().ktk_append_v(_ptr(k), _ptr(v), _ptr(kv_cache), _ptr(summaries), stride, _ptr(kv_indices),
+                                   _ptr(kv_indptr), _ptr(kv_last_page_len), vp, ctypes.byref(shp), _ptr(status),
+                                   _stream()))
     _launched()
 
 
-def build_summaries(kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len, status=None) -> None:
+def build_summaries(kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len, status=None, view=None) -> None:
     """Recompute the mean-key summary of every page of every sequence."""
     _cuda(kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len, status)
-    B = kv_indptr.numel() - 1
+    B = _batch_of(kv_indptr, view)
     shp = _shape(B, kv_cache, kv_cache.shape[3])
-    if summaries.dtype != kv_cache.dtype or summaries.shape[0] < B or summaries.shape[1] != shp.num_kv_heads:
-        raise ValueError("summaries must be [>=B, Hkv, pages, D] in the cache dtype")
-    check(_lib.load().ktk_build_summaries(_ptr(kv_cache), _ptr(summaries), summaries.shape[2], _ptr(kv_indices),
-                                          _ptr(kv_indptr), _ptr(kv_last_page_len), ctypes.byref(shp),
-                                          _ptr(status), _stream()))
+    if summaries.dtype != kv_cache.dtype or summaries.shape[1] != shp.num_kv_heads:
+        raise ValueError("summaries must be [rows, Hkv, pages, D] in the cache dtype")
+    vp, _keep = _view_ref(view)
+    check(_lib.load().ktk_build_summaries_v(_ptr(kv_cache), _ptr(summaries), summaries.shape[2], _ptr(kv_indices),
+                                            _ptr(kv_indptr), _ptr(kv_last_page_len), vp, ctypes.byref(shp),
+                                            _ptr(status), _stream()))
     _launched()
 
 
 def select_pages(q, summaries, kv_indices, kv_indptr, kv_last_page_len, topk: int, num_pages: int,
-                 out=None, out_logical=None, out_scores=None, status=None):
+                 out=None, out_logical=None, out_scores=None, status=None, view=None):
     """Score every filled page against the query group and pick the top-k pages.
 
     q [B, Hq, D]; summaries [B, Hkv, n, D].  Returns int32 [B, Hkv, topk+1] physical page ids
@@ -142,14 +188,20 @@ def select_pages(q, summaries, kv_indices, kv_indptr, kv_last_page_len, topk: in
     Hkv = summaries.shape[1]
     if q.dtype != summaries.dtype:
         raise TypeError("q and summaries must share a dtype")
-    if kv_indptr.numel() - 1 != B or summaries.shape[0] < B:
-        raise ValueError("batch mismatch between q, kv_indptr and summaries")
+    if _batch_of(kv_indptr, view) != B:
+        raise ValueError("batch mismatch between q and kv_indptr")
+    width = topk + 1 if view is None else view.row_width(topk)
     if out is None:
-        out = torch.empty(B, Hkv, topk + 1, dtype=torch.int32, device=q.device)
+        out = torch.empty(B, Hkv, width, dtype=torch.int32, device=q.device)
+    elif out.shape[-1] < width:
+        raise ValueError(f"select_pages: output rows must hold {width} entries")
+    if out_logical is not None and out_logical.shape[-1] != out.shape[-1]:
+        raise ValueError("select_pages: out_logical must have the row width of out")
     shp = Shape(B, Hkv, Hq // Hkv, Dh, PAGE_SIZE, _dtype_code(q), num_pages)
-    check(_lib.load().ktk_select(_ptr(q), _ptr(summaries), summaries.shape[2], _ptr(kv_indices), _ptr(kv_indptr),
-                                 _ptr(kv_last_page_len), topk, _ptr(out), _ptr(out_logical), _ptr(out_scores),
-                                 ctypes.byref(shp), _ptr(status), _stream()))
+    vp, _keep = _view_ref(view)
+    check(_lib.load().ktk_select_v(_ptr(q), _ptr(summaries), summaries.shape[2], _ptr(kv_indices), _ptr(kv_indptr),
+                                   _ptr(kv_last_page_len), topk, vp, out.shape[-1], _ptr(out), _ptr(out_logical),
+                                   _ptr(out_scores), ctypes.byref(shp), _ptr(status), _stream()))
     _launched()
     return out
 
@@ -180,32 +232,38 @@ def _decode_args(q, kv_cache, max_entries, workspace, num_splits):
 
 
 def sparse_decode(q, kv_cache, sel_pages, kv_indptr, kv_last_page_len, sm_scale: Optional[float] = None,
-                  workspace=None, num_splits: int = 0, variant: int = 0, out=None, status=None):
+                  workspace=None, num_splits: int = 0, variant: int = 0, out=None, status=None, view=None,
+                  topk: Optional[int] = None):
     """Attention of q [B, Hq, D] over the pages listed in sel_pages [B, Hkv, topk+1].
 
     Replaces mylib::decode -> flashinfer BatchDecodeWithPagedKVCacheWrapper.run
     (benchmark/blocktopk_decoder.py:176-178).
     """
     _cuda(q, kv_cache, sel_pages, kv_indptr, kv_last_page_len, workspace, out, status)
-    topk = sel_pages.shape[-1] - 1
-    shp, num_splits = _decode_args(q, kv_cache, topk + 1, workspace, num_splits)
-    if sel_pages.dtype != torch.int32 or sel_pages.numel() != shp.batch * shp.num_kv_heads * (topk + 1):
-        raise ValueError("sel_pages must be int32 [B, Hkv, topk+1]")
+    width = sel_pages.shape[-1]
+    if topk is None:
+        if view is not None:
+            raise ValueError("sparse_decode: pass topk together with a view")
+        topk = width - 1
+    shp, num_splits = _decode_args(q, kv_cache, width, workspace, num_splits)
+    if sel_pages.dtype != torch.int32 or sel_pages.numel() != shp.batch * shp.num_kv_heads * width:
+        raise ValueError("sel_pages must be int32 [B, Hkv, row width]")
     if out is None:
         out = torch.empty_like(q)
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(q.shape[-1])
     wsb = 0 if workspace is None else workspace.numel() * workspace.element_size()
-    check(_lib.load().ktk_sparse_decode(_ptr(q), _ptr(kv_cache), _ptr(sel_pages), topk, _ptr(kv_indptr),
-                                        _ptr(kv_last_page_len), sm_scale, _ptr(out), _ptr(workspace), wsb,
-                                        num_splits, variant, ctypes.byref(shp), _ptr(status), _stream()))
+    vp, _keep = _view_ref(view)
+    check(_lib.load().ktk_sparse_decode_v(_ptr(q), _ptr(kv_cache), _ptr(sel_pages), topk, vp, width, _ptr(kv_indptr),
+                                          _ptr(kv_last_page_len), sm_scale, _ptr(out), _ptr(workspace), wsb,
+                                          num_splits, variant, ctypes.byref(shp), _ptr(status), _stream()))
     _launched(2 if num_splits > 1 else 1)
     return out
 
 
 def dense_decode(q, kv_cache, kv_indices, kv_indptr, kv_last_page_len, max_pages_per_seq: int,
                  sm_scale: Optional[float] = None, workspace=None, num_splits: int = 0, variant: int = 0,
-                 out=None, status=None):
+                 out=None, status=None, view=None):
     """Attention of q over every page of each sequence (benchmark/dense_decoder.py:168-170)."""
     _cuda(q, kv_cache, kv_indices, kv_indptr, kv_last_page_len, workspace, out, status)
     shp, num_splits = _decode_args(q, kv_cache, max_pages_per_seq, workspace, num_splits)
@@ -214,8 +272,9 @@ def dense_decode(q, kv_cache, kv_indices, kv_indptr, kv_last_page_len, max_pages
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(q.shape[-1])
     wsb = 0 if workspace is None else workspace.numel() * workspace.element_size()
-    check(_lib.load().ktk_dense_decode(_ptr(q), _ptr(kv_cache), _ptr(kv_indices), _ptr(kv_indptr),
-                                       _ptr(kv_last_page_len), max_pages_per_seq, sm_scale, _ptr(out),
+    vp, _keep = _view_ref(view)
+    check(_lib.load().ktk_dense_decode_v(_ptr(q), _ptr(kv_cache), _ptr(kv_indices), _ptr(kv_indptr),
+                                       _ptr(kv_last_page_len), vp, max_pages_per_seq, sm_scale, _ptr(out),
                                        _ptr(workspace), wsb, num_splits, variant, ctypes.byref(shp),
                                        _ptr(status), _stream()))
     return out

@@ -261,3 +261,171 @@ int ktko_decode(const void* q, const void* cache, const int32_t* entries, int to
     }
     return 0;
 }
+
+
+/* ------------------------------------------------------------------------------------------
+ * The same operations under a page view (sink_tokens, local_tokens) -- the LiteSys semantics of
+ * LiteSys/litesys/attention/sparsity_utils.py:24-47: logical page 0 holds the `sink` first tokens
+ * (sparsity_utils.py:24 `sink=4`), 16-token blocks are counted from the end of the sink (:33-37),
+ * the blocks whose tokens all lie more than `local` tokens behind the end are scored
+ * (`_n_dynamic`, :33), everything after them is always kept (`_local`, :34), and nothing is
+ * dropped while `_n_dynamic / 16 <= topk` (:27-32).  sink = 0, local = 1 is the benchmark view.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct { int n_pages, front, n_dyn, back, last; } page_split_t;
+
+static page_split_t page_split(const int32_t* kv_indptr, const int32_t* kv_last_page_len, int b, int sink, int local) {
+    page_split_t ps;
+    ps.n_pages = kv_indptr[b + 1] - kv_indptr[b];
+    ps.last = ps.n_pages > 0 ? kv_last_page_len[b] : P;
+    ps.front = (sink > 0 && ps.n_pages > 0) ? 1 : 0;
+    const int n_after = ps.n_pages - ps.front;
+    const int len_after = n_after > 0 ? (n_after - 1) * P + ps.last : 0;
+    const int dyn = len_after - local;
+    ps.n_dyn = dyn > 0 ? dyn / P : 0;
+    ps.back = n_after - ps.n_dyn;
+    return ps;
+}
+
+static int page_tokens(const page_split_t* ps, int logical, int sink) {
+    if (logical == ps->n_pages - 1) return ps->last;
+    if (logical == 0 && ps->front) return sink;
+    return P;
+}
+
+int ktko_summaries_v(const void* cache, void* summaries, int64_t summary_stride, const int32_t* kv_indices,
+                     const int32_t* kv_indptr, const int32_t* kv_last_page_len, int sink, int B, int Hkv, int dtype) {
+    for (int b = 0; b < B; ++b) {
+        const page_split_t ps = page_split(kv_indptr, kv_last_page_len, b, sink, 1);
+        const int beg = kv_indptr[b];
+        for (int p = 0; p < ps.n_pages; ++p) {
+            const int c = page_tokens(&ps, p, sink);
+            const int64_t page = kv_indices[beg + p];
+            for (int h = 0; h < Hkv; ++h)
+                for (int d = 0; d < D; ++d) {
+                    float acc = 0.0f;
+                    for (int t = 0; t < c; ++t) acc = acc + ld(cache, dtype, kv_row(page, 0, t, h, Hkv) + d);
+                    st(summaries, dtype, (((int64_t)b * Hkv + h) * summary_stride + p) * D + d, acc / (float)c);
+                }
+        }
+    }
+    return 0;
+}
+
+/* scores[b, h, logical page] for the scored pages front .. front + n_dyn - 1, same arithmetic as ktko_scores */
+int ktko_scores_v(const void* q, const void* summaries, int64_t summary_stride, const int32_t* kv_indptr,
+                  const int32_t* kv_last_page_len, int sink, int local, float* scores, int B, int Hkv, int G,
+                  int dtype) {
+    for (int bh = 0; bh < B * Hkv; ++bh) {
+        const int b = bh / Hkv, h = bh % Hkv;
+        const page_split_t ps = page_split(kv_indptr, kv_last_page_len, b, sink, local);
+        float qbar[D];
+        const float inv_g = 1.0f / (float)G;
+        for (int d = 0; d < D; ++d) {
+            float acc = 0.0f;
+            for (int g = 0; g < G; ++g) acc = acc + ld(q, dtype, (((int64_t)b * Hkv + h) * G + g) * D + d);
+            qbar[d] = acc * inv_g;
+        }
+        for (int r = 0; r < ps.n_dyn; ++r) {
+            const int64_t base = ((int64_t)bh * summary_stride + ps.front + r) * D;
+            float part[16];
+            for (int j = 0; j < 16; ++j) {
+                float acc = 0.0f;
+                for (int e = 0; e < 8; ++e) acc = fmaf(qbar[8 * j + e], ld(summaries, dtype, base + 8 * j + e), acc);
+                part[j] = acc;
+            }
+            for (int off = 8; off > 0; off >>= 1) {
+                float nxt[16];
+                for (int j = 0; j < 16; ++j) nxt[j] = part[j] + part[j ^ off];
+                memcpy(part, nxt, sizeof(part));
+            }
+            scores[(int64_t)bh * summary_stride + ps.front + r] = part[0] + 0.0f;
+        }
+    }
+    return 0;
+}
+
+/* rows of `row_width` ints: [sink page][picks, best first, ties to the lowest page][tail pages], then -1 */
+int ktko_select_v(const float* scores, int64_t summary_stride, const int32_t* kv_indices, const int32_t* kv_indptr,
+                  const int32_t* kv_last_page_len, int topk, int sink, int local, int row_width,
+                  int32_t* out_pages, int32_t* out_logical, int B, int Hkv) {
+    for (int bh = 0; bh < B * Hkv; ++bh) {
+        const int b = bh / Hkv;
+        const int beg = kv_indptr[b];
+        const page_split_t ps = page_split(kv_indptr, kv_last_page_len, b, sink, local);
+        int32_t* lo = out_logical + (int64_t)bh * row_width;
+        int32_t* ph = out_pages + (int64_t)bh * row_width;
+        for (int i = 0; i < row_width; ++i) { lo[i] = -1; ph[i] = -1; }
+        if (ps.n_pages <= 0) continue;
+        int cnt = 0;
+        if (ps.n_dyn <= topk) {
+            for (int p = 0; p < ps.n_pages; ++p) lo[cnt++] = p;
+        } else {
+            if (ps.front) lo[cnt++] = 0;
+            keyed* ks = (keyed*)malloc(sizeof(keyed) * (size_t)ps.n_dyn);
+            for (int r = 0; r < ps.n_dyn; ++r) {
+                ks[r].key = score_key(scores[(int64_t)bh * summary_stride + ps.front + r]);
+                ks[r].page = r;
+            }
+            qsort(ks, (size_t)ps.n_dyn, sizeof(keyed), keyed_cmp);
+            for (int i = 0; i < topk; ++i) lo[cnt++] = ps.front + ks[i].page;
+            free(ks);
+            for (int p = ps.front + ps.n_dyn; p < ps.n_pages; ++p) lo[cnt++] = p;
+        }
+        for (int i = 0; i < cnt; ++i) ph[i] = kv_indices[beg + lo[i]];
+    }
+    return 0;
+}
+
+/* attention over the listed pages (sparse: rows of row_width; dense: topk < 0, entries = kv_indices) */
+int ktko_decode_v(const void* q, const void* cache, const int32_t* entries, int topk, int sink, int local,
+                  int row_width, const int32_t* kv_indptr, const int32_t* kv_last_page_len, float sm_scale,
+                  float* out, int B, int Hkv, int G, int dtype) {
+#pragma omp parallel for schedule(dynamic)
+    for (int bh = 0; bh < B * Hkv; ++bh) {
+        const int b = bh / Hkv, h = bh % Hkv;
+        const page_split_t ps = page_split(kv_indptr, kv_last_page_len, b, sink, local);
+        float* ob = out + ((int64_t)bh * G) * D;
+        for (int i = 0; i < G * D; ++i) ob[i] = 0.0f;
+        if (ps.n_pages <= 0) continue;
+        const int32_t* list;
+        int cnt;
+        if (topk >= 0) {
+            cnt = ps.front + (ps.n_dyn < topk ? ps.n_dyn : topk) + ps.back;
+            list = entries + (int64_t)bh * row_width;
+        } else {
+            cnt = ps.n_pages;
+            list = entries + kv_indptr[b];
+        }
+        double* logit = (double*)malloc(sizeof(double) * (size_t)cnt * P);
+        for (int g = 0; g < G; ++g) {
+            const int64_t qoff = ((int64_t)bh * G + g) * D;
+            double mx = -INFINITY;
+            for (int e = 0; e < cnt; ++e) {
+                const int nt = (e == cnt - 1) ? ps.last : ((e == 0 && ps.front) ? sink : P);
+                for (int t = 0; t < nt; ++t) {
+                    const int64_t kr = kv_row(list[e], 0, t, h, Hkv);
+                    double acc = 0.0;
+                    for (int d = 0; d < D; ++d) acc += (double)ld(q, dtype, qoff + d) * (double)ld(cache, dtype, kr + d);
+                    acc *= (double)sm_scale;
+                    logit[e * P + t] = acc;
+                    if (acc > mx) mx = acc;
+                }
+            }
+            double den = 0.0;
+            double o[D];
+            for (int d = 0; d < D; ++d) o[d] = 0.0;
+            for (int e = 0; e < cnt; ++e) {
+                const int nt = (e == cnt - 1) ? ps.last : ((e == 0 && ps.front) ? sink : P);
+                for (int t = 0; t < nt; ++t) {
+                    const double w = exp(logit[e * P + t] - mx);
+                    den += w;
+                    const int64_t vr = kv_row(list[e], 1, t, h, Hkv);
+                    for (int d = 0; d < D; ++d) o[d] += w * (double)ld(cache, dtype, vr + d);
+                }
+            }
+            for (int d = 0; d < D; ++d) ob[g * D + d] = (float)(o[d] / den);
+        }
+        free(logit);
+    }
+    return 0;
+}

@@ -124,6 +124,52 @@ def decode(q, kv_cache, entries, topk: int, kv_indptr, kv_last_page_len, sm_scal
 
 
 # --------------------------------------------------------------------------------------
+# The same under a page view (sink_tokens, local_tokens): LiteSys semantics
+# --------------------------------------------------------------------------------------
+
+def back_max(local: int) -> int:
+    return 1 if local <= 1 else 1 + (local - 1 + P - 1) // P
+
+
+def row_width(topk: int, sink: int, local: int) -> int:
+    return (1 if sink > 0 else 0) + topk + back_max(local)
+
+
+def summaries_v(kv_cache, kv_indices, kv_indptr, kv_last_page_len, summary_stride: int, sink: int):
+    B = kv_indptr.numel() - 1
+    Hkv = kv_cache.shape[3]
+    out = torch.zeros(B, Hkv, summary_stride, D, dtype=kv_cache.dtype)
+    _lib().ktko_summaries_v(_p(kv_cache), _p(out), ctypes.c_int64(summary_stride), _i32(kv_indices),
+                            _i32(kv_indptr), _i32(kv_last_page_len), sink, B, Hkv, _dt(kv_cache))
+    return out
+
+
+def select_v(q, summ, kv_indices, kv_indptr, kv_last_page_len, topk: int, sink: int, local: int):
+    """(physical, logical, scores) under the view; rows are row_width(topk, sink, local) wide."""
+    B, Hq = q.shape[0], q.shape[1]
+    Hkv, stride = summ.shape[1], summ.shape[2]
+    sc = torch.full((B, Hkv, stride), float("nan"), dtype=torch.float32)
+    _lib().ktko_scores_v(_p(q), _p(summ), ctypes.c_int64(stride), _i32(kv_indptr), _i32(kv_last_page_len), sink,
+                         local, _p(sc), B, Hkv, Hq // Hkv, _dt(q))
+    w = row_width(topk, sink, local)
+    phys = torch.empty(B, Hkv, w, dtype=torch.int32)
+    logical = torch.empty(B, Hkv, w, dtype=torch.int32)
+    _lib().ktko_select_v(_p(sc), ctypes.c_int64(stride), _i32(kv_indices), _i32(kv_indptr), _i32(kv_last_page_len),
+                         topk, sink, local, w, _p(phys), _p(logical), B, Hkv)
+    return phys, logical, sc
+
+
+def decode_v(q, kv_cache, entries, topk: int, kv_indptr, kv_last_page_len, sm_scale: float, sink: int, local: int):
+    B, Hq = q.shape[0], q.shape[1]
+    Hkv = kv_cache.shape[3]
+    out = torch.empty(B, Hq, D, dtype=torch.float32)
+    w = entries.shape[-1] if topk >= 0 else 0
+    _lib().ktko_decode_v(_p(q), _p(kv_cache), _i32(entries), topk, sink, local, w, _i32(kv_indptr),
+                         _i32(kv_last_page_len), ctypes.c_float(sm_scale), _p(out), B, Hkv, Hq // Hkv, _dt(q))
+    return out
+
+
+# --------------------------------------------------------------------------------------
 # The reference's own PyTorch statements, on CPU tensors
 # --------------------------------------------------------------------------------------
 

@@ -29,6 +29,16 @@ CASES = {
 }
 
 
+# LiteSys semantics (sink of 4 tokens, `local` newest tokens always kept, 16-token blocks counted from
+# the end of the sink): name -> (seed, Hkv, G, lens, topk, local, dtype)
+SINK = 4
+LITESYS_CASES = {
+    "ls_fp32_local0": (2101, 2, 2, [100, 260, 53, 4, 3, 21, 68, 84], 4, 0, "float32"),
+    "ls_bf16_local7": (2392, 2, 4, [300, 1029, 77], 8, 7, "bfloat16"),
+    "ls_bf16_local64": (2113, 1, 4, [700, 400], 6, 64, "bfloat16"),
+}
+
+
 def _bf16_round(x: np.ndarray) -> np.ndarray:
     """Round fp32 to the nearest bf16-representable fp32 (ties to even)."""
     u = x.astype(np.float32).view(np.uint32).astype(np.uint64)
@@ -37,7 +47,11 @@ def _bf16_round(x: np.ndarray) -> np.ndarray:
 
 
 def make_case(name: str) -> dict:
-    seed, hkv, g, lens, topk, dtype = CASES[name]
+    local = None
+    if name in LITESYS_CASES:
+        seed, hkv, g, lens, topk, local, dtype = LITESYS_CASES[name]
+    else:
+        seed, hkv, g, lens, topk, dtype = CASES[name]
     rng = np.random.default_rng(seed)
     B, L = len(lens), max(lens)
     q = rng.standard_normal((B, hkv * g, D), dtype=np.float32)
@@ -52,4 +66,4 @@ def make_case(name: str) -> dict:
     for a in (q, k, v):
         h.update(np.ascontiguousarray(a).tobytes())
     return dict(name=name, seed=seed, Hkv=hkv, G=g, lens=np.asarray(lens, np.int32), topk=topk, dtype=dtype,
-                q=q, k=k, v=v, checksum=h.hexdigest())
+                q=q, k=k, v=v, checksum=h.hexdigest(), local=local, sink=SINK if local is not None else 0)

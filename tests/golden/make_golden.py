@@ -29,7 +29,7 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE))
-from cases import CASES, D, P, make_case  # noqa: E402
+from cases import CASES, LITESYS_CASES, SINK, D, P, make_case  # noqa: E402
 
 
 def run_reference(ref_root: str, case: dict) -> dict:
@@ -88,6 +88,66 @@ def run_reference(ref_root: str, case: dict) -> dict:
     return dict(out=out.float().numpy().reshape(B, hq, D), kept=kept, margin=margin)
 
 
+def run_reference_litesys(ref_root: str, case: dict) -> dict:
+    """The LiteSys decode chain exactly as BatchKVManager.decode runs it (batch_cache.py:154-168):
+    qk -> attn_logits_processor(**preprocess_sparse_args(attn_block_topk, attn_local, attn_block_size))
+    -> softmax -> sv, for a layer that is not in attn_layer_skip.  Defaults of the reference: sink = 4."""
+    sys.path.insert(0, os.path.join(ref_root, "LiteSys"))
+    from litesys.attention.cache_utils import qk, softmax, sv
+    from litesys.attention.sparsity_utils import attn_logits_processor, preprocess_sparse_args
+
+    hkv, g, topk, local = case["Hkv"], case["G"], case["topk"], case["local"]
+    hq = hkv * g
+    lens = torch.from_numpy(case["lens"])
+    B, L = len(lens), int(lens.max())
+    max_len = (L + 127) // 128 * 128
+    k_cache = torch.zeros(B, hkv, max_len, D)
+    v_cache = torch.zeros(B, hkv, max_len, D)
+    k_cache[:, :, :L] = torch.from_numpy(case["k"])
+    v_cache[:, :, :L] = torch.from_numpy(case["v"])
+    query = torch.from_numpy(case["q"]).view(B, hq, 1, D)
+    batch_idx = torch.arange(B, dtype=torch.long)
+    offset = lens.to(torch.int32)
+    logits = torch.full((B, hq, max_len), float("-inf"), dtype=torch.float32)
+    out_buf = torch.zeros(B, hq, (max_len + 127) // 128, D, dtype=torch.float32)
+    kwargs = preprocess_sparse_args(attn_topk=None, attn_block_topk=topk, attn_local=local, attn_block_size=P)
+
+    qk(query=query, key=k_cache, batch_idx=batch_idx, offset=offset, logits_buffer=logits, BLOCK_SEQ=128)
+    dense_logits = logits.clone()
+    logits = attn_logits_processor(logits, offset, hq, hkv, 1, **kwargs)
+    masked = logits.clone()
+    softmax(logits, batch_idx, offset)
+    out = sv(value=v_cache, batch_idx=batch_idx, offset=offset, logits_buffer=logits, output_buffer=out_buf,
+             BLOCK_SEQ=128)
+
+    kept = np.full((B, hkv, topk), -1, np.int32)
+    margin = np.full((B, hkv), np.inf, np.float64)
+    n_full = (SINK + local + topk * P + P - 1) // P * P          # sparsity_utils.py:27-28
+    for b in range(B):
+        n = int(lens[b])
+        n_dyn = max(0, n - local - SINK) // P
+        for h in range(hkv):
+            fin = torch.isfinite(masked[b, h * g, SINK: SINK + n_dyn * P]).view(n_dyn, P)
+            assert bool((fin.all(1) | (~fin).all(1)).all()), "a block is partly masked"
+            blocks = torch.nonzero(fin[:, 0]).flatten().numpy() if n_dyn else np.zeros(0, np.int64)
+            assert bool(torch.isfinite(masked[b, h * g, :min(SINK, n)]).all())           # the sink is kept
+            assert bool(torch.isfinite(masked[b, h * g, SINK + n_dyn * P: n]).all())     # so is the tail
+            if n > n_full:
+                assert len(blocks) == topk, (b, h, len(blocks))
+                kept[b, h] = np.sort(blocks)
+                sc = dense_logits[b, h * g:(h + 1) * g, SINK: SINK + n_dyn * P].double().mean(0).view(n_dyn, P).mean(1)
+                srt = torch.sort(sc, descending=True).values
+                if n_dyn > topk:
+                    margin[b, h] = float((srt[topk - 1] - srt[topk]) / (srt[0] - srt[-1]))
+            else:
+                assert len(blocks) == n_dyn
+                kept[b, h, :min(n_dyn, topk)] = blocks[:topk]
+                assert n_dyn <= topk
+    need = 2e-2 if case["dtype"] == "bfloat16" else 1e-4
+    assert margin.min() > need, f"near tie in case {case['name']}: margin {margin.min():.3g}; change the seed"
+    return dict(out=out.float().numpy().reshape(B, hq, D), kept=kept, margin=margin)
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     for name in CASES:
@@ -96,6 +156,13 @@ def main():
         np.savez_compressed(HERE / f"{name}.npz", out=res["out"], kept=res["kept"], margin=res["margin"],
                             lens=case["lens"], topk=case["topk"], Hkv=case["Hkv"], G=case["G"],
                             checksum=case["checksum"], dtype=case["dtype"])
+        print(f"{name}: out {res['out'].shape} min margin {res['margin'].min():.3g}")
+    for name in LITESYS_CASES:
+        case = make_case(name)
+        res = run_reference_litesys(ref_root, case)
+        np.savez_compressed(HERE / f"{name}.npz", out=res["out"], kept=res["kept"], margin=res["margin"],
+                            lens=case["lens"], topk=case["topk"], Hkv=case["Hkv"], G=case["G"], local=case["local"],
+                            sink=SINK, checksum=case["checksum"], dtype=case["dtype"])
         print(f"{name}: out {res['out'].shape} min margin {res['margin'].min():.3g}")
 
 

@@ -6,7 +6,7 @@ from pathlib import Path
 import numpy as np
 import torch
 
-from golden.cases import CASES, D, P, make_case  # noqa: F401
+from golden.cases import CASES, LITESYS_CASES, SINK, D, P, make_case  # noqa: F401
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
@@ -15,7 +15,7 @@ def torch_dtype(name: str):
     return torch.bfloat16 if name == "bfloat16" else torch.float32
 
 
-def paged_state(k, v, lens, dtype, seed=0, extra_pages=7, summary_stride=None, fill=None):
+def paged_state(k, v, lens, dtype, seed=0, extra_pages=7, summary_stride=None, fill=None, sink=0):
     """Scatter contiguous histories k, v [B, Hkv, L, D] (fp32 numpy/torch) into a paged cache.
 
     Returns dict(kv_cache [N,2,P,Hkv,D], kv_indices, kv_indptr, kv_last_page_len, page_table list,
@@ -26,7 +26,20 @@ def paged_state(k, v, lens, dtype, seed=0, extra_pages=7, summary_stride=None, f
     v = torch.as_tensor(v)
     lens = [int(x) for x in lens]
     B, Hkv = k.shape[0], k.shape[1]
-    npages = [(n + P - 1) // P for n in lens]
+    # with a sink, logical page 0 holds tokens [0, sink) and page p >= 1 tokens [sink + 16(p-1), sink + 16p)
+    def n_pages_of(n):
+        if sink == 0:
+            return (n + P - 1) // P
+        return 0 if n == 0 else (1 if n <= sink else 1 + (n - sink + P - 1) // P)
+
+    def span(p, n):
+        if sink == 0:
+            return p * P, min(n, (p + 1) * P)
+        if p == 0:
+            return 0, min(n, sink)
+        return sink + (p - 1) * P, min(n, sink + p * P)
+
+    npages = [n_pages_of(n) for n in lens]
     total = sum(npages) + extra_pages
     g = torch.Generator().manual_seed(seed)
     perm = torch.randperm(total, generator=g).tolist()
@@ -38,9 +51,9 @@ def paged_state(k, v, lens, dtype, seed=0, extra_pages=7, summary_stride=None, f
         cur += npages[b]
         indices += pages
         indptr.append(len(indices))
-        last.append(lens[b] - (npages[b] - 1) * P if npages[b] else 0)
+        last.append(lens[b] - span(npages[b] - 1, lens[b])[0] if npages[b] else 0)
         for p, phys in enumerate(pages):
-            t0, t1 = p * P, min(lens[b], (p + 1) * P)
+            t0, t1 = span(p, lens[b])
             cache[phys, 0, : t1 - t0] = k[b, :, t0:t1].permute(1, 0, 2)
             cache[phys, 1, : t1 - t0] = v[b, :, t0:t1].permute(1, 0, 2)
     if summary_stride is None:
@@ -58,7 +71,7 @@ def case_state(name: str, seed=0):
     """Golden case -> (case dict, paged state, q tensor in the case dtype)."""
     case = make_case(name)
     dt = torch_dtype(case["dtype"])
-    st = paged_state(case["k"], case["v"], case["lens"], dt, seed=seed)
+    st = paged_state(case["k"], case["v"], case["lens"], dt, seed=seed, sink=case["sink"])
     q = torch.from_numpy(case["q"]).to(dt)
     return case, st, q
 

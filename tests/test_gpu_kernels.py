@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import CASES, P, case_state, load_golden, paged_state, random_case, to_dev
+from helpers import CASES, LITESYS_CASES, P, SINK, case_state, load_golden, paged_state, random_case, to_dev
 from oracle import oracle
 
 pytestmark = pytest.mark.gpu
@@ -289,6 +289,120 @@ def test_large_logits_do_not_overflow(cuda_device):
                                d["kv_last_page_len"], 25, num_splits=1, variant=variant)
         assert torch.isfinite(out).all()
         np.testing.assert_allclose(out.float().cpu().numpy(), ref.numpy(), rtol=3e-2, atol=3e-2)
+
+
+# ---------------------------------------------------------------- page views (LiteSys semantics)
+
+def _view_roundtrip(ops, device, q, st, topk, sink, local, gold_out=None, scattered=False):
+    """build summaries, select and decode under a view on the GPU; compare with the oracle under the same view"""
+    dtype = q.dtype
+    B, Hq = q.shape[:2]
+    Hkv = st["kv_cache"].shape[3]
+    summ = oracle.summaries_v(st["kv_cache"], st["kv_indices"], st["kv_indptr"], st["kv_last_page_len"],
+                              st["summary_stride"], sink)
+    phys, logical, sc = oracle.select_v(q, summ, st["kv_indices"], st["kv_indptr"], st["kv_last_page_len"], topk,
+                                        sink, local)
+    ref = oracle.decode_v(q, st["kv_cache"], phys, topk, st["kv_indptr"], st["kv_last_page_len"],
+                          oracle.default_scale(), sink, local)
+    ref_dense = oracle.decode_v(q, st["kv_cache"], st["kv_indices"], -1, st["kv_indptr"], st["kv_last_page_len"],
+                                oracle.default_scale(), sink, local)
+    d = to_dev(st, device)
+    indptr, rows = d["kv_indptr"], B
+    page_count = slot_index = None
+    if scattered:
+        # lists given by (start, count), summaries kept in other rows than the batch order
+        page_count = (d["kv_indptr"][1:] - d["kv_indptr"][:-1]).contiguous()
+        indptr = d["kv_indptr"][:-1].contiguous()
+        perm = torch.randperm(B + 3, generator=torch.Generator().manual_seed(5))[:B]
+        slot_index = perm.to(torch.int32).to(device)
+        rows = B + 3
+    view = ops.PageView(sink, local, page_count, slot_index)
+    summ_g = torch.zeros(rows, Hkv, st["summary_stride"], 128, dtype=dtype, device=device)
+    status = ops.new_status(device)
+    ops.build_summaries(d["kv_cache"], summ_g, d["kv_indices"], indptr, d["kv_last_page_len"], status=status,
+                        view=view)
+    got_summ = summ_g.cpu() if slot_index is None else summ_g.cpu()[slot_index.cpu().long()]
+    for b, npg in enumerate(st["npages"]):
+        assert torch.equal(_bits(got_summ[b, :, :npg]), _bits(summ[b, :, :npg]))
+    width = view.row_width(topk)
+    assert width == phys.shape[-1]
+    out_l = torch.empty(B, Hkv, width, dtype=torch.int32, device=device)
+    sel = ops.select_pages(q.to(device), summ_g, d["kv_indices"], indptr, d["kv_last_page_len"], topk,
+                           st["num_pages"], out_logical=out_l, status=status, view=view)
+    ops.raise_on_status(status)
+    assert torch.equal(out_l.cpu(), logical)
+    assert torch.equal(sel.cpu(), phys)
+    tol = _tol(dtype)
+    for variant in VARIANTS[dtype]:
+        for splits in (1, 3):
+            ws = torch.empty(max(ops.decode_workspace_bytes(B, Hkv, Hq // Hkv, splits), 1), dtype=torch.uint8,
+                             device=device)
+            out = ops.sparse_decode(q.to(device), d["kv_cache"], sel, indptr, d["kv_last_page_len"], workspace=ws,
+                                    num_splits=splits, variant=variant, view=view, topk=topk, status=status)
+            np.testing.assert_allclose(out.float().cpu().numpy(), ref.numpy(), rtol=tol, atol=tol)
+            if gold_out is not None:
+                np.testing.assert_allclose(out.float().cpu().numpy(), gold_out, rtol=tol, atol=tol)
+            dn = ops.dense_decode(q.to(device), d["kv_cache"], d["kv_indices"], indptr, d["kv_last_page_len"],
+                                  max(st["npages"]), workspace=ws, num_splits=splits, variant=variant, view=view,
+                                  status=status)
+            np.testing.assert_allclose(dn.float().cpu().numpy(), ref_dense.numpy(), rtol=tol, atol=tol)
+    ops.raise_on_status(status)
+
+
+@pytest.mark.parametrize("scattered", [False, True])
+@pytest.mark.parametrize("name", sorted(LITESYS_CASES))
+def test_view_kernels_on_litesys_golden_cases(cuda_device, name, scattered):
+    ops = _ops()
+    case, st, q = case_state(name, seed=6)
+    gold = load_golden(name)
+    _view_roundtrip(ops, cuda_device, q, st, case["topk"], SINK, case["local"], gold_out=gold["out"],
+                    scattered=scattered)
+
+
+@pytest.mark.parametrize("dtype,G,Hkv,topk,sink,local,lens", [
+    (torch.bfloat16, 8, 1, 32, 4, 100, [5000, 3, 4, 5, 20, 21, 1234]),
+    (torch.bfloat16, 4, 2, 16, 4, 0, [4 + 16 * 40, 4 + 16 * 17 + 1, 4 + 16 * 16]),     # lengths that end on a block edge
+    (torch.float32, 2, 2, 8, 7, 33, [700, 8, 300]),
+    (torch.bfloat16, 4, 1, 64, 0, 50, [2049, 100]),                                 # no sink, wider always-kept tail
+])
+def test_view_kernels_random(cuda_device, dtype, G, Hkv, topk, sink, local, lens):
+    ops = _ops()
+    q, k, v = random_case(31, len(lens), Hkv, G, lens, dtype)
+    st = paged_state(k, v, lens, dtype, seed=10, sink=sink)
+    _view_roundtrip(ops, cuda_device, q, st, topk, sink, local)
+
+
+def test_view_append_maintains_block_summaries(cuda_device):
+    # tokens appended one at a time through the sink page and the pages behind it
+    ops = _ops()
+    dtype = torch.bfloat16
+    B, Hkv, sink, steps = 3, 2, 4, 41
+    per = 1 + (steps - sink + P - 1) // P
+    total = B * per + 2
+    table = torch.randperm(total, generator=torch.Generator().manual_seed(3))[: B * per].view(B, per).to(torch.int32)
+    cache = torch.zeros(total, 2, P, Hkv, 128, dtype=dtype, device=cuda_device)
+    summ = torch.zeros(B, Hkv, per, 128, dtype=dtype, device=cuda_device)
+    view = ops.PageView(sink, 0)
+    ks, vs = [], []
+    status = ops.new_status(cuda_device)
+    for s_ in range(steps):
+        n = s_ + 1
+        npg = 1 if n <= sink else 1 + (n - sink + P - 1) // P
+        last = n if n <= sink else (n - sink - 1) % P + 1
+        indices = table[:, :npg].contiguous().view(-1).to(cuda_device)
+        indptr = (torch.arange(B + 1) * npg).to(torch.int32).to(cuda_device)
+        lastt = torch.full((B,), last, dtype=torch.int32, device=cuda_device)
+        k = torch.randn(B, Hkv, 128).to(dtype)
+        v = torch.randn(B, Hkv, 128).to(dtype)
+        ks.append(k); vs.append(v)
+        ops.append_kv(k.to(cuda_device), v.to(cuda_device), cache, summ, indices, indptr, lastt, status=status,
+                      view=view)
+    ops.raise_on_status(status)
+    kk = torch.stack(ks, 2).float()            # [B, Hkv, steps, D]
+    vv = torch.stack(vs, 2).float()
+    st = paged_state(kk, vv, [steps] * B, dtype, seed=0, sink=sink, summary_stride=per)
+    want = oracle.summaries_v(st["kv_cache"], st["kv_indices"], st["kv_indptr"], st["kv_last_page_len"], per, sink)
+    assert torch.equal(_bits(summ.cpu()), _bits(want))
 
 
 # ---------------------------------------------------------------- small ops

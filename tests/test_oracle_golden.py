@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import CASES, P, case_state, load_golden
+from helpers import CASES, LITESYS_CASES, P, SINK, case_state, load_golden
 from oracle import oracle
 
 
@@ -120,3 +120,46 @@ def test_reference_torch_lines_agree_with_oracle_selection():
     out = oracle.decode(q, st["kv_cache"], phys, topk, st["kv_indptr"], st["kv_last_page_len"],
                         oracle.default_scale())
     assert torch.allclose(out_ref, out, atol=1e-5, rtol=1e-5)
+
+
+# ---------------------------------------------------------------- LiteSys semantics (sink 4, local window)
+
+@pytest.mark.parametrize("name", sorted(LITESYS_CASES))
+def test_oracle_view_reproduces_litesys_chain(name):
+    """qk -> attn_logits_processor(blockwise top-k) -> softmax -> sv of the reference, run on CPU when the
+    fixtures were made, against the oracle under the view (sink_tokens=4, local_tokens=attn_local)."""
+    case, st, q = case_state(name, seed=13)
+    gold = load_golden(name)
+    assert str(gold["checksum"]) == case["checksum"]
+    topk, local = int(gold["topk"]), int(gold["local"])
+    summ = oracle.summaries_v(st["kv_cache"], st["kv_indices"], st["kv_indptr"], st["kv_last_page_len"],
+                              st["summary_stride"], SINK)
+    phys, logical, _ = oracle.select_v(q, summ, st["kv_indices"], st["kv_indptr"], st["kv_last_page_len"], topk,
+                                       SINK, local)
+    B, Hkv = logical.shape[:2]
+    for b in range(B):
+        n = int(case["lens"][b])
+        n_dyn = max(0, n - local - SINK) // P
+        for h in range(Hkv):
+            row = logical[b, h][logical[b, h] >= 0].numpy()
+            assert row[0] == 0                                   # the sink page
+            picks = row[(row >= 1) & (row < 1 + n_dyn)] - 1      # scored pages <-> reference blocks
+            ref = gold["kept"][b, h][gold["kept"][b, h] >= 0]
+            assert np.array_equal(np.sort(picks), ref), (name, b, h)
+            tail = row[row >= 1 + n_dyn]
+            assert np.array_equal(tail, np.arange(1 + n_dyn, st["npages"][b]))   # everything after them
+    out = oracle.decode_v(q, st["kv_cache"], phys, topk, st["kv_indptr"], st["kv_last_page_len"],
+                          oracle.default_scale(), SINK, local)
+    assert np.abs(out.numpy() - gold["out"]).max() < 5e-5
+    dense = oracle.decode_v(q, st["kv_cache"], st["kv_indices"], -1, st["kv_indptr"], st["kv_last_page_len"],
+                            oracle.default_scale(), SINK, local)
+    assert torch.isfinite(dense).all()
+
+
+def test_view_defaults_equal_plain_oracle():
+    case, st, q = case_state("ragged_fp32", seed=2)
+    summ = oracle.summaries(st["kv_cache"], st["kv_indices"], st["kv_indptr"], st["kv_last_page_len"],
+                            st["summary_stride"])
+    a, la = oracle.select(q, summ, st["kv_indices"], st["kv_indptr"], case["topk"])
+    b, lb, _ = oracle.select_v(q, summ, st["kv_indices"], st["kv_indptr"], st["kv_last_page_len"], case["topk"], 0, 1)
+    assert torch.equal(a, b) and torch.equal(la, lb)
