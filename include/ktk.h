@@ -241,6 +241,27 @@ KTK_API int ktk_rmsnorm(const void* x, const void* w, float eps, void* out, int6
                 int32_t cols, int32_t dtype, void* stream);
 
 /*
+ * Residual add + RMSNorm in one pass: s = x + residual (rounded to dtype, stored to out_sum when
+ * that is non-null), out_norm = s * rsqrt(mean(s^2) + eps) * w.  residual may be null (plain RMSNorm).
+ * cols a multiple of 8, at most 8192; pointers 16-byte aligned.
+ * Replaces `hidden_states = residual + hidden_states` followed by mylib::layer_norm
+ * (benchmark/blocktopk_decoder.py:229-231); flashinfer's own fused form is
+ * benchmark/model_utils.py:27-41 (fused_add_rmsnorm, unused by the reference layer).
+ */
+KTK_API int ktk_add_rmsnorm(const void* x, const void* residual, const void* w, float eps, void* out_sum,
+                            void* out_norm, int64_t rows, int32_t cols, int32_t dtype, void* stream);
+
+/*
+ * Split of the fused QKV projection with q-norm and k-norm applied on the way:
+ * proj [B, (Hq + 2 Hkv) * 128] -> q [B, Hq, 128] (RMSNorm, wq), k [B, Hkv, 128] (RMSNorm, wk),
+ * v [B, Hkv, 128] (copied).  Replaces the split / view / contiguous / mylib::qk_norm sequence of
+ * benchmark/blocktopk_decoder.py:197-207.
+ */
+KTK_API int ktk_qkv_norm(const void* proj, const void* wq, const void* wk, float eps, void* q, void* k,
+                         void* v, int64_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t dtype,
+                         void* stream);
+
+/*
  * SwiGLU gate: out = silu(gate) * up, elementwise, fp32 arithmetic.
  * Replaces the activation + multiply of benchmark/blocktopk_decoder.py:235-236.
  */

@@ -70,6 +70,10 @@ _SIGNATURES = {
                                      c_void_p, c_void_p, c_size_t, c_int32, c_int32, POINTER(Shape), _i32p,
                                      c_void_p]),
     "ktk_rmsnorm": (c_int32, [c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int32, c_int32, c_void_p]),
+    "ktk_add_rmsnorm": (c_int32, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int64, c_int32,
+                                  c_int32, c_void_p]),
+    "ktk_qkv_norm": (c_int32, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int64, c_int32,
+                               c_int32, c_int32, c_void_p]),
     "ktk_silu_mul": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
 }
 

@@ -5,6 +5,8 @@
 
 namespace ktk {
 
+int silu_mul_vectorised(const void* gate, const void* up, void* out, int64_t n, int dtype, cudaStream_t st);
+
 // One CTA per (sequence, kv head), one thread per head-dim element.
 // Writes the new key/value at (last page, last slot) and rewrites that page's
 // summary: fp32 sum over slots 0..c-1 in slot order, divided by c, rounded to T.
@@ -291,6 +293,8 @@ extern "C" int ktk_silu_mul(const void* gate, const void* up, void* out, int64_t
     if (n == 0) return KTK_OK;
     if (!gate || !up || !out) { set_error("ktk_silu_mul: null pointer argument"); return KTK_ERR_ARG; }
     cudaStream_t st = (cudaStream_t)stream;
+    if (n % 8 == 0 && ((((uintptr_t)gate | (uintptr_t)up | (uintptr_t)out) & 15u) == 0))
+        return silu_mul_vectorised(gate, up, out, n, dtype, st);
     int64_t blocks = (n + 255) / 256;
     const int64_t cap = (int64_t)sm_count() * 16;
     if (blocks > cap) blocks = cap;

@@ -27,6 +27,10 @@ template <> struct SelStage<__nv_bfloat16> { static constexpr int kRows = 24; };
 template <> struct SelStage<float> { static constexpr int kRows = 16; };           // 8 KiB
 constexpr int kSelCtasPerSm = 3;
 constexpr int kMaxTopk = 1024;
+constexpr int kSelBins = 2048;                      // first radix digit: the top 11 bits of a key
+constexpr int kSelBinShift = 21;
+constexpr int kCandMax = 512;                       // pages of the threshold bin ranked directly
+static_assert(kSelBins == 8 * kSelThreads, "eight bins per thread in the digit search");
 static_assert(kSelStages % kSelWarps == 0, "a stage must belong to one consumer warp");
 
 __device__ __forceinline__ unsigned long long composite(uint32_t key, int page) {
@@ -103,8 +107,10 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
     __shared__ __align__(8) uint64_t full_bar[kSelStages];
     __shared__ __align__(8) uint64_t empty_bar[kSelStages];
     __shared__ float qbar[kHeadDim];
-    __shared__ unsigned int hist[256];
-    __shared__ int s_digit, s_greater, s_bincount, s_count;
+    __shared__ unsigned int hist[kSelBins];              // first radix digit, filled while scoring
+    __shared__ unsigned long long candc[kCandMax];       // composites of the threshold bin
+    __shared__ unsigned int s_wsum[kSelWarps];
+    __shared__ int s_digit, s_greater, s_bincount, s_count, s_ccount;
     __shared__ int abort_flag, issued_total;
 
     constexpr int kRowBytes = kHeadDim * (int)sizeof(T);
@@ -174,8 +180,9 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
             }
 
             if (it.scan) {
-                hist[tid] = 0;
-                if (tid == 0) s_count = 0;
+#pragma unroll
+                for (int i = 0; i < kSelBins / kSelThreads; ++i) hist[tid + i * kSelThreads] = 0;
+                if (tid == 0) { s_count = 0; s_ccount = 0; }
                 if (tid < kHeadDim) {
                     const T* qp = q + ((int64_t)b * Hkv * G + (int64_t)h * G) * kHeadDim + tid;
                     float acc = 0.0f;
@@ -235,7 +242,7 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
                         if (j4 == 0 && r < it.n_scored) {
                             const uint32_t key = score_to_key(acc);
                             keys[r] = key;
-                            if (it.need_select) atomicAdd(&hist[key >> 24], 1u);
+                            if (it.need_select) atomicAdd(&hist[key >> kSelBinShift], 1u);
                             if (score_row) score_row[r] = acc;
                         }
                     }
@@ -262,12 +269,65 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
                 continue;
             }
 
-            // ---- radix select of the topk-th largest 48-bit composite, 8 bits per pass; the
-            //      histogram of the first pass (top byte of the key) was filled while scoring ----
-            unsigned long long prefix = 0, mask = 0;
-            int need = topk;
-            for (int shift = 40; shift >= 0; shift -= 8) {
-                if (shift != 40) {
+            // ---- the k-th largest 48-bit composite.  First digit: the top 11 bits of the key (sign,
+            //      exponent, two mantissa bits), histogrammed while scoring.  Thread t owns bins
+            //      2047-8t .. 2040-8t; a block-wide scan finds the bin in which the k-th largest falls.
+            {
+                unsigned cnt[8];
+                unsigned mine = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    cnt[j] = hist[kSelBins - 1 - 8 * tid - j];
+                    mine += cnt[j];
+                }
+                unsigned incl = mine;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const unsigned up = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += up;
+                }
+                if (lane == 31) s_wsum[warp] = incl;
+                consumer_sync();
+                unsigned running = incl - mine;   // elements in strictly larger bins
+                for (int w = 0; w < warp; ++w) running += s_wsum[w];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (running < (unsigned)topk && (unsigned)topk <= running + cnt[j]) {
+                        s_digit = kSelBins - 1 - 8 * tid - j;
+                        s_greater = (int)running;
+                        s_bincount = (int)cnt[j];
+                    }
+                    running += cnt[j];
+                }
+                consumer_sync();
+            }
+            const int digit = s_digit, greater = s_greater, bincount = s_bincount;
+            if (bincount <= kCandMax) {
+                // ---- usual case: pages with a larger digit are winners; the few pages of the threshold
+                //      bin are ranked among themselves and the best (topk - greater) of them join.
+                for (int i = tid; i < it.n_scored; i += kSelThreads) {
+                    const uint32_t key = keys[i];
+                    const int dg = (int)(key >> kSelBinShift);
+                    if (dg > digit) {
+                        sel[atomicAdd(&s_count, 1)] = composite(key, i);
+                    } else if (dg == digit) {
+                        candc[atomicAdd(&s_ccount, 1)] = composite(key, i);
+                    }
+                }
+                consumer_sync();
+                const int need = topk - greater;
+                for (int c = tid; c < bincount; c += kSelThreads) {
+                    const unsigned long long mine = candc[c];
+                    int rank = 0;
+                    for (int j = 0; j < bincount; ++j) rank += (candc[j] > mine) ? 1 : 0;
+                    if (rank < need) sel[greater + rank] = mine;
+                }
+            } else {
+                // ---- many pages share the threshold bin (near-equal scores): radix select on the whole
+                //      composite, 8 bits per pass ----
+                unsigned long long prefix = 0, mask = 0;
+                int need = topk;
+                for (int shift = 40; shift >= 0; shift -= 8) {
                     hist[tid] = 0;
                     consumer_sync();
                     for (int i = tid; i < it.n_scored; i += kSelThreads) {
@@ -275,68 +335,96 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
                         if ((c & mask) == prefix) atomicAdd(&hist[(unsigned)(c >> shift) & 255u], 1u);
                     }
                     consumer_sync();
-                }
-                if (warp == 0) {
-                    // lane l owns bins 255-8l .. 248-8l, walked from the largest digit down
-                    unsigned cnt[8];
-                    unsigned mine = 0;
+                    if (warp == 0) {
+                        // lane l owns bins 255-8l .. 248-8l, walked from the largest digit down
+                        unsigned cnt[8];
+                        unsigned mine = 0;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        cnt[j] = hist[255 - 8 * lane - j];
-                        mine += cnt[j];
-                    }
-                    unsigned incl = mine;
-#pragma unroll
-                    for (int o = 1; o < 32; o <<= 1) {
-                        const unsigned up = __shfl_up_sync(0xffffffffu, incl, o);
-                        if (lane >= o) incl += up;
-                    }
-                    unsigned running = incl - mine;   // elements in strictly larger bins
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        if (running < (unsigned)need && (unsigned)need <= running + cnt[j]) {
-                            s_digit = 255 - 8 * lane - j;
-                            s_greater = (int)running;
-                            s_bincount = (int)cnt[j];
+                        for (int j = 0; j < 8; ++j) {
+                            cnt[j] = hist[255 - 8 * lane - j];
+                            mine += cnt[j];
                         }
-                        running += cnt[j];
+                        unsigned incl = mine;
+#pragma unroll
+                        for (int o = 1; o < 32; o <<= 1) {
+                            const unsigned up = __shfl_up_sync(0xffffffffu, incl, o);
+                            if (lane >= o) incl += up;
+                        }
+                        unsigned running = incl - mine;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if (running < (unsigned)need && (unsigned)need <= running + cnt[j]) {
+                                s_digit = 255 - 8 * lane - j;
+                                s_greater = (int)running;
+                                s_bincount = (int)cnt[j];
+                            }
+                            running += cnt[j];
+                        }
                     }
+                    consumer_sync();
+                    need -= s_greater;
+                    prefix |= (unsigned long long)s_digit << shift;
+                    mask |= 0xFFull << shift;
+                    if (s_bincount == need) break;   // the whole bin is taken: threshold found
                 }
-                consumer_sync();
-                need -= s_greater;
-                prefix |= (unsigned long long)s_digit << shift;
-                mask |= 0xFFull << shift;
-                if (s_bincount == need) break;   // the whole bin is taken: threshold found
-            }
-
-            // ---- gather the topk composites >= threshold, sort them descending ----
-            for (int i = tid; i < it.n_scored; i += kSelThreads) {
-                const unsigned long long c = composite(keys[i], i);
-                if ((c & mask) >= prefix) {
-                    const int pos = atomicAdd(&s_count, 1);
-                    if (pos < kp) sel[pos] = c;
+                for (int i = tid; i < it.n_scored; i += kSelThreads) {
+                    const unsigned long long c = composite(keys[i], i);
+                    if ((c & mask) >= prefix) {
+                        const int pos = atomicAdd(&s_count, 1);
+                        if (pos < kp) sel[pos] = c;
+                    }
                 }
             }
             for (int i = topk + tid; i < kp; i += kSelThreads) sel[i] = 0ull;
             consumer_sync();
-            for (int k2 = 2; k2 <= kp; k2 <<= 1) {
-                for (int j = k2 >> 1; j > 0; j >>= 1) {
-                    for (int i = tid; i < kp; i += kSelThreads) {
-                        const int ixj = i ^ j;
-                        if (ixj > i) {
-                            const unsigned long long a = sel[i], c = sel[ixj];
-                            const bool desc = (i & k2) == 0;
-                            if (desc ? (a < c) : (a > c)) { sel[i] = c; sel[ixj] = a; }
+
+            // ---- order the winners, best first, and write the row:
+            //      [sink page][picks][always-attended tail pages], then -1 ----
+            if (topk <= kSelThreads / 2) {
+                // the composites are distinct, so the number of larger ones is the position;
+                // two threads per winner, half of the comparisons each
+                const int e = tid >> 1, hf = tid & 1;
+                int rank = 0;
+                unsigned long long mine = 0ull;
+                if (e < topk) {
+                    mine = sel[e];
+                    const int j0 = hf ? (topk + 1) / 2 : 0, j1 = hf ? topk : (topk + 1) / 2;
+                    for (int j = j0; j < j1; ++j) rank += (sel[j] > mine) ? 1 : 0;
+                }
+                rank += __shfl_xor_sync(0xffffffffu, rank, 1);
+                if (e < topk && hf == 0) {
+                    const int logical = it.front + (int)(0xFFFFu - (unsigned)(mine & 0xFFFFull));
+                    const int phys = kv_indices[it.beg + logical];
+                    if (phys < 0 || phys >= num_pages) report(status, KTK_STATUS_BAD_PAGE);
+                    row_pages[it.front + rank] = phys;
+                    if (row_logical) row_logical[it.front + rank] = logical;
+                }
+            } else {
+                for (int k2 = 2; k2 <= kp; k2 <<= 1) {
+                    for (int j = k2 >> 1; j > 0; j >>= 1) {
+                        for (int i = tid; i < kp; i += kSelThreads) {
+                            const int ixj = i ^ j;
+                            if (ixj > i) {
+                                const unsigned long long a = sel[i], c = sel[ixj];
+                                const bool desc = (i & k2) == 0;
+                                if (desc ? (a < c) : (a > c)) { sel[i] = c; sel[ixj] = a; }
+                            }
                         }
+                        consumer_sync();
                     }
-                    consumer_sync();
+                }
+                for (int i = tid; i < topk; i += kSelThreads) {
+                    const int logical = it.front + (int)(0xFFFFu - (unsigned)(sel[i] & 0xFFFFull));
+                    const int phys = kv_indices[it.beg + logical];
+                    if (phys < 0 || phys >= num_pages) report(status, KTK_STATUS_BAD_PAGE);
+                    row_pages[it.front + i] = phys;
+                    if (row_logical) row_logical[it.front + i] = logical;
                 }
             }
             for (int i = tid; i < stride_out; i += kSelThreads) {
-                // [sink page][picks, best first][always-attended tail pages], then -1
+                if (i >= it.front && i < it.front + topk) continue;       // the picks, written above
                 int logical = -1, phys = -1;
                 if (i < it.front) logical = 0;
-                else if (i < it.front + topk) logical = it.front + (int)(0xFFFFu - (unsigned)(sel[i - it.front] & 0xFFFFull));
                 else if (i < it.front + topk + it.back) logical = it.front + it.n_scored + (i - it.front - topk);
                 if (logical >= 0) {
                     phys = kv_indices[it.beg + logical];

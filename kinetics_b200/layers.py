@@ -166,38 +166,31 @@ class _PagedDecoderLayer(nn.Module):
     @torch.inference_mode()
     def forward(self, hidden_states):
         self._bind()      # the torch ops find this layer's page state through its kv_cache
-        residual = hidden_states
-        hidden_states = torch.ops.mylib.layer_norm(hidden_states, self.input_layernorm_variance_epsilon,
-                                                   self.input_layernorm_weight)
         bsz, q_len, _ = hidden_states.size()
-        q_dim, kv_dim = self.head_dim * self.num_heads, self.head_dim * self.num_kv_heads
+        residual = hidden_states.reshape(bsz * q_len, self.dim)
+        # input RMSNorm (mylib::layer_norm of the reference, :192), 16-byte accesses
+        _, hidden_states = ops.add_rmsnorm(residual, None, self.input_layernorm_weight,
+                                           self.input_layernorm_variance_epsilon)
         proj = self.wqkv(hidden_states)
-        query_states, key_states, value_states = proj.split((q_dim, kv_dim, kv_dim), dim=-1)
-        query_states = query_states.reshape(bsz, q_len, self.num_heads, self.head_dim)
-        key_states = key_states.reshape(bsz, q_len, self.num_kv_heads, self.head_dim)
-        value_states = value_states.reshape(bsz, self.num_kv_heads, self.head_dim).contiguous()
-
-        query_states = torch.ops.mylib.qk_norm(query_states, self.qnorm_variance_epsilon, self.qnorm_weight)
-        key_states = torch.ops.mylib.qk_norm(key_states, self.knorm_variance_epsilon, self.knorm_weight)
-        query_states = query_states.reshape(bsz, self.num_heads, self.head_dim)
-        key_states = key_states.reshape(bsz, self.num_kv_heads, self.head_dim)
-
+        # split + q-norm + k-norm (:198-207) in one launch
+        query_states, key_states, value_states = ops.qkv_norm(proj, self.qnorm_weight, self.knorm_weight,
+                                                              self.qnorm_variance_epsilon, self.num_heads,
+                                                              self.num_kv_heads)
         if self.capture is not None:
             self.capture.update(q=query_states.clone(), k=key_states.clone(), v=value_states.clone())
         with self._timed("append"):
             torch.ops.mylib.update_kv(key_states, value_states, self.qkv_indptr, self.kv_cache,
                                       self.paged_kv_indices, self.full_kv_indptr, self.last_kv_lens)
         o = self._attention(query_states)
-        o = o.reshape(bsz, q_len, self.head_dim * self.num_heads)
+        o = o.reshape(bsz * q_len, self.head_dim * self.num_heads)
         hidden_states = self.wo(o)
         if self.process_group is not None:
             torch.distributed.all_reduce(hidden_states, group=self.process_group)
-        hidden_states = residual + hidden_states
-        residual = hidden_states
-        hidden_states = torch.ops.mylib.layer_norm(hidden_states, self.post_attention_layernorm_variance_epsilon,
-                                                   self.post_attention_layernorm_weight)
+        # residual add + post-attention RMSNorm (:229-231) in one pass
+        residual, hidden_states = ops.add_rmsnorm(hidden_states, residual, self.post_attention_layernorm_weight,
+                                                  self.post_attention_layernorm_variance_epsilon)
         hidden_states = self._mlp(hidden_states)
-        return residual + hidden_states
+        return (residual + hidden_states).view(bsz, q_len, self.dim)
 
     def _timed(self, name):
         return _EventPair(self.timers, name)

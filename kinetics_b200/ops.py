@@ -293,6 +293,37 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     return out
 
 
+def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], weight: torch.Tensor, eps: float):
+    """(x + residual, rmsnorm(x + residual)) in one kernel; residual None -> (x, rmsnorm(x)).
+
+    Replaces the residual add followed by mylib::layer_norm (benchmark/blocktopk_decoder.py:229-231)."""
+    _cuda(x, residual, weight)
+    cols = x.shape[-1]
+    if weight.dtype != x.dtype or weight.numel() != cols or (residual is not None and residual.shape != x.shape):
+        raise ValueError("add_rmsnorm: shapes / dtypes of x, residual and weight do not match")
+    out_norm = torch.empty_like(x)
+    out_sum = torch.empty_like(x) if residual is not None else None
+    check(_lib.load().ktk_add_rmsnorm(_ptr(x), _ptr(residual), _ptr(weight), eps, _ptr(out_sum), _ptr(out_norm),
+                                      x.numel() // cols, cols, _dtype_code(x), _stream()))
+    _launched()
+    return (out_sum if residual is not None else x), out_norm
+
+
+def qkv_norm(proj: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor, eps: float, num_q_heads: int, num_kv_heads: int):
+    """Fused projection [B, (Hq + 2 Hkv) * 128] -> (q-normed q [B, Hq, 128], k-normed k [B, Hkv, 128], v).
+
+    One launch for the split / contiguous / qk_norm sequence of benchmark/blocktopk_decoder.py:197-207."""
+    _cuda(proj, wq, wk)
+    B = proj.numel() // ((num_q_heads + 2 * num_kv_heads) * HEAD_DIM)
+    q = torch.empty(B, num_q_heads, HEAD_DIM, dtype=proj.dtype, device=proj.device)
+    k = torch.empty(B, num_kv_heads, HEAD_DIM, dtype=proj.dtype, device=proj.device)
+    v = torch.empty(B, num_kv_heads, HEAD_DIM, dtype=proj.dtype, device=proj.device)
+    check(_lib.load().ktk_qkv_norm(_ptr(proj), _ptr(wq), _ptr(wk), eps, _ptr(q), _ptr(k), _ptr(v), B, num_q_heads,
+                                   num_kv_heads, _dtype_code(proj), _stream()))
+    _launched()
+    return q, k, v
+
+
 def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """silu(gate) * up (benchmark/blocktopk_decoder.py:235-236)."""
     _cuda(gate, up)

@@ -429,3 +429,41 @@ def test_silu_mul(cuda_device, dtype):
     out = ops.silu_mul(g.to(cuda_device), u.to(cuda_device))
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     torch.testing.assert_close(out.float().cpu(), ref, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("cols", [512, 4096, 5120])
+def test_add_rmsnorm(cuda_device, dtype, cols):
+    ops = _ops()
+    torch.manual_seed(3)
+    x, r = torch.randn(19, cols).to(dtype), torch.randn(19, cols).to(dtype)
+    w = (torch.rand(cols) + 0.5).to(dtype)
+    s_ref = (x.float() + r.float()).to(dtype)
+    n_ref = s_ref.float() * torch.rsqrt(s_ref.float().pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+    s, n = ops.add_rmsnorm(x.to(cuda_device), r.to(cuda_device), w.to(cuda_device), 1e-6)
+    assert torch.equal(s.cpu(), s_ref)                       # the stored sum is the rounded sum
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    torch.testing.assert_close(n.float().cpu(), n_ref, rtol=tol, atol=tol)
+    s0, n0 = ops.add_rmsnorm(x.to(cuda_device), None, w.to(cuda_device), 1e-6)
+    n0_ref = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+    torch.testing.assert_close(n0.float().cpu(), n0_ref, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_qkv_norm_split(cuda_device, dtype):
+    ops = _ops()
+    torch.manual_seed(4)
+    B, Hq, Hkv = 7, 8, 2
+    proj = torch.randn(B, (Hq + 2 * Hkv) * 128).to(dtype)
+    wq, wk = (torch.rand(128) + 0.5).to(dtype), (torch.rand(128) + 0.5).to(dtype)
+    q, k, v = ops.qkv_norm(proj.to(cuda_device), wq.to(cuda_device), wk.to(cuda_device), 1e-6, Hq, Hkv)
+
+    def norm(t, w):
+        t = t.float()
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+
+    pq, pk, pv = proj.split((Hq * 128, Hkv * 128, Hkv * 128), dim=-1)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    torch.testing.assert_close(q.float().cpu(), norm(pq.view(B, Hq, 128), wq), rtol=tol, atol=tol)
+    torch.testing.assert_close(k.float().cpu(), norm(pk.view(B, Hkv, 128), wk), rtol=tol, atol=tol)
+    assert torch.equal(v.cpu(), pv.reshape(B, Hkv, 128))
