@@ -349,6 +349,14 @@ def run_ours(args):
         host_out = [torch.empty(B, 1, cfg.hidden_size, dtype=dtype).pin_memory() for _ in range(2)]
         s_in, s_out, s_comp = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
 
+        # With several ranks the layer input is the same on every rank (tensor parallelism replicates
+        # the hidden states) and the layer output is the sum of the ranks' partial results: rank 0 alone
+        # talks to the host, a broadcast hands the input to the others and a reduce brings the sum back,
+        # each on a communicator of its own, so that the broadcast of the next step, the reduce of the
+        # previous one and the all-reduce inside the current step are three independent queues.
+        pg_in = dist.new_group() if world > 1 else None
+        pg_out = dist.new_group() if world > 1 else None
+
         def run_steps(n):
             ev_in = [None, None]; ev_comp = [None, None]; ev_out = [None, None]
             for i in range(n):
@@ -357,7 +365,10 @@ def run_ours(args):
                 with torch.cuda.stream(s_in):
                     if ev_comp[j] is not None:
                         s_in.wait_event(ev_comp[j])          # the graph that read this buffer has finished
-                    buf_in.copy_(host_in[j], non_blocking=True)
+                    if rank == 0:
+                        buf_in.copy_(host_in[j], non_blocking=True)
+                    if world > 1:
+                        dist.broadcast(buf_in, src=0, group=pg_in)
                     ev_in[j] = torch.cuda.Event(); ev_in[j].record(s_in)
                 s_comp.wait_event(ev_in[j])
                 if ev_out[j] is not None:
@@ -366,7 +377,10 @@ def run_ours(args):
                 ev_comp[j] = torch.cuda.Event(); ev_comp[j].record(s_comp)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(ev_comp[j])
-                    host_out[j].copy_(buf_out, non_blocking=True)
+                    if world > 1:
+                        dist.reduce(buf_out, dst=0, group=pg_out)
+                    if rank == 0:
+                        host_out[j].copy_(buf_out, non_blocking=True)
                     ev_out[j] = torch.cuda.Event(); ev_out[j].record(s_out)
             s_comp.wait_stream(s_out)
             s_comp.wait_stream(s_in)
@@ -383,7 +397,9 @@ def run_ours(args):
         e2e = {"value": B * world / tp / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
                "how": "pinned host input -> device, layer step, output -> pinned host, every step; copies of "
-                      "neighbouring steps overlap the compute on separate streams"}
+                      "neighbouring steps overlap the compute on separate streams"
+                      + ("; rank 0 holds the host buffers, the input is broadcast and the partial outputs are "
+                         "reduced to it over NVLink" if world > 1 else "")}
     sparse.check_status()
 
     # ---- the repository's dense paged decode at the same shape, sharing the KV cache ----

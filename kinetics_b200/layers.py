@@ -153,7 +153,8 @@ class _PagedDecoderLayer(nn.Module):
     def _bind(self):
         raise NotImplementedError
 
-    def _mlp(self, hidden_states):
+    def _mlp(self, hidden_states, residual):
+        """SwiGLU MLP; the residual add rides in the epilogue of the down projection GEMM."""
         up = self.up_proj(hidden_states)
         gate = self.gate_proj(hidden_states)
         if self.hidden_act == "silu":
@@ -161,7 +162,7 @@ class _PagedDecoderLayer(nn.Module):
         else:
             from transformers.activations import ACT2FN
             hidden_states = ACT2FN[self.hidden_act](gate) * up
-        return self.down_proj(hidden_states)
+        return torch.addmm(residual, hidden_states, self.down_proj.weight.t())
 
     @torch.inference_mode()
     def forward(self, hidden_states):
@@ -189,8 +190,7 @@ class _PagedDecoderLayer(nn.Module):
         # residual add + post-attention RMSNorm (:229-231) in one pass
         residual, hidden_states = ops.add_rmsnorm(hidden_states, residual, self.post_attention_layernorm_weight,
                                                   self.post_attention_layernorm_variance_epsilon)
-        hidden_states = self._mlp(hidden_states)
-        return (residual + hidden_states).view(bsz, q_len, self.dim)
+        return self._mlp(hidden_states, residual).view(bsz, q_len, self.dim)
 
     def _timed(self, name):
         return _EventPair(self.timers, name)
