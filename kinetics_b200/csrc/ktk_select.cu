@@ -5,10 +5,13 @@
 // The arithmetic order of a score is part of the contract (selection must be
 // bit-exact against the CPU oracle):
 //   qbar[d]  = (q[g=0][d] + q[1][d] + ... + q[G-1][d]) * (1/G)      fp32, in g order
-//   lane j of a 16-lane group owns elements 8j..8j+7 of the summary row:
+//   sixteen chains over the 8-element chunks j = 0..15 of the summary row:
 //   part_j   = fma(qbar[8j+7], s[8j+7], ... fma(qbar[8j], s[8j], 0))   in element order
-//   then four butterfly steps part_j += part_(j xor off), off = 8, 4, 2, 1
+//   then four butterfly levels part_j += part_(j xor off), off = 8, 4, 2, 1
 //   score    = part_0 + 0.0f
+// The kernel gives the chains j, j+4, j+8, j+12 to one lane (four lanes per row): the levels
+// "xor 8" and "xor 4" are then adds inside the lane, "xor 2" and "xor 1" two shuffles; fp32
+// addition is commutative, so the bits are those of the sixteen-lane butterfly.
 // Selection orders pages by the 48-bit composite (key(score) << 16) | (0xFFFF - page),
 // which is unique per page: the k largest composites are "largest score first, ties
 // to the lowest page number".
@@ -216,10 +219,12 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
                     }
                     const T* stage = reinterpret_cast<const T*>(sel_smem + s * kSelStageBytes);
                     const int r0 = (i - ibase) * kRowsPerStage;
+                    constexpr int kSteps = kRowsPerStage / 8;
+                    static_assert(kSteps <= 4, "one lane of a row group finishes one step's scores");
+                    float accs[kSteps];
 #pragma unroll
-                    for (int step = 0; step < kRowsPerStage / 8; ++step) {
+                    for (int step = 0; step < kSteps; ++step) {
                         const int lr = step * 8 + rw;                 // row inside the stage
-                        const int r = r0 + lr;
                         const T* rowp = stage + lr * kHeadDim;        // rows past the item's last hold stale data: unused
                         float x0[8], x1[8], x2[8], x3[8];
                         lds8(rowp + c0, x0);
@@ -238,13 +243,19 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
                         float acc = __fadd_rn(__fadd_rn(p0, p2), __fadd_rn(p1, p3));
                         acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
                         acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
-                        acc = __fadd_rn(acc, 0.0f);
-                        if (j4 == 0 && r < it.n_scored) {
-                            const uint32_t key = score_to_key(acc);
-                            keys[r] = key;
-                            if (it.need_select) atomicAdd(&hist[key >> kSelBinShift], 1u);
-                            if (score_row) score_row[r] = acc;
-                        }
+                        accs[step] = __fadd_rn(acc, 0.0f);
+                    }
+                    // all four lanes of a row group hold the same totals: lane j4 finishes step j4
+                    // (key, histogram, stores), so that this tail runs once per stage
+                    float mine = accs[0];
+#pragma unroll
+                    for (int step = 1; step < kSteps; ++step) mine = (j4 == step) ? accs[step] : mine;
+                    const int r = r0 + j4 * 8 + rw;
+                    if (j4 < kSteps && r < it.n_scored) {
+                        const uint32_t key = score_to_key(mine);
+                        keys[r] = key;
+                        if (it.need_select) atomicAdd(&hist[key >> kSelBinShift], 1u);
+                        if (score_row) score_row[r] = mine;
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&empty_bar[s]);
