@@ -39,6 +39,8 @@ WORKLOADS = {
     "cfg2-tp1": dict(model="Qwen3-8B", tp=1, batch=256, ctx=8192, topk=64),
     # configs[3] shape with uniform context (ragged contexts are covered by the parity tests)
     "cfg4-shard": dict(model="Qwen3-32B", tp=8, batch=1024, ctx=8192, topk=64),
+    # configs[3]: ragged contexts uniform in [1024, 16384], fragmented (randomly permuted) page pool, GQA 8
+    "cfg4-ragged": dict(model="Qwen3-32B", tp=8, batch=1024, ctx=16384, topk=64, ragged=(1024, 16384)),
     "tiny": dict(model="Qwen3-8B", tp=8, batch=64, ctx=2048, topk=16),
 }
 PAGE = 16
@@ -246,10 +248,17 @@ def run_ours(args):
     dtype = torch.bfloat16
     torch.manual_seed(args.seed * 1000 + rank)
 
+    ctx_lens = None
+    if "ragged" in wl:
+        lo, hi = wl["ragged"]
+        gl = torch.Generator().manual_seed(args.seed)            # the same lengths on every rank
+        ctx_lens = torch.randint(lo, hi + 1, (B,), generator=gl)
+        args.page_table = "random"
+
     def make(cls, **kw):
         layer = cls(config=cfg, world_size=tp, batch_size=B, prefix_len=ctx, max_len=ctx + 512, page_size=PAGE,
                     device=device, dtype=dtype, page_table=args.page_table, process_group=pg,
-                    seed=args.seed + rank, variant=args.variant, **kw)
+                    seed=args.seed + rank, variant=args.variant, context_lens=ctx_lens, **kw)
         for m in layer.modules():
             if isinstance(m, torch.nn.Linear):
                 torch.nn.init.normal_(m.weight, 0.0, 0.02)
@@ -308,8 +317,9 @@ def run_ours(args):
     t_append = mean_ms(timers["append"][2:])
     hkv = cfg.num_key_value_heads // tp
     esz = 2
-    bytes_select = B * hkv * (ctx // PAGE) * HEAD_DIM * esz
-    bytes_decode = B * hkv * (min(topk, ctx // PAGE) + 1) * PAGE * HEAD_DIM * 2 * esz
+    scored = (ctx_lens // PAGE) if ctx_lens is not None else torch.full((B,), ctx // PAGE)
+    bytes_select = int(scored.sum()) * hkv * HEAD_DIM * esz
+    bytes_decode = int((torch.clamp(scored, max=topk) + 1).sum()) * hkv * PAGE * HEAD_DIM * 2 * esz
     peaks = {}
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -419,7 +429,7 @@ def run_ours(args):
         ms_dense = max_over_ranks(e0.elapsed_time(e1) / dsteps)
         t_dd = mean_ms(dense.timers["decode"][2:])
         dense.timers = None
-        bytes_dense = B * hkv * (ctx // PAGE + 1) * PAGE * HEAD_DIM * 2 * esz
+        bytes_dense = int((scored + 1).sum()) * hkv * PAGE * HEAD_DIM * 2 * esz
         dense_info = {"tokens_per_s": B * world / tp / (ms_dense * 1e-3), "ms_per_step": ms_dense,
                       "decode_ms": t_dd, "decode_gbs": bytes_dense / (t_dd * 1e-3) / 1e9,
                       "sparse_over_dense": ms_dense / ms_step}
@@ -428,7 +438,7 @@ def run_ours(args):
 
     # ---- CPU baseline (rank 0, single-GPU run only) ----
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if rank == 0 and world == 1 and not args.no_cpu and ctx_lens is None:
         sys.path.insert(0, ROOT)
         v, ms, threads, done = cpu_reference_run(wl, args.cpu_sample, 1000, 1, args.seed, budget_s=15.0)
         cpu = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "ms_per_step": ms,

@@ -75,7 +75,7 @@ class _PagedDecoderLayer(nn.Module):
 
     def __init__(self, config, world_size, batch_size, prefix_len, max_len, page_size, device, dtype,
                  page_table: str = "interleaved", process_group=None, seed: int = 0, variant: int = 0,
-                 kv_cache: Optional[torch.Tensor] = None):
+                 kv_cache: Optional[torch.Tensor] = None, context_lens=None):
         super().__init__()
         self.num_heads = config.num_attention_heads // world_size
         self.num_kv_heads = config.num_key_value_heads // world_size
@@ -117,21 +117,45 @@ class _PagedDecoderLayer(nn.Module):
         if page_size != ops.PAGE_SIZE or self.head_dim != ops.HEAD_DIM:
             raise ValueError(f"only page_size={ops.PAGE_SIZE}, head_dim={ops.HEAD_DIM} are built")
 
-        # paged KV state: prefix fills num_pages_per_req pages, the step appends into one more
+        # paged KV state: prefix fills num_pages_per_req pages, the step appends into one more.
+        # `context_lens` (one prefix length per sequence) makes the batch ragged: sequence b then owns
+        # context_lens[b] // page_size full pages plus the page the step writes into, laid out as one
+        # CSR list over a randomly permuted ("fragmented") or packed page pool.
         self.max_num_pages = max_num_pages = max_len // page_size
-        self.num_pages_per_req = n = prefix_len // page_size
-        if n + 1 > max_num_pages:
-            raise ValueError("max_len leaves no page for the decoded token")
         self.total_pages = max_num_pages * batch_size
-        if page_table == "interleaved":
-            table = interleaved_page_table(batch_size, n + 1, device)
-        elif page_table == "random":
-            table = random_page_table(batch_size, n + 1, self.total_pages, device, seed)
+        if context_lens is None:
+            self.num_pages_per_req = n = prefix_len // page_size
+            if n + 1 > max_num_pages:
+                raise ValueError("max_len leaves no page for the decoded token")
+            if page_table == "interleaved":
+                table = interleaved_page_table(batch_size, n + 1, device)
+            elif page_table == "random":
+                table = random_page_table(batch_size, n + 1, self.total_pages, device, seed)
+            else:
+                raise ValueError(f"page_table {page_table!r}: 'interleaved' or 'random'")
+            self.page_table = table                                  # [B, n+1]
+            self.paged_kv_indices = table.view(-1)
+            self.full_kv_indptr = (torch.arange(batch_size + 1, dtype=torch.int32, device=device) * (n + 1))
+            self.max_pages_per_seq = n + 1
         else:
-            raise ValueError(f"page_table {page_table!r}: 'interleaved' or 'random'")
-        self.page_table = table                                  # [B, n+1]
-        self.paged_kv_indices = table.view(-1)
-        self.full_kv_indptr = (torch.arange(batch_size + 1, dtype=torch.int32, device=device) * (n + 1))
+            lens = torch.as_tensor(context_lens, dtype=torch.int64)
+            if lens.numel() != batch_size or int(lens.min()) < 0 or int(lens.max()) // page_size + 1 > max_num_pages:
+                raise ValueError("context_lens: one length per sequence, each leaving a page for the new token")
+            counts = lens // page_size + 1
+            self.num_pages_per_req = int(counts.max()) - 1
+            self.max_pages_per_seq = int(counts.max())
+            indptr = torch.zeros(batch_size + 1, dtype=torch.int64)
+            indptr[1:] = torch.cumsum(counts, 0)
+            total_used = int(indptr[-1])
+            if page_table == "random":
+                g = torch.Generator(device="cpu").manual_seed(seed)
+                ids = torch.randperm(self.total_pages, generator=g)[:total_used]
+            else:
+                ids = torch.arange(total_used)
+            self.page_table = None
+            self.paged_kv_indices = ids.to(torch.int32).to(device).contiguous()
+            self.full_kv_indptr = indptr.to(torch.int32).to(device)
+        self.context_lens = context_lens
         self.last_kv_lens = torch.ones(batch_size, dtype=torch.int32, device=device)
         self.qkv_indptr = torch.arange(batch_size + 1, dtype=torch.int32, device=device)
         self.status = ops.new_status(device)
@@ -225,7 +249,7 @@ class BlockTopkDecoderLayer(_PagedDecoderLayer):
         self.topk_page_indices = torch.full((batch_size * self.num_kv_heads * (topk_page + 1),), -1,
                                             dtype=torch.int32, device=device)
         # one summary row per (sequence, kv head, logical page); reference: [B, n, D] for one head
-        self.compressed_key_cache = torch.zeros(batch_size, self.num_kv_heads, self.max_num_pages, self.head_dim,
+        self.compressed_key_cache = torch.zeros(batch_size, self.num_kv_heads, self.max_pages_per_seq + 7, self.head_dim,
                                                 dtype=dtype, device=device)
         self.rebuild_summaries()
         ops.bind_summaries(self.kv_cache, self.compressed_key_cache)
@@ -281,7 +305,7 @@ class DecoderLayer(_PagedDecoderLayer):
 
     def prepare_wrapper(self):
         plan = ops.DecodePlan(self.kv_cache, self.full_kv_indptr, self.last_kv_lens,
-                              kv_indices=self.paged_kv_indices, max_pages_per_seq=self.num_pages_per_req + 1,
+                              kv_indices=self.paged_kv_indices, max_pages_per_seq=self.max_pages_per_seq,
                               sm_scale=1.0 / math.sqrt(self.head_dim), variant=self.variant, status=self.status)
         ops.bind_decode_plan(plan)
         self.decode_plan = plan

@@ -97,3 +97,32 @@ def test_graph_replay_equals_eager(cuda_device):
     torch.cuda.synchronize()
     torch.testing.assert_close(static_out, eager, rtol=0, atol=0)
     layer.check_status()
+
+
+def test_ragged_contexts_select_like_the_oracle(cuda_device):
+    # BASELINE.json configs[3] in small: ragged per-sequence contexts, fragmented page pool
+    import kinetics_b200 as kb
+    dtype = torch.bfloat16
+    torch.manual_seed(0)
+    lens = [40 * 16, 17, 16, 0, 333, 100]
+    layer = kb.BlockTopkDecoderLayer(config=Cfg, world_size=1, batch_size=6, prefix_len=40 * 16, max_len=40 * 16 + 64,
+                                     page_size=16, topk_page=8, device=cuda_device, dtype=dtype, page_table="random",
+                                     seed=5, context_lens=lens)
+    layer.apply(kb.init_weights)
+    layer.eval()
+    layer.to(cuda_device, dtype=dtype)
+    assert (layer.full_kv_indptr[1:] - layer.full_kv_indptr[:-1]).tolist() == [n // 16 + 1 for n in lens]
+    x = torch.randn(6, 1, Cfg.hidden_size, device=cuda_device, dtype=dtype)
+    layer.capture = {}
+    y = layer(x)
+    layer.check_status()
+    assert torch.isfinite(y).all()
+    q = layer.capture["q"].cpu()
+    phys, _ = oracle.select(q, layer.compressed_key_cache.cpu(), layer.paged_kv_indices.cpu(),
+                            layer.full_kv_indptr.cpu(), 8)
+    assert torch.equal(layer.topk_page_indices.view(6, 2, 9).cpu(), phys)
+    ref = oracle.decode(q, layer.kv_cache.cpu(), phys, 8, layer.full_kv_indptr.cpu(), layer.last_kv_lens.cpu(),
+                        oracle.default_scale())
+    got = kb.ops.sparse_decode(layer.capture["q"], layer.kv_cache, layer.topk_page_indices.view(6, 2, 9),
+                               layer.full_kv_indptr, layer.last_kv_lens, num_splits=1)
+    torch.testing.assert_close(got.float().cpu(), ref, rtol=2e-2, atol=2e-2)
