@@ -2,7 +2,7 @@
 
 Run once in a container that has the reference checkout (it is not needed afterwards):
 
-    TRITON_INTERPRET=1 python tests/golden/make_golden.py /root/reference
+    TRITON_INTERPRET=1 python tests/golden/make_golden.py <path to the Kinetics checkout>
 
 What runs is the reference's LiteSys decode chain, unmodified, imported from its checkout:
 ``qk`` -> ``blockwise_topk_sparsity`` -> ``softmax`` -> ``sv``
@@ -149,7 +149,9 @@ def run_reference_litesys(ref_root: str, case: dict) -> dict:
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to the Kinetics checkout>")
+    ref_root = sys.argv[1]
     for name in CASES:
         case = make_case(name)
         res = run_reference(ref_root, case)
