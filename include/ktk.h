@@ -281,6 +281,19 @@ KTK_API int ktk_append_v(const void* k, const void* v, void* kv_cache, void* sum
                          int64_t summary_stride, const int32_t* kv_indices, const int32_t* kv_indptr,
                          const int32_t* kv_last_page_len, const ktk_view* view, const ktk_shape* shape,
                          int32_t* status, void* stream);
+/*
+ * Append several tokens per sequence (prefill, chunked append) and refresh the summaries of the
+ * pages they touch.  k, v: [total_tokens, Hkv, D] packed by sequence; append_indptr int32[B+1] gives
+ * each sequence's range, exactly the `kv_append_indptr` argument of mylib::update_kv ->
+ * flashinfer.append_paged_kv_cache (benchmark/blocktopk_decoder.py:23-46); the page table describes
+ * the state after the append.  Also the write half of the LiteSys prefill
+ * (LiteSys/litesys/attention/batch_cache.py:123-127).  `view` may be null.
+ */
+KTK_API int ktk_append_tokens(const void* k, const void* v, const int32_t* append_indptr, int64_t total_tokens,
+                              void* kv_cache, void* summaries, int64_t summary_stride,
+                              const int32_t* kv_indices, const int32_t* kv_indptr,
+                              const int32_t* kv_last_page_len, const ktk_view* view, const ktk_shape* shape,
+                              int32_t* status, void* stream);
 KTK_API int ktk_build_summaries_v(const void* kv_cache, void* summaries, int64_t summary_stride,
                                   const int32_t* kv_indices, const int32_t* kv_indptr,
                                   const int32_t* kv_last_page_len, const ktk_view* view,

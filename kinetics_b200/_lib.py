@@ -59,6 +59,8 @@ _SIGNATURES = {
     "ktk_view_row_width": (c_int32, [c_int32, POINTER(View)]),
     "ktk_append_v": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, _i32p, _i32p, _i32p, POINTER(View),
                                POINTER(Shape), _i32p, c_void_p]),
+    "ktk_append_tokens": (c_int32, [c_void_p, c_void_p, _i32p, c_int64, c_void_p, c_void_p, c_int64, _i32p, _i32p,
+                                    _i32p, POINTER(View), POINTER(Shape), _i32p, c_void_p]),
     "ktk_build_summaries_v": (c_int32, [c_void_p, c_void_p, c_int64, _i32p, _i32p, _i32p, POINTER(View),
                                         POINTER(Shape), _i32p, c_void_p]),
     "ktk_select_v": (c_int32, [c_void_p, c_void_p, c_int64, _i32p, _i32p, _i32p, c_int32, POINTER(View), c_int32,

@@ -175,17 +175,16 @@ class BatchKVManager:
         slot = int(batch_idx.item())
         offset = int(self.kv_offset[layer_idx][slot].item())
         pos = torch.arange(offset, offset + seq_len, device=self.device)
-        page = torch.where(pos < SINK, torch.zeros_like(pos), 1 + (pos - SINK) // PAGE) + slot * self.pages_per_slot
-        slot_in_page = torch.where(pos < SINK, pos, (pos - SINK) % PAGE)
         pages = self.kv_pages[layer_idx]
-        pages[page, 0, slot_in_page] = key_states[0].transpose(0, 1).to(self.dtype)
-        pages[page, 1, slot_in_page] = value_states[0].transpose(0, 1).to(self.dtype)
         self.kv_offset[layer_idx][slot] += seq_len
         total = offset + seq_len
         bi = torch.tensor([slot], device=self.device, dtype=torch.int64)
         start, last, view = self._table(bi, torch.tensor([total], device=self.device, dtype=torch.int32))
-        ops.build_summaries(pages, self.summaries[layer_idx], self.kv_indices, start, last, status=self.status,
-                            view=view)
+        append_indptr = torch.tensor([0, seq_len], device=self.device, dtype=torch.int32)
+        # write the chunk into its pages and refresh the summaries of the pages it touched
+        ops.append_tokens(key_states[0].transpose(0, 1).to(self.dtype).contiguous(),
+                          value_states[0].transpose(0, 1).to(self.dtype).contiguous(), append_indptr, pages,
+                          self.summaries[layer_idx], self.kv_indices, start, last, status=self.status, view=view)
         # gather the slot's history as [Hkv, total, D]
         allpos = torch.arange(total, device=self.device)
         apage = torch.where(allpos < SINK, torch.zeros_like(allpos), 1 + (allpos - SINK) // PAGE) \

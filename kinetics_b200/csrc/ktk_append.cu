@@ -50,6 +50,65 @@ append_kernel(const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ 
     }
 }
 
+// tokens of a sequence of n_pages pages whose last page holds `last` tokens (a sink page holds sink_tokens)
+__device__ __forceinline__ int seq_tokens(int n_pages, int last, int sink_tokens) {
+    if (sink_tokens == 0) return (n_pages - 1) * kPageSize + last;
+    return n_pages == 1 ? last : sink_tokens + (n_pages - 2) * kPageSize + last;
+}
+// logical page and slot of token `pos`
+__device__ __forceinline__ int token_page(int pos, int sink_tokens) {
+    if (sink_tokens == 0) return pos / kPageSize;
+    return pos < sink_tokens ? 0 : 1 + (pos - sink_tokens) / kPageSize;
+}
+__device__ __forceinline__ int token_slot(int pos, int sink_tokens) {
+    if (sink_tokens == 0) return pos % kPageSize;
+    return pos < sink_tokens ? pos : (pos - sink_tokens) % kPageSize;
+}
+
+// Several tokens per sequence (prefill, chunked append): token j of the packed k / v belongs to the
+// sequence b with append_indptr[b] <= j < append_indptr[b+1] and is the (j - append_indptr[b])-th of the
+// sequence's n_app newest tokens.  grid (tokens, Hkv), one thread per head-dim element.
+template <typename T>
+__global__ void __launch_bounds__(kHeadDim)
+append_tokens_kernel(const T* __restrict__ k, const T* __restrict__ v, const int32_t* __restrict__ append_indptr,
+                     int B, T* __restrict__ cache, const int32_t* __restrict__ kv_indices,
+                     const int32_t* __restrict__ kv_indptr, const int32_t* __restrict__ kv_last_page_len,
+                     const int32_t* __restrict__ page_count, int sink_tokens, int Hkv, int64_t num_pages,
+                     int32_t* status) {
+    const int j = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+    // the sequence that owns token j: last b with append_indptr[b] <= j
+    int lo = 0, hi = B;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (append_indptr[mid] <= j) lo = mid; else hi = mid;
+    }
+    const int b = lo;
+    const int a0 = append_indptr[b], n_app = append_indptr[b + 1] - a0;
+    if (j < a0 || j >= a0 + n_app) return;                       // token outside every range
+    const int beg = kv_indptr[b];
+    const int n_pages = page_count ? page_count[b] : kv_indptr[b + 1] - beg;
+    const int last = (n_pages > 0) ? kv_last_page_len[b] : 0;
+    if (n_pages <= 0 || last < 1 || last > kPageSize) {
+        if (d == 0) report(status, KTK_STATUS_BAD_TABLE);
+        return;
+    }
+    const int pos = seq_tokens(n_pages, last, sink_tokens) - n_app + (j - a0);
+    if (pos < 0) {
+        if (d == 0) report(status, KTK_STATUS_BAD_TABLE);
+        return;
+    }
+    const int64_t page = kv_indices[beg + token_page(pos, sink_tokens)];
+    if (page < 0 || page >= num_pages) {
+        if (d == 0) report(status, KTK_STATUS_BAD_PAGE);
+        return;
+    }
+    const int64_t row = (int64_t)Hkv * kHeadDim;
+    T* kp = cache + ((page * 2) * kPageSize + token_slot(pos, sink_tokens)) * row + (int64_t)h * kHeadDim + d;
+    const int64_t src = ((int64_t)j * Hkv + h) * kHeadDim + d;
+    kp[0] = k[src];
+    kp[kPageSize * row] = v[src];
+}
+
 // grid (B, Hkv, Z): CTA z rebuilds the summaries of logical pages z, z+Z, ...
 template <typename T>
 __global__ void __launch_bounds__(kHeadDim)
@@ -57,8 +116,8 @@ build_summaries_kernel(const T* __restrict__ cache, T* __restrict__ summaries,
                        int64_t summary_stride, const int32_t* __restrict__ kv_indices,
                        const int32_t* __restrict__ kv_indptr,
                        const int32_t* __restrict__ kv_last_page_len, const int32_t* __restrict__ page_count,
-                       const int32_t* __restrict__ slot_index, int sink_tokens, int Hkv, int64_t num_pages,
-                       int32_t* status) {
+                       const int32_t* __restrict__ slot_index, const int32_t* __restrict__ append_indptr,
+                       int sink_tokens, int Hkv, int64_t num_pages, int32_t* status) {
     const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
     const int beg = kv_indptr[b];
     const int n_pages = page_count ? page_count[b] : kv_indptr[b + 1] - beg;
@@ -71,7 +130,15 @@ build_summaries_kernel(const T* __restrict__ cache, T* __restrict__ summaries,
     }
     const int64_t row = (int64_t)Hkv * kHeadDim;
     T* sbase = summaries + ((int64_t)srow_b * Hkv + h) * summary_stride * kHeadDim + d;
-    for (int p = blockIdx.z; p < n_pages; p += gridDim.z) {
+    // after an append of several tokens only the pages they touched need a new summary
+    int first = 0;
+    if (append_indptr != nullptr) {
+        const int n_app = append_indptr[b + 1] - append_indptr[b];
+        if (n_app <= 0) return;
+        const int len = seq_tokens(n_pages, last, sink_tokens);
+        first = token_page(len - n_app < 0 ? 0 : len - n_app, sink_tokens);
+    }
+    for (int p = first + blockIdx.z; p < n_pages; p += gridDim.z) {
         const int64_t page = kv_indices[beg + p];
         if (page < 0 || page >= num_pages) {
             if (d == 0) report(status, KTK_STATUS_BAD_PAGE);
@@ -171,7 +238,7 @@ template <typename T>
 static int build_impl(const void* cache, void* summaries, int64_t summary_stride,
                       const int32_t* kv_indices, const int32_t* kv_indptr,
                       const int32_t* kv_last_page_len, const View& view, const ktk_shape* s, int32_t* status,
-                      cudaStream_t st) {
+                      cudaStream_t st, const int32_t* append_indptr = nullptr) {
     const int64_t bh = (int64_t)s->batch * s->num_kv_heads;
     int z = (int)((8LL * sm_count() + bh - 1) / bh);
     if (z < 1) z = 1;
@@ -179,7 +246,7 @@ static int build_impl(const void* cache, void* summaries, int64_t summary_stride
     dim3 grid(s->batch, s->num_kv_heads, z);
     build_summaries_kernel<T><<<grid, kHeadDim, 0, st>>>(
         (const T*)cache, (T*)summaries, summary_stride, kv_indices, kv_indptr, kv_last_page_len,
-        view.page_count, view.slot_index, view.sink_tokens, s->num_kv_heads, s->num_pages, status);
+        view.page_count, view.slot_index, append_indptr, view.sink_tokens, s->num_kv_heads, s->num_pages, status);
     KTK_CUDA_TRY(cudaGetLastError(), "ktk_build_summaries");
     return KTK_OK;
 }
@@ -246,6 +313,49 @@ extern "C" int ktk_build_summaries_v(const void* kv_cache, void* summaries, int6
                                  kv_last_page_len, view, shape, status, st);
     return build_impl<__nv_bfloat16>(kv_cache, summaries, summary_stride, kv_indices, kv_indptr,
                                      kv_last_page_len, view, shape, status, st);
+}
+
+extern "C" int ktk_append_tokens(const void* k, const void* v, const int32_t* append_indptr, int64_t total_tokens,
+                                 void* kv_cache, void* summaries, int64_t summary_stride,
+                                 const int32_t* kv_indices, const int32_t* kv_indptr,
+                                 const int32_t* kv_last_page_len, const ktk_view* view_in, const ktk_shape* shape,
+                                 int32_t* status, void* stream) {
+    int rc = check_shape(shape, "ktk_append_tokens");
+    if (rc != KTK_OK) return rc;
+    rc = check_view(view_in, "ktk_append_tokens");
+    if (rc != KTK_OK) return rc;
+    if (total_tokens < 0 || total_tokens > 2147483647LL) {
+        set_error("ktk_append_tokens: total_tokens %lld out of range", (long long)total_tokens);
+        return KTK_ERR_ARG;
+    }
+    if (shape->batch == 0 || total_tokens == 0) return KTK_OK;
+    if (!k || !v || !append_indptr || !kv_cache || !kv_indices || !kv_indptr || !kv_last_page_len) {
+        set_error("ktk_append_tokens: null pointer argument");
+        return KTK_ERR_ARG;
+    }
+    if (summaries != nullptr && summary_stride <= 0) {
+        set_error("ktk_append_tokens: summary_stride must be positive");
+        return KTK_ERR_ARG;
+    }
+    const View view = make_view(view_in);
+    cudaStream_t st = (cudaStream_t)stream;
+    dim3 grid((unsigned)total_tokens, shape->num_kv_heads);
+    if (shape->dtype == KTK_F32)
+        append_tokens_kernel<float><<<grid, kHeadDim, 0, st>>>(
+            (const float*)k, (const float*)v, append_indptr, shape->batch, (float*)kv_cache, kv_indices, kv_indptr,
+            kv_last_page_len, view.page_count, view.sink_tokens, shape->num_kv_heads, shape->num_pages, status);
+    else
+        append_tokens_kernel<__nv_bfloat16><<<grid, kHeadDim, 0, st>>>(
+            (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, append_indptr, shape->batch, (__nv_bfloat16*)kv_cache,
+            kv_indices, kv_indptr, kv_last_page_len, view.page_count, view.sink_tokens, shape->num_kv_heads,
+            shape->num_pages, status);
+    KTK_CUDA_TRY(cudaGetLastError(), "ktk_append_tokens");
+    if (summaries == nullptr) return KTK_OK;
+    if (shape->dtype == KTK_F32)
+        return build_impl<float>(kv_cache, summaries, summary_stride, kv_indices, kv_indptr, kv_last_page_len, view,
+                                 shape, status, st, append_indptr);
+    return build_impl<__nv_bfloat16>(kv_cache, summaries, summary_stride, kv_indices, kv_indptr, kv_last_page_len,
+                                     view, shape, status, st, append_indptr);
 }
 
 extern "C" int ktk_build_summaries(const void* kv_cache, void* summaries, int64_t summary_stride,

@@ -161,6 +161,28 @@ def append_kv(k, v, kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len
     _launched()
 
 
+def append_tokens(k, v, append_indptr, kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len, status=None,
+                  view=None) -> None:
+    """Append several tokens per sequence (prefill / chunked append) and refresh the touched page summaries.
+
+    k, v: [total_tokens, Hkv, D] packed by sequence, append_indptr int32 [B+1]; the page table already
+    includes the new tokens.  The multi-token form of flashinfer.append_paged_kv_cache
+    (benchmark/blocktopk_decoder.py:38-46)."""
+    _cuda(k, v, append_indptr, kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len, status)
+    B = append_indptr.numel() - 1
+    if k.dim() != 3 or k.shape[1:] != (kv_cache.shape[3], kv_cache.shape[4]) or v.shape != k.shape:
+        raise ValueError("k/v must be [total_tokens, Hkv, D]")
+    if k.dtype != kv_cache.dtype or v.dtype != kv_cache.dtype or append_indptr.dtype != torch.int32:
+        raise TypeError("k, v and kv_cache must share a dtype; append_indptr must be int32")
+    shp = _shape(B, kv_cache, kv_cache.shape[3])
+    stride = 0 if summaries is None else summaries.shape[2]
+    vp, _keep = _view_ref(view)
+    check(_lib.load().ktk_append_tokens(_ptr(k), _ptr(v), _ptr(append_indptr), k.shape[0], _ptr(kv_cache),
+                                        _ptr(summaries), stride, _ptr(kv_indices), _ptr(kv_indptr),
+                                        _ptr(kv_last_page_len), vp, ctypes.byref(shp), _ptr(status), _stream()))
+    _launched(1 if summaries is None else 2)
+
+
 def build_summaries(kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len, status=None, view=None) -> None:
     """Recompute the mean-key summary of every page of every sequence."""
     _cuda(kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len, status)
@@ -413,9 +435,12 @@ torch.library.define(
 
 @torch.library.impl("mylib::update_kv", "cuda")
 def _update_kv(k, v, kv_append_indptr, kv_cache, kv_page_indices, kv_page_indptr, kv_page_last_len):
-    # kv_append_indptr is arange(B+1) at decode (one token per sequence) and is not read
-    append_kv(k, v, kv_cache, _SUMMARIES.get(kv_cache.data_ptr()), kv_page_indices, kv_page_indptr,
-              kv_page_last_len)
+    summ = _SUMMARIES.get(kv_cache.data_ptr())
+    if k.shape[0] == kv_page_indptr.numel() - 1:
+        # one token per sequence (decode): kv_append_indptr is arange(B+1) and need not be read
+        append_kv(k, v, kv_cache, summ, kv_page_indices, kv_page_indptr, kv_page_last_len)
+    else:
+        append_tokens(k, v, kv_append_indptr, kv_cache, summ, kv_page_indices, kv_page_indptr, kv_page_last_len)
 
 
 @torch.library.register_fake("mylib::update_kv")

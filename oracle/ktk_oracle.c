@@ -429,3 +429,32 @@ int ktko_decode_v(const void* q, const void* cache, const int32_t* entries, int 
     }
     return 0;
 }
+
+
+/* several tokens per sequence: k, v [total, Hkv, D] packed by sequence, append_indptr [B+1]
+ * (the kv_append_indptr of flashinfer.append_paged_kv_cache, benchmark/blocktopk_decoder.py:38-46);
+ * the page table describes the state after the append.  Summaries are not touched here. */
+int ktko_append_tokens(const void* k, const void* v, const int32_t* append_indptr, void* cache,
+                       const int32_t* kv_indices, const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                       int sink, int B, int Hkv, int dtype) {
+    for (int b = 0; b < B; ++b) {
+        const int a0 = append_indptr[b], n_app = append_indptr[b + 1] - a0;
+        const int beg = kv_indptr[b], n_pages = kv_indptr[b + 1] - beg;
+        if (n_app <= 0 || n_pages <= 0) continue;
+        const int last = kv_last_page_len[b];
+        const int len = sink == 0 ? (n_pages - 1) * P + last : (n_pages == 1 ? last : sink + (n_pages - 2) * P + last);
+        for (int i = 0; i < n_app; ++i) {
+            const int pos = len - n_app + i;
+            const int lp = sink == 0 ? pos / P : (pos < sink ? 0 : 1 + (pos - sink) / P);
+            const int sl = sink == 0 ? pos % P : (pos < sink ? pos : (pos - sink) % P);
+            const int64_t page = kv_indices[beg + lp];
+            for (int h = 0; h < Hkv; ++h)
+                for (int d = 0; d < D; ++d) {
+                    const int64_t src = (((int64_t)(a0 + i)) * Hkv + h) * D + d;
+                    st(cache, dtype, kv_row(page, 0, sl, h, Hkv) + d, ld(k, dtype, src));
+                    st(cache, dtype, kv_row(page, 1, sl, h, Hkv) + d, ld(v, dtype, src));
+                }
+        }
+    }
+    return 0;
+}

@@ -89,6 +89,13 @@ def append(k, v, kv_cache, summ, kv_indices, kv_indptr, kv_last_page_len):
                        _i32(kv_indptr), _i32(kv_last_page_len), B, Hkv, _dt(k))
 
 
+def append_tokens(k, v, append_indptr, kv_cache, kv_indices, kv_indptr, kv_last_page_len, sink: int = 0):
+    """In-place append of several tokens per sequence (k, v [total, Hkv, D] packed by sequence)."""
+    B = append_indptr.numel() - 1
+    _lib().ktko_append_tokens(_p(k), _p(v), _i32(append_indptr), _p(kv_cache), _i32(kv_indices), _i32(kv_indptr),
+                              _i32(kv_last_page_len), sink, B, kv_cache.shape[3], _dt(k))
+
+
 def scores(q, summ, kv_indptr):
     """fp32 page scores in the contract's summation order -> [B, Hkv, summary_stride]."""
     B, Hq = q.shape[0], q.shape[1]

@@ -467,3 +467,52 @@ def test_qkv_norm_split(cuda_device, dtype):
     torch.testing.assert_close(q.float().cpu(), norm(pq.view(B, Hq, 128), wq), rtol=tol, atol=tol)
     torch.testing.assert_close(k.float().cpu(), norm(pk.view(B, Hkv, 128), wk), rtol=tol, atol=tol)
     assert torch.equal(v.cpu(), pv.reshape(B, Hkv, 128))
+
+
+@pytest.mark.parametrize("sink", [0, 4])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_append_tokens_chunks_bit_exact(cuda_device, dtype, sink):
+    # ragged chunks appended behind ragged prefixes: cache and the touched summaries follow the oracle
+    ops = _ops()
+    before = [0, 37, 5, 100, 16]
+    chunk = [50, 1, 0, 29, 16]
+    after = [a + c for a, c in zip(before, chunk)]
+    B, Hkv = len(before), 2
+    q, k, v = random_case(41, B, Hkv, 1, after, dtype)
+    st_after = paged_state(k, v, after, dtype, seed=2, sink=sink, fill=0.0)
+    # the same table, holding only the prefix
+    cache = st_after["kv_cache"].clone()
+    kk = torch.cat([k[b, :, before[b]:after[b]].transpose(0, 1) for b in range(B)]).to(dtype).contiguous()
+    vv = torch.cat([v[b, :, before[b]:after[b]].transpose(0, 1) for b in range(B)]).to(dtype).contiguous()
+    ai = torch.tensor([0] + list(np.cumsum(chunk)), dtype=torch.int32)
+    blank = torch.zeros_like(kk)
+    oracle.append_tokens(blank, blank, ai, cache, st_after["kv_indices"], st_after["kv_indptr"],
+                         st_after["kv_last_page_len"], sink)                      # wipe the chunk
+    want_cache = cache.clone()
+    oracle.append_tokens(kk, vv, ai, want_cache, st_after["kv_indices"], st_after["kv_indptr"],
+                         st_after["kv_last_page_len"], sink)
+    assert torch.equal(_bits(want_cache), _bits(st_after["kv_cache"]))
+    d = to_dev(st_after, cuda_device)
+    cache_g = cache.to(cuda_device)
+    summ_g = torch.zeros(B, Hkv, st_after["summary_stride"], 128, dtype=dtype, device=cuda_device)
+    status = ops.new_status(cuda_device)
+    view = ops.PageView(sink, 1) if sink else None
+    ops.append_tokens(kk.to(cuda_device), vv.to(cuda_device), ai.to(cuda_device), cache_g, summ_g, d["kv_indices"],
+                      d["kv_indptr"], d["kv_last_page_len"], status=status, view=view)
+    ops.raise_on_status(status)
+    assert torch.equal(_bits(cache_g.cpu()), _bits(want_cache))
+    want_summ = oracle.summaries_v(want_cache, st_after["kv_indices"], st_after["kv_indptr"],
+                                   st_after["kv_last_page_len"], st_after["summary_stride"], sink)
+
+    def page_of(pos):
+        return pos // P if sink == 0 else (0 if pos < sink else 1 + (pos - sink) // P)
+
+    got = summ_g.cpu()
+    for b in range(B):
+        if chunk[b] == 0:
+            assert not got[b].any()                      # untouched sequence: nothing rewritten
+            continue
+        first = page_of(before[b])
+        npg = st_after["npages"][b]
+        assert torch.equal(_bits(got[b, :, first:npg]), _bits(want_summ[b, :, first:npg]))
+        assert not got[b, :, :first].any()               # pages in front of the chunk keep their summaries
