@@ -63,6 +63,8 @@ def parse():
     ap.add_argument("--page-table", default="interleaved", choices=["interleaved", "random"])
     ap.add_argument("--seed", type=int, default=1236)
     ap.add_argument("--cpu-sample", type=int, default=32, help="sequences in the CPU sample")
+    ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: sum the o_proj partials with the fused multicast kernel, or with NCCL")
     ap.add_argument("--micro", default="", choices=["", "select"],
                     help="time one kernel alone on the workload's shapes (select: only the page summaries are "
                          "allocated, so the full batch fits in a few GB)")
@@ -258,7 +260,8 @@ def run_ours(args):
     def make(cls, **kw):
         layer = cls(config=cfg, world_size=tp, batch_size=B, prefix_len=ctx, max_len=ctx + 512, page_size=PAGE,
                     device=device, dtype=dtype, page_table=args.page_table, process_group=pg,
-                    seed=args.seed + rank, variant=args.variant, context_lens=ctx_lens, **kw)
+                    seed=args.seed + rank, variant=args.variant, context_lens=ctx_lens,
+                    fused_allreduce=(world > 1 and args.allreduce == "fused"), **kw)
         for m in layer.modules():
             if isinstance(m, torch.nn.Linear):
                 torch.nn.init.normal_(m.weight, 0.0, 0.02)

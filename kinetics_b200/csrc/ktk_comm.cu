@@ -1,0 +1,181 @@
+// o_proj all-reduce fused with the residual add and the post-attention RMSNorm,
+// over NVSwitch multicast (multimem) instead of a separate NCCL all-reduce followed
+// by an element-wise kernel.
+//
+// Every rank holds its partial o_proj output X_r [rows, cols] in a buffer that is mapped
+// into one multicast object, and the residual (identical on all ranks).  Rank r owns the
+// rows [r * rows / world, (r + 1) * rows / world):
+//   1. barrier: every rank's X is complete (same-index CTAs of all ranks meet)
+//   2. s = bf16( multimem.ld_reduce.add(X)[row] + residual[row] )   -- the switch adds the partials
+//      n = s * rsqrt(mean(s^2) + eps) * w
+//      multimem.st of s and n: every rank receives the row
+//   3. barrier: the rows of all ranks have landed everywhere
+// The barriers are flags in peer memory (one word per (CTA, source rank)), written with
+// release and polled with acquire at system scope; the values grow from launch to launch
+// (a per-CTA launch counter in local memory), so nothing needs resetting and the kernel can
+// sit in a CUDA graph.  Every poll loop is bounded: on expiry the CTA records
+// KTK_STATUS_TIMEOUT and goes on without waiting.
+#include "ktk_common.cuh"
+
+namespace ktk {
+
+constexpr int kCommThreads = 256;
+constexpr int kCommMaxVec = 4;          // 8 elements each: cols <= 8192
+constexpr int kCommMaxWorld = 16;
+constexpr uint32_t kCommSpinCap = 1u << 24;   // ~ a second of polling
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// eight bf16 summed over all ranks by the switch (fp32 accumulation), returned as four bf16x2
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+    uint4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(mc_addr)
+                 : "memory");
+    return r;
+}
+// sixteen bytes to every rank of the multicast object
+__device__ __forceinline__ void multimem_st_16(void* mc_addr, const uint4& v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc_addr), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+                   "f"(__uint_as_float(v.w))
+                 : "memory");
+}
+
+// Same-index CTAs of all ranks meet: tell every peer that this rank reached `value`, then wait
+// until every peer said the same.  flags[p] is rank p's flag array, [CTA][source rank].
+__device__ __forceinline__ void cta_barrier_all_ranks(uint32_t* const* flags, int rank, int world, uint32_t value,
+                                                      int32_t* status) {
+    __syncthreads();
+    if ((int)threadIdx.x < world) {
+        const int peer = threadIdx.x;
+        st_release_sys(flags[peer] + (size_t)blockIdx.x * world + rank, value);
+        const uint32_t* mine = flags[rank] + (size_t)blockIdx.x * world + peer;
+        bool ok = false;
+        for (uint32_t i = 0; i < kCommSpinCap; ++i) {
+            if ((int32_t)(ld_acquire_sys(mine) - value) >= 0) { ok = true; break; }
+            if (i > 64) __nanosleep(64);
+        }
+        if (!ok) report(status, KTK_STATUS_TIMEOUT);
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(kCommThreads)
+allreduce_add_rmsnorm_kernel(const __nv_bfloat16* x_mc, const __nv_bfloat16* __restrict__ residual,
+                             const __nv_bfloat16* __restrict__ w, __nv_bfloat16* sum_mc, __nv_bfloat16* norm_mc,
+                             uint32_t* const* flags, uint32_t* launch_count, int rank, int world, int rows,
+                             int cols, float eps, int32_t* status) {
+    __shared__ float part[kCommThreads / 32];
+    __shared__ uint32_t s_epoch;
+    if (threadIdx.x == 0) s_epoch = launch_count[blockIdx.x];
+    __syncthreads();
+    const uint32_t epoch = s_epoch;
+
+    cta_barrier_all_ranks(flags, rank, world, 2 * epoch + 1, status);     // every rank's partial output is complete
+
+    const int per = rows / world;
+    const int nvec = cols / 8;
+    for (int r = rank * per + blockIdx.x; r < (rank + 1) * per; r += gridDim.x) {
+        float v[kCommMaxVec][8];
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kCommMaxVec; ++i) {
+            const int c = threadIdx.x + i * kCommThreads;
+            if (c < nvec) {
+                const size_t off = (size_t)r * cols + (size_t)c * 8;
+                float x[8], t[8];
+                unpack8(multimem_ld_reduce_bf16x8(x_mc + off), x);
+                unpack8(*reinterpret_cast<const uint4*>(residual + off), t);
+                uint4 packed;
+                uint32_t* pw = &packed.x;
+#pragma unroll
+                for (int e = 0; e < 8; e += 2) {
+                    const __nv_bfloat162 two = __floats2bfloat162_rn(x[e] + t[e], x[e + 1] + t[e + 1]);
+                    pw[e / 2] = *reinterpret_cast<const uint32_t*>(&two);
+                }
+                multimem_st_16(sum_mc + off, packed);
+                unpack8(packed, v[i]);                     // normalise the rounded sum, as if it had been re-read
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        __syncthreads();                                   // `part` of the previous row has been read
+        if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float tot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kCommThreads / 32; ++i) tot += part[i];
+        const float inv = rsqrtf(tot / (float)cols + eps);
+#pragma unroll
+        for (int i = 0; i < kCommMaxVec; ++i) {
+            const int c = threadIdx.x + i * kCommThreads;
+            if (c < nvec) {
+                float wv[8];
+                unpack8(*reinterpret_cast<const uint4*>(w + (size_t)c * 8), wv);
+                uint4 packed;
+                uint32_t* pw = &packed.x;
+#pragma unroll
+                for (int e = 0; e < 8; e += 2) {
+                    const __nv_bfloat162 two =
+                        __floats2bfloat162_rn(v[i][e] * inv * wv[e], v[i][e + 1] * inv * wv[e + 1]);
+                    pw[e / 2] = *reinterpret_cast<const uint32_t*>(&two);
+                }
+                multimem_st_16(norm_mc + (size_t)r * cols + (size_t)c * 8, packed);
+            }
+        }
+    }
+    __threadfence_system();                                // this CTA's rows are on their way to every rank
+    cta_barrier_all_ranks(flags, rank, world, 2 * epoch + 2, status);     // and so are everybody else's
+    if (threadIdx.x == 0) launch_count[blockIdx.x] = epoch + 1;
+}
+
+}  // namespace ktk
+
+using namespace ktk;
+
+extern "C" int32_t ktk_allreduce_grid(int64_t rows, int32_t world) {
+    if (rows <= 0 || world <= 0) return 0;
+    const int64_t per = rows / world;
+    const int64_t cap = sm_count();
+    return (int32_t)(per < cap ? per : cap);
+}
+
+extern "C" int ktk_allreduce_add_rmsnorm(const void* x_multicast, const void* residual, const void* w,
+                                         void* sum_multicast, void* norm_multicast, const void* flag_ptrs,
+                                         void* launch_count, int32_t rank, int32_t world, int64_t rows,
+                                         int32_t cols, float eps, int32_t* status, void* stream) {
+    if (world < 2 || world > kCommMaxWorld || rank < 0 || rank >= world || rows <= 0 || cols <= 0) {
+        set_error("ktk_allreduce_add_rmsnorm: bad arguments rank=%d world=%d rows=%lld cols=%d", rank, world,
+                  (long long)rows, cols);
+        return KTK_ERR_ARG;
+    }
+    if (!x_multicast || !residual || !w || !sum_multicast || !norm_multicast || !flag_ptrs || !launch_count) {
+        set_error("ktk_allreduce_add_rmsnorm: null pointer argument");
+        return KTK_ERR_ARG;
+    }
+    if (rows % world != 0 || cols % 8 != 0 || cols > 8 * kCommThreads * kCommMaxVec || rows > 2147483647LL) {
+        set_error("ktk_allreduce_add_rmsnorm: rows (%lld) must divide by the ranks (%d), cols (%d) by 8 and be <= %d",
+                  (long long)rows, world, cols, 8 * kCommThreads * kCommMaxVec);
+        return KTK_ERR_UNSUPPORTED;
+    }
+    const uintptr_t al = (uintptr_t)x_multicast | (uintptr_t)residual | (uintptr_t)w | (uintptr_t)sum_multicast |
+                         (uintptr_t)norm_multicast;
+    if ((al & 15u) != 0) { set_error("ktk_allreduce_add_rmsnorm: pointers must be 16-byte aligned"); return KTK_ERR_ARG; }
+    const int grid = ktk_allreduce_grid(rows, world);
+    allreduce_add_rmsnorm_kernel<<<grid, kCommThreads, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)x_multicast, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w,
+        (__nv_bfloat16*)sum_multicast, (__nv_bfloat16*)norm_multicast, (uint32_t* const*)flag_ptrs,
+        (uint32_t*)launch_count, rank, world, (int)rows, cols, eps, status);
+    KTK_CUDA_TRY(cudaGetLastError(), "ktk_allreduce_add_rmsnorm");
+    return KTK_OK;
+}

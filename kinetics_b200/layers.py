@@ -75,7 +75,7 @@ class _PagedDecoderLayer(nn.Module):
 
     def __init__(self, config, world_size, batch_size, prefix_len, max_len, page_size, device, dtype,
                  page_table: str = "interleaved", process_group=None, seed: int = 0, variant: int = 0,
-                 kv_cache: Optional[torch.Tensor] = None, context_lens=None):
+                 kv_cache: Optional[torch.Tensor] = None, context_lens=None, fused_allreduce: bool = False):
         super().__init__()
         self.num_heads = config.num_attention_heads // world_size
         self.num_kv_heads = config.num_key_value_heads // world_size
@@ -114,6 +114,12 @@ class _PagedDecoderLayer(nn.Module):
         self.dtype = dtype
         self.process_group = process_group
         self.variant = variant
+        # with a process group: sum the o_proj partials either with NCCL followed by the add + norm
+        # kernel, or (fused_allreduce) with the one multicast kernel of comm.py
+        self.fused = None
+        if process_group is not None and fused_allreduce:
+            from .comm import FusedAllReduceNorm
+            self.fused = FusedAllReduceNorm(process_group, batch_size, self.dim, dtype, device)
         if page_size != ops.PAGE_SIZE or self.head_dim != ops.HEAD_DIM:
             raise ValueError(f"only page_size={ops.PAGE_SIZE}, head_dim={ops.HEAD_DIM} are built")
 
@@ -208,12 +214,19 @@ class _PagedDecoderLayer(nn.Module):
                                       self.paged_kv_indices, self.full_kv_indptr, self.last_kv_lens)
         o = self._attention(query_states)
         o = o.reshape(bsz * q_len, self.head_dim * self.num_heads)
-        hidden_states = self.wo(o)
-        if self.process_group is not None:
-            torch.distributed.all_reduce(hidden_states, group=self.process_group)
-        # residual add + post-attention RMSNorm (:229-231) in one pass
-        residual, hidden_states = ops.add_rmsnorm(hidden_states, residual, self.post_attention_layernorm_weight,
-                                                  self.post_attention_layernorm_variance_epsilon)
+        if self.fused is not None:
+            # o_proj partial straight into the symmetric buffer, then all-reduce + residual add + norm at once
+            torch.mm(o, self.wo.weight.t(), out=self.fused.x)
+            residual, hidden_states = self.fused(residual.contiguous(), self.post_attention_layernorm_weight,
+                                                 self.post_attention_layernorm_variance_epsilon)
+        else:
+            hidden_states = self.wo(o)
+            if self.process_group is not None:
+                torch.distributed.all_reduce(hidden_states, group=self.process_group)
+            # residual add + post-attention RMSNorm (:229-231) in one pass
+            residual, hidden_states = ops.add_rmsnorm(hidden_states, residual,
+                                                      self.post_attention_layernorm_weight,
+                                                      self.post_attention_layernorm_variance_epsilon)
         return self._mlp(hidden_states, residual).view(bsz, q_len, self.dim)
 
     def _timed(self, name):
