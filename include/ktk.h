@@ -269,19 +269,21 @@ KTK_API int ktk_qkv_norm(const void* proj, const void* wq, const void* wk, float
  *                    buffer (written by its o_proj GEMM) is bound to that multicast object
  *   residual, w      local [rows, cols] (identical on all ranks), [cols]
  *   sum_multicast    multicast address of [rows, cols]: receives residual + sum of the partials
- *   norm_multicast   multicast address of [rows, cols]: receives RMSNorm of that sum
+ *   sum_local        this rank's own mapping of the same buffer (read back for the other ranks' rows)
+ *   norm_local       local [rows, cols]: receives RMSNorm of that sum (computed on every rank)
  *   flag_ptrs        device array of `world` pointers: rank p's flag words, uint32[grid * world],
  *                    zero before the first launch, reachable from every rank (peer memory)
  *   launch_count     local uint32[grid], zero before the first launch (kept by the kernel)
  * grid = ktk_allreduce_grid(rows, world).  rows must divide by world; cols a multiple of 8, <= 8192.
- * Rank r reduces and normalises rows [r*rows/world, (r+1)*rows/world) and multicasts them; the ranks
- * meet in bounded flag barriers before and after (expiry: KTK_STATUS_TIMEOUT in `status`).
+ * Rank r reduces rows [r*rows/world, (r+1)*rows/world) and multicasts their sum; every rank normalises
+ * all rows into its own `norm_local`.  The ranks meet in bounded flag barriers before the reduction
+ * and after the multicast (expiry: KTK_STATUS_TIMEOUT in `status`).
  * All ranks must launch it the same number of times with the same shape.
  */
 KTK_API int32_t ktk_allreduce_grid(int64_t rows, int32_t world);
 KTK_API int ktk_allreduce_add_rmsnorm(const void* x_multicast, const void* residual, const void* w,
-                                      void* sum_multicast, void* norm_multicast, const void* flag_ptrs,
-                                      void* launch_count, int32_t rank, int32_t world, int64_t rows,
+                                      void* sum_multicast, const void* sum_local, void* norm_local,
+                                      const void* flag_ptrs, void* launch_count, int32_t rank, int32_t world, int64_t rows,
                                       int32_t cols, float eps, int32_t* status, void* stream);
 
 /*

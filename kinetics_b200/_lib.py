@@ -78,7 +78,7 @@ _SIGNATURES = {
                                c_int32, c_int32, c_void_p]),
     "ktk_allreduce_grid": (c_int32, [c_int64, c_int32]),
     "ktk_allreduce_add_rmsnorm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                            c_int32, c_int32, c_int64, c_int32, c_float, _i32p, c_void_p]),
+                                            c_void_p, c_int32, c_int32, c_int64, c_int32, c_float, _i32p, c_void_p]),
     "ktk_silu_mul": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
 }
 

@@ -20,7 +20,7 @@ from ._lib import check
 
 class FusedAllReduceNorm:
     """Owns the symmetric buffers of one layer: `x` (the o_proj GEMM writes its partial output here),
-    `sum` and `norm` (what the kernel multicasts back to every rank)."""
+    `sum` (what the kernel multicasts back to every rank) and the local `norm`."""
 
     def __init__(self, group, rows: int, cols: int, dtype, device):
         import torch.distributed._symmetric_memory as symm_mem
@@ -36,16 +36,15 @@ class FusedAllReduceNorm:
             raise ValueError(f"{rows} rows do not divide over {self.world} ranks")
         self.x = symm_mem.empty(rows, cols, dtype=dtype, device=device)
         self.sum = symm_mem.empty(rows, cols, dtype=dtype, device=device)
-        self.norm = symm_mem.empty(rows, cols, dtype=dtype, device=device)
+        self.norm = torch.empty(rows, cols, dtype=dtype, device=device)
         self.flags = symm_mem.empty(self.grid * self.world, dtype=torch.int32, device=device)
         self.flags.zero_()
         self.launch_count = torch.zeros(self.grid, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self._hx = symm_mem.rendezvous(self.x, group)
         self._hs = symm_mem.rendezvous(self.sum, group)
-        self._hn = symm_mem.rendezvous(self.norm, group)
         self._hf = symm_mem.rendezvous(self.flags, group)
-        for h in (self._hx, self._hs, self._hn):
+        for h in (self._hx, self._hs):
             if not h.multicast_ptr:
                 raise RuntimeError("this system gives no NVSwitch multicast mapping: use the NCCL all-reduce")
         torch.cuda.synchronize(device)
@@ -58,7 +57,8 @@ class FusedAllReduceNorm:
         check(_lib.load().ktk_allreduce_add_rmsnorm(
             ctypes.c_void_p(self._hx.multicast_ptr), ctypes.c_void_p(residual.data_ptr()),
             ctypes.c_void_p(weight.data_ptr()), ctypes.c_void_p(self._hs.multicast_ptr),
-            ctypes.c_void_p(self._hn.multicast_ptr), ctypes.c_void_p(self._hf.buffer_ptrs_dev),
+            ctypes.c_void_p(self.sum.data_ptr()), ctypes.c_void_p(self.norm.data_ptr()),
+            ctypes.c_void_p(self._hf.buffer_ptrs_dev),
             ctypes.c_void_p(self.launch_count.data_ptr()), self.rank, self.world, self.rows, self.cols, eps,
             ctypes.c_void_p(self.status.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
         return self.sum, self.norm

@@ -7,9 +7,10 @@
 // rows [r * rows / world, (r + 1) * rows / world):
 //   1. barrier: every rank's X is complete (same-index CTAs of all ranks meet)
 //   2. s = bf16( multimem.ld_reduce.add(X)[row] + residual[row] )   -- the switch adds the partials
-//      n = s * rsqrt(mean(s^2) + eps) * w
-//      multimem.st of s and n: every rank receives the row
-//   3. barrier: the rows of all ranks have landed everywhere
+//      multimem.st of s: every rank receives the row (the only bytes that cross NVLink twice)
+//      n = s * rsqrt(mean(s^2) + eps) * w, from registers, into this rank's own `norm`
+//   3. barrier: the rows of the same-index CTAs of all ranks have landed here
+//   4. the other ranks' rows of `sum` are normalised locally (read from L2) into `norm`
 // The barriers are flags in peer memory (one word per (CTA, source rank)), written with
 // release and polled with acquire at system scope; the values grow from launch to launch
 // (a per-CTA launch counter in local memory), so nothing needs resetting and the kernel can
@@ -20,7 +21,7 @@
 namespace ktk {
 
 constexpr int kCommThreads = 256;
-constexpr int kCommMaxVec = 4;          // 8 elements each: cols <= 8192
+constexpr int kCommMaxVec = 4;          // vectors of 8 elements per thread: cols <= 8192
 constexpr int kCommMaxWorld = 16;
 constexpr uint32_t kCommSpinCap = 1u << 24;   // ~ a second of polling
 
@@ -35,10 +36,11 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 // eight bf16 summed over all ranks by the switch (fp32 accumulation), returned as four bf16x2
 __device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
     uint4 r;
+    // no "memory" clobber: the loads of a row may be in flight together; the barrier before them
+    // (bar.sync) already keeps them behind the flag waits
     asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                 : "l"(mc_addr)
-                 : "memory");
+                 : "l"(mc_addr));
     return r;
 }
 // sixteen bytes to every rank of the multicast object
@@ -68,11 +70,46 @@ __device__ __forceinline__ void cta_barrier_all_ranks(uint32_t* const* flags, in
     __syncthreads();
 }
 
-__global__ void __launch_bounds__(kCommThreads)
+// RMSNorm of one row held in registers (v, the bf16-rounded sum) -> plain stores to this rank's `norm`
+template <int NV>
+__device__ __forceinline__ void norm_row_store(const float (&v)[NV][8], float ss, float* part,
+                                               const __nv_bfloat16* __restrict__ w, __nv_bfloat16* norm_row,
+                                               int nvec, int cols, float eps) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    __syncthreads();                                   // `part` of the previous row has been read
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kCommThreads / 32; ++i) tot += part[i];
+    const float inv = rsqrtf(tot / (float)cols + eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = threadIdx.x + i * kCommThreads;
+        if (c < nvec) {
+            float wv[8];
+            unpack8(__ldg(reinterpret_cast<const uint4*>(w + (size_t)c * 8)), wv);
+            uint4 packed;
+            uint32_t* pw = &packed.x;
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+                const __nv_bfloat162 two = __floats2bfloat162_rn(v[i][e] * inv * wv[e], v[i][e + 1] * inv * wv[e + 1]);
+                pw[e / 2] = *reinterpret_cast<const uint32_t*>(&two);
+            }
+            *reinterpret_cast<uint4*>(norm_row + (size_t)c * 8) = packed;
+        }
+    }
+}
+
+// NV: vectors per thread, cols <= NV * 8 * kCommThreads
+template <int NV>
+__global__ void __launch_bounds__(kCommThreads, 4)
 allreduce_add_rmsnorm_kernel(const __nv_bfloat16* x_mc, const __nv_bfloat16* __restrict__ residual,
-                             const __nv_bfloat16* __restrict__ w, __nv_bfloat16* sum_mc, __nv_bfloat16* norm_mc,
-                             uint32_t* const* flags, uint32_t* launch_count, int rank, int world, int rows,
-                             int cols, float eps, int32_t* status) {
+                             const __nv_bfloat16* __restrict__ w, __nv_bfloat16* sum_mc,
+                             const __nv_bfloat16* sum_local, __nv_bfloat16* norm_local, uint32_t* const* flags,
+                             uint32_t* launch_count, int rank, int world, int rows, int cols, float eps,
+                             int32_t* status) {
     __shared__ float part[kCommThreads / 32];
     __shared__ uint32_t s_epoch;
     if (threadIdx.x == 0) s_epoch = launch_count[blockIdx.x];
@@ -83,17 +120,29 @@ allreduce_add_rmsnorm_kernel(const __nv_bfloat16* x_mc, const __nv_bfloat16* __r
 
     const int per = rows / world;
     const int nvec = cols / 8;
+    // the rows this rank owns: reduce through the switch, add the residual, multicast the sum,
+    // normalise from registers
     for (int r = rank * per + blockIdx.x; r < (rank + 1) * per; r += gridDim.x) {
-        float v[kCommMaxVec][8];
+        float v[NV][8];
         float ss = 0.0f;
+        uint4 xr[NV], tr[NV];
 #pragma unroll
-        for (int i = 0; i < kCommMaxVec; ++i) {
+        for (int i = 0; i < NV; ++i) {          // all of the row's loads first
+            const int c = threadIdx.x + i * kCommThreads;
+            if (c < nvec) {
+                const size_t off = (size_t)r * cols + (size_t)c * 8;
+                xr[i] = multimem_ld_reduce_bf16x8(x_mc + off);
+                tr[i] = __ldg(reinterpret_cast<const uint4*>(residual + off));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
             const int c = threadIdx.x + i * kCommThreads;
             if (c < nvec) {
                 const size_t off = (size_t)r * cols + (size_t)c * 8;
                 float x[8], t[8];
-                unpack8(multimem_ld_reduce_bf16x8(x_mc + off), x);
-                unpack8(*reinterpret_cast<const uint4*>(residual + off), t);
+                unpack8(xr[i], x);
+                unpack8(tr[i], t);
                 uint4 packed;
                 uint32_t* pw = &packed.x;
 #pragma unroll
@@ -102,40 +151,41 @@ allreduce_add_rmsnorm_kernel(const __nv_bfloat16* x_mc, const __nv_bfloat16* __r
                     pw[e / 2] = *reinterpret_cast<const uint32_t*>(&two);
                 }
                 multimem_st_16(sum_mc + off, packed);
-                unpack8(packed, v[i]);                     // normalise the rounded sum, as if it had been re-read
+                unpack8(packed, v[i]);                     // normalise the rounded sum, as a reader of `sum` would
 #pragma unroll
                 for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
             }
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        __syncthreads();                                   // `part` of the previous row has been read
-        if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
-        __syncthreads();
-        float tot = 0.0f;
-#pragma unroll
-        for (int i = 0; i < kCommThreads / 32; ++i) tot += part[i];
-        const float inv = rsqrtf(tot / (float)cols + eps);
-#pragma unroll
-        for (int i = 0; i < kCommMaxVec; ++i) {
-            const int c = threadIdx.x + i * kCommThreads;
-            if (c < nvec) {
-                float wv[8];
-                unpack8(*reinterpret_cast<const uint4*>(w + (size_t)c * 8), wv);
-                uint4 packed;
-                uint32_t* pw = &packed.x;
-#pragma unroll
-                for (int e = 0; e < 8; e += 2) {
-                    const __nv_bfloat162 two =
-                        __floats2bfloat162_rn(v[i][e] * inv * wv[e], v[i][e + 1] * inv * wv[e + 1]);
-                    pw[e / 2] = *reinterpret_cast<const uint32_t*>(&two);
-                }
-                multimem_st_16(norm_mc + (size_t)r * cols + (size_t)c * 8, packed);
-            }
-        }
+        norm_row_store<NV>(v, ss, part, w, norm_local + (size_t)r * cols, nvec, cols, eps);
     }
     __threadfence_system();                                // this CTA's rows are on their way to every rank
-    cta_barrier_all_ranks(flags, rank, world, 2 * epoch + 2, status);     // and so are everybody else's
+    cta_barrier_all_ranks(flags, rank, world, 2 * epoch + 2, status);     // and so are the same-index CTAs' rows
+
+    // the rows the same-index CTAs of the other ranks sent: normalise them from this rank's copy of `sum`
+    // (read at L2, where the peers' stores land)
+    for (int p = 1; p < world; ++p) {
+        const int owner = (rank + p) % world;
+        for (int r = owner * per + blockIdx.x; r < (owner + 1) * per; r += gridDim.x) {
+            float v[NV][8];
+            float ss = 0.0f;
+            uint4 sr[NV];
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                const int c = threadIdx.x + i * kCommThreads;
+                if (c < nvec) sr[i] = __ldcg(reinterpret_cast<const uint4*>(sum_local + (size_t)r * cols + (size_t)c * 8));
+            }
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                const int c = threadIdx.x + i * kCommThreads;
+                if (c < nvec) {
+                    unpack8(sr[i], v[i]);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+                }
+            }
+            norm_row_store<NV>(v, ss, part, w, norm_local + (size_t)r * cols, nvec, cols, eps);
+        }
+    }
     if (threadIdx.x == 0) launch_count[blockIdx.x] = epoch + 1;
 }
 
@@ -146,12 +196,13 @@ using namespace ktk;
 extern "C" int32_t ktk_allreduce_grid(int64_t rows, int32_t world) {
     if (rows <= 0 || world <= 0) return 0;
     const int64_t per = rows / world;
-    const int64_t cap = sm_count();
+    const int64_t cap = 4LL * sm_count();        // four 256-thread CTAs fit an SM: every CTA is resident
     return (int32_t)(per < cap ? per : cap);
 }
 
 extern "C" int ktk_allreduce_add_rmsnorm(const void* x_multicast, const void* residual, const void* w,
-                                         void* sum_multicast, void* norm_multicast, const void* flag_ptrs,
+                                         void* sum_multicast, const void* sum_local, void* norm_local,
+                                         const void* flag_ptrs,
                                          void* launch_count, int32_t rank, int32_t world, int64_t rows,
                                          int32_t cols, float eps, int32_t* status, void* stream) {
     if (world < 2 || world > kCommMaxWorld || rank < 0 || rank >= world || rows <= 0 || cols <= 0) {
@@ -159,7 +210,7 @@ extern "C" int ktk_allreduce_add_rmsnorm(const void* x_multicast, const void* re
                   (long long)rows, cols);
         return KTK_ERR_ARG;
     }
-    if (!x_multicast || !residual || !w || !sum_multicast || !norm_multicast || !flag_ptrs || !launch_count) {
+    if (!x_multicast || !residual || !w || !sum_multicast || !sum_local || !norm_local || !flag_ptrs || !launch_count) {
         set_error("ktk_allreduce_add_rmsnorm: null pointer argument");
         return KTK_ERR_ARG;
     }
@@ -169,13 +220,19 @@ extern "C" int ktk_allreduce_add_rmsnorm(const void* x_multicast, const void* re
         return KTK_ERR_UNSUPPORTED;
     }
     const uintptr_t al = (uintptr_t)x_multicast | (uintptr_t)residual | (uintptr_t)w | (uintptr_t)sum_multicast |
-                         (uintptr_t)norm_multicast;
+                         (uintptr_t)sum_local | (uintptr_t)norm_local;
     if ((al & 15u) != 0) { set_error("ktk_allreduce_add_rmsnorm: pointers must be 16-byte aligned"); return KTK_ERR_ARG; }
     const int grid = ktk_allreduce_grid(rows, world);
-    allreduce_add_rmsnorm_kernel<<<grid, kCommThreads, 0, (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)x_multicast, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w,
-        (__nv_bfloat16*)sum_multicast, (__nv_bfloat16*)norm_multicast, (uint32_t* const*)flag_ptrs,
-        (uint32_t*)launch_count, rank, world, (int)rows, cols, eps, status);
+    const int nv = (cols + 8 * kCommThreads - 1) / (8 * kCommThreads);
+#define KTK_COMM_LAUNCH(NV)                                                                                   \
+    allreduce_add_rmsnorm_kernel<NV><<<grid, kCommThreads, 0, (cudaStream_t)stream>>>(                        \
+        (const __nv_bfloat16*)x_multicast, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w,           \
+        (__nv_bfloat16*)sum_multicast, (const __nv_bfloat16*)sum_local, (__nv_bfloat16*)norm_local,           \
+        (uint32_t* const*)flag_ptrs, (uint32_t*)launch_count, rank, world, (int)rows, cols, eps, status)
+    if (nv <= 1) KTK_COMM_LAUNCH(1);
+    else if (nv == 2) KTK_COMM_LAUNCH(2);
+    else KTK_COMM_LAUNCH(4);
+#undef KTK_COMM_LAUNCH
     KTK_CUDA_TRY(cudaGetLastError(), "ktk_allreduce_add_rmsnorm");
     return KTK_OK;
 }

@@ -44,6 +44,34 @@ def main():
     torch.cuda.synchronize()
     if rank == 0:
         print(f"fused all-reduce ok on {world} ranks, max |sum - ref| {worst:.4f}", flush=True)
+    if os.environ.get("KTK_TIME_ALLREDUCE"):
+        # the layer's shape: 4096 x 4096 bf16 = 32 MiB per rank
+        from kinetics_b200 import ops
+        big = FusedAllReduceNorm(dist.group.WORLD, 4096, 4096, torch.bfloat16, dev)
+        res = torch.randn(4096, 4096, device=dev).to(torch.bfloat16)
+        wb = torch.ones(4096, device=dev, dtype=torch.bfloat16)
+        part = torch.randn(4096, 4096, device=dev).to(torch.bfloat16)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+        def timed(fn, n=50):
+            for _ in range(5):
+                fn()
+            dist.barrier(); torch.cuda.synchronize()
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record(); torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / n
+
+        t_fused = timed(lambda: big(res, wb, eps))
+
+        def nccl_path():
+            dist.all_reduce(part)
+            ops.add_rmsnorm(part, res, wb, eps)
+
+        t_nccl = timed(nccl_path)
+        if rank == 0:
+            print(f"32 MiB: fused kernel {t_fused * 1e3:.1f} us, NCCL all-reduce + add_rmsnorm {t_nccl * 1e3:.1f} us", flush=True)
     sys.stdout.flush()
     os._exit(0)
 
