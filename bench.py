@@ -63,8 +63,11 @@ def parse():
     ap.add_argument("--page-table", default="interleaved", choices=["interleaved", "random"])
     ap.add_argument("--seed", type=int, default=1236)
     ap.add_argument("--cpu-sample", type=int, default=32, help="sequences in the CPU sample")
-    ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
-                    help="N > 1: sum the o_proj partials with the fused multicast kernel, or with NCCL")
+    ap.add_argument("--allreduce", default="auto", choices=["auto", "fused", "nccl"],
+                    help="N > 1: sum the o_proj partials with the fused multicast kernel (all-reduce + residual add "
+                         "+ RMSNorm in one launch), or with NCCL followed by the add + norm kernel.  auto: fused "
+                         "from 4 ranks up (at 2 ranks both directions of the link carry 1.5x NCCL's bytes and the "
+                         "two measure the same)")
     ap.add_argument("--micro", default="", choices=["", "select"],
                     help="time one kernel alone on the workload's shapes (select: only the page summaries are "
                          "allocated, so the full batch fits in a few GB)")
@@ -203,6 +206,12 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def use_fused_allreduce(args, world):
+    if world < 2 or args.allreduce == "nccl":
+        return False
+    return args.allreduce == "fused" or world >= 4
+
+
 def workload_config(args, wl, n_gpus):
     return {
         "workload": (f"{args.workload}: {wl['model']} decoder layer, 8-way KV-head shard per GPU "
@@ -211,7 +220,9 @@ def workload_config(args, wl, n_gpus):
         "batch": wl["batch"], "context": wl["ctx"], "page_size": PAGE, "topk_pages": wl["topk"],
         "tp_shards_total": wl["tp"], "shards_resident": n_gpus, "page_table": args.page_table,
         "l2": "per-step traffic (summaries + selected pages) exceeds the 126 MB L2; no flush needed",
-        "parallelism": f"tp{wl['tp']} by KV head, {n_gpus} shard(s) resident, o_proj all-reduce over NCCL"
+        "parallelism": f"tp{wl['tp']} by KV head, {n_gpus} shard(s) resident, o_proj all-reduce: "
+                       + ("fused multicast kernel (all-reduce + add + RMSNorm)" if use_fused_allreduce(args, n_gpus)
+                          else "NCCL")
                        if n_gpus > 1 else f"tp{wl['tp']} by KV head, 1 shard resident",
     }
 
@@ -261,7 +272,7 @@ def run_ours(args):
         layer = cls(config=cfg, world_size=tp, batch_size=B, prefix_len=ctx, max_len=ctx + 512, page_size=PAGE,
                     device=device, dtype=dtype, page_table=args.page_table, process_group=pg,
                     seed=args.seed + rank, variant=args.variant, context_lens=ctx_lens,
-                    fused_allreduce=(world > 1 and args.allreduce == "fused"), **kw)
+                    fused_allreduce=use_fused_allreduce(args, world), **kw)
         for m in layer.modules():
             if isinstance(m, torch.nn.Linear):
                 torch.nn.init.normal_(m.weight, 0.0, 0.02)

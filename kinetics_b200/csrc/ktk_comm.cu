@@ -9,8 +9,9 @@
 //   2. s = bf16( multimem.ld_reduce.add(X)[row] + residual[row] )   -- the switch adds the partials
 //      multimem.st of s: every rank receives the row (the only bytes that cross NVLink twice)
 //      n = s * rsqrt(mean(s^2) + eps) * w, from registers, into this rank's own `norm`
-//   3. barrier: the rows of the same-index CTAs of all ranks have landed here
-//   4. the other ranks' rows of `sum` are normalised locally (read from L2) into `norm`
+//   3. signal: this CTA's rows are on their way to every rank
+//   4. owner by owner, as the same-index CTA of that rank signals: its rows of `sum` are normalised
+//      locally (read from L2) into `norm`
 // The barriers are flags in peer memory (one word per (CTA, source rank)), written with
 // release and polled with acquire at system scope; the values grow from launch to launch
 // (a per-CTA launch counter in local memory), so nothing needs resetting and the kernel can
@@ -51,22 +52,29 @@ __device__ __forceinline__ void multimem_st_16(void* mc_addr, const uint4& v) {
                  : "memory");
 }
 
-// Same-index CTAs of all ranks meet: tell every peer that this rank reached `value`, then wait
-// until every peer said the same.  flags[p] is rank p's flag array, [CTA][source rank].
-__device__ __forceinline__ void cta_barrier_all_ranks(uint32_t* const* flags, int rank, int world, uint32_t value,
-                                                      int32_t* status) {
+// Same-index CTAs of all ranks signal one another: flags[p] is rank p's flag array, [CTA][source rank].
+// Tell every peer that this CTA reached `value` (all of the CTA's earlier writes come first).
+__device__ __forceinline__ void cta_signal_all_ranks(uint32_t* const* flags, int rank, int world, uint32_t value) {
     __syncthreads();
-    if ((int)threadIdx.x < world) {
-        const int peer = threadIdx.x;
-        st_release_sys(flags[peer] + (size_t)blockIdx.x * world + rank, value);
-        const uint32_t* mine = flags[rank] + (size_t)blockIdx.x * world + peer;
-        bool ok = false;
-        for (uint32_t i = 0; i < kCommSpinCap; ++i) {
-            if ((int32_t)(ld_acquire_sys(mine) - value) >= 0) { ok = true; break; }
-            if (i > 64) __nanosleep(64);
-        }
-        if (!ok) report(status, KTK_STATUS_TIMEOUT);
+    if ((int)threadIdx.x < world)
+        st_release_sys(flags[threadIdx.x] + (size_t)blockIdx.x * world + rank, value);
+}
+// Wait until the same-index CTA of rank `src` said `value` (bounded).
+__device__ __forceinline__ void flag_wait(const uint32_t* mine, uint32_t value, int32_t* status) {
+    for (uint32_t i = 0; i < kCommSpinCap; ++i) {
+        if ((int32_t)(ld_acquire_sys(mine) - value) >= 0) return;
+        if (i > 64) __nanosleep(64);
     }
+    report(status, KTK_STATUS_TIMEOUT);
+}
+__device__ __forceinline__ void cta_wait_rank(uint32_t* const* flags, int rank, int world, int src, uint32_t value,
+                                              int32_t* status) {
+    if (threadIdx.x == 0) flag_wait(flags[rank] + (size_t)blockIdx.x * world + src, value, status);
+    __syncthreads();
+}
+__device__ __forceinline__ void cta_wait_all_ranks(uint32_t* const* flags, int rank, int world, uint32_t value,
+                                                   int32_t* status) {
+    if ((int)threadIdx.x < world) flag_wait(flags[rank] + (size_t)blockIdx.x * world + threadIdx.x, value, status);
     __syncthreads();
 }
 
@@ -116,7 +124,8 @@ allreduce_add_rmsnorm_kernel(const __nv_bfloat16* x_mc, const __nv_bfloat16* __r
     __syncthreads();
     const uint32_t epoch = s_epoch;
 
-    cta_barrier_all_ranks(flags, rank, world, 2 * epoch + 1, status);     // every rank's partial output is complete
+    cta_signal_all_ranks(flags, rank, world, 2 * epoch + 1);
+    cta_wait_all_ranks(flags, rank, world, 2 * epoch + 1, status);        // every rank's partial output is complete
 
     const int per = rows / world;
     const int nvec = cols / 8;
@@ -159,12 +168,14 @@ allreduce_add_rmsnorm_kernel(const __nv_bfloat16* x_mc, const __nv_bfloat16* __r
         norm_row_store<NV>(v, ss, part, w, norm_local + (size_t)r * cols, nvec, cols, eps);
     }
     __threadfence_system();                                // this CTA's rows are on their way to every rank
-    cta_barrier_all_ranks(flags, rank, world, 2 * epoch + 2, status);     // and so are the same-index CTAs' rows
+    cta_signal_all_ranks(flags, rank, world, 2 * epoch + 2);
 
-    // the rows the same-index CTAs of the other ranks sent: normalise them from this rank's copy of `sum`
-    // (read at L2, where the peers' stores land)
+    // the rows the same-index CTAs of the other ranks sent, one owner after another as its flag arrives:
+    // normalise them from this rank's copy of `sum` (read at L2, where the peers' stores land).  Having
+    // seen every peer's second flag also means that no peer still reads this rank's `x`.
     for (int p = 1; p < world; ++p) {
         const int owner = (rank + p) % world;
+        cta_wait_rank(flags, rank, world, owner, 2 * epoch + 2, status);
         for (int r = owner * per + blockIdx.x; r < (owner + 1) * per; r += gridDim.x) {
             float v[NV][8];
             float ss = 0.0f;
