@@ -41,6 +41,9 @@ WORKLOADS = {
     "cfg4-shard": dict(model="Qwen3-32B", tp=8, batch=1024, ctx=8192, topk=64),
     # configs[3]: ragged contexts uniform in [1024, 16384], fragmented (randomly permuted) page pool, GQA 8
     "cfg4-ragged": dict(model="Qwen3-32B", tp=8, batch=1024, ctx=16384, topk=64, ragged=(1024, 16384)),
+    # configs[4]: Qwen3-1.7B (GQA 2, all 8 KV heads on one GPU), 512 sequences with contexts uniform in
+    # [512, 32768]; a tenth of them sit on a page boundary, so the step opens a new page for those
+    "cfg5-tp1": dict(model="Qwen3-1.7B", tp=1, batch=512, ctx=32768, topk=32, ragged=(512, 32768), boundary=0.1),
     "tiny": dict(model="Qwen3-8B", tp=8, batch=64, ctx=2048, topk=16),
 }
 PAGE = 16
@@ -214,9 +217,11 @@ def use_fused_allreduce(args, world):
 
 def workload_config(args, wl, n_gpus):
     return {
-        "workload": (f"{args.workload}: {wl['model']} decoder layer, 8-way KV-head shard per GPU "
-                     f"(tp={wl['tp']}), batch {wl['batch']}, context {wl['ctx']}, page {PAGE}, "
-                     f"top-k {wl['topk']} pages, one decode step"),
+        "workload": (f"{args.workload}: {wl['model']} decoder layer, "
+                     + (f"{wl['tp']}-way KV-head shard per GPU" if wl["tp"] > 1 else "all KV heads on one GPU")
+                     + f" (tp={wl['tp']}), batch {wl['batch']}, context "
+                     + (f"uniform in {list(wl['ragged'])}" if "ragged" in wl else str(wl["ctx"]))
+                     + f", page {PAGE}, top-k {wl['topk']} pages, one decode step"),
         "batch": wl["batch"], "context": wl["ctx"], "page_size": PAGE, "topk_pages": wl["topk"],
         "tp_shards_total": wl["tp"], "shards_resident": n_gpus, "page_table": args.page_table,
         "l2": "per-step traffic (summaries + selected pages) exceeds the 126 MB L2; no flush needed",
@@ -266,6 +271,10 @@ def run_ours(args):
         lo, hi = wl["ragged"]
         gl = torch.Generator().manual_seed(args.seed)            # the same lengths on every rank
         ctx_lens = torch.randint(lo, hi + 1, (B,), generator=gl)
+        on_boundary = int(round(wl.get("boundary", 0.0) * B))
+        if on_boundary:
+            pick = torch.randperm(B, generator=gl)[:on_boundary]
+            ctx_lens[pick] = ctx_lens[pick] // PAGE * PAGE
         args.page_table = "random"
 
     def make(cls, **kw):

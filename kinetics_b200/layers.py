@@ -125,8 +125,9 @@ class _PagedDecoderLayer(nn.Module):
 
         # paged KV state: prefix fills num_pages_per_req pages, the step appends into one more.
         # `context_lens` (one prefix length per sequence) makes the batch ragged: sequence b then owns
-        # context_lens[b] // page_size full pages plus the page the step writes into, laid out as one
-        # CSR list over a randomly permuted ("fragmented") or packed page pool.
+        # context_lens[b] // page_size full pages plus the page the step writes into (which already holds
+        # context_lens[b] % page_size tokens; a multiple of the page size means the step opens a new
+        # page), laid out as one CSR list over a randomly permuted ("fragmented") or packed page pool.
         self.max_num_pages = max_num_pages = max_len // page_size
         self.total_pages = max_num_pages * batch_size
         if context_lens is None:
@@ -162,7 +163,10 @@ class _PagedDecoderLayer(nn.Module):
             self.paged_kv_indices = ids.to(torch.int32).to(device).contiguous()
             self.full_kv_indptr = indptr.to(torch.int32).to(device)
         self.context_lens = context_lens
-        self.last_kv_lens = torch.ones(batch_size, dtype=torch.int32, device=device)
+        if context_lens is None:
+            self.last_kv_lens = torch.ones(batch_size, dtype=torch.int32, device=device)
+        else:
+            self.last_kv_lens = (lens % page_size + 1).to(torch.int32).to(device)
         self.qkv_indptr = torch.arange(batch_size + 1, dtype=torch.int32, device=device)
         self.status = ops.new_status(device)
 

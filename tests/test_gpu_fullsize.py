@@ -116,3 +116,63 @@ def test_append_then_select_sees_the_new_page_summary(cuda_device):
     for t in range(16):
         acc = acc + keys[t].float()
     assert torch.equal(summ[:, :, 0].float(), (acc / 16).to(torch.bfloat16).float())
+
+
+def test_ragged_gqa2_properties_at_the_cfg5_shape(cuda_device):
+    # BASELINE.json configs[4] at TP=1: Qwen3-1.7B heads (8 KV heads, 2 query heads each), 512 sequences,
+    # contexts uniform in [512, 32768], 51 of them on a page boundary (the step opens a new page), top-k 32.
+    # The physical pool is smaller than the logical page count (ids are reused): the kernels only read it.
+    from kinetics_b200 import ops
+    B, Hkv, G, k, pool = 512, 8, 2, 32, 32768
+    g = torch.Generator(device="cpu").manual_seed(1238)
+    lens = torch.randint(512, 32768 + 1, (B,), generator=g)
+    pick = torch.randperm(B, generator=g)[:51]
+    lens[pick] = lens[pick] // 16 * 16
+    n_full = lens // 16                                   # scored pages; the step writes into page n_full
+    counts = n_full + 1
+    indptr_c = torch.zeros(B + 1, dtype=torch.int64)
+    indptr_c[1:] = torch.cumsum(counts, 0)
+    total = int(indptr_c[-1])
+    indices = torch.randint(0, pool, (total,), generator=g).to(torch.int32).to(cuda_device)
+    indptr = indptr_c.to(torch.int32).to(cuda_device)
+    last = (lens % 16 + 1).to(torch.int32).to(cuda_device)
+    stride = int(counts.max())
+    torch.manual_seed(14)
+    cache = torch.randn(pool, 2, 16, Hkv, 128, device=cuda_device, dtype=torch.bfloat16)
+    summ = torch.randn(B, Hkv, stride, 128, device=cuda_device, dtype=torch.bfloat16)
+    q = torch.randn(B, Hkv * G, 128, device=cuda_device, dtype=torch.bfloat16)
+    status = ops.new_status(cuda_device)
+    logical = torch.empty(B, Hkv, k + 1, dtype=torch.int32, device=cuda_device)
+    scores = torch.full((B, Hkv, stride), float("nan"), device=cuda_device)
+    phys = ops.select_pages(q, summ, indices, indptr, last, k, pool, out_logical=logical, out_scores=scores,
+                            status=status)
+    ops.raise_on_status(status)
+
+    nf = n_full.to(cuda_device)
+    col = torch.arange(stride, device=cuda_device)
+    valid = col[None, None, :] < nf[:, None, None]                       # [B, 1, stride]
+    ref = torch.einsum("bhgd,bhnd->bhn", q.view(B, Hkv, G, 128).float(), summ.float()) / G
+    assert torch.allclose(torch.where(valid, scores, 0.0), torch.where(valid, ref, 0.0), atol=2e-4, rtol=1e-5)
+    assert torch.isnan(scores[~valid.expand_as(scores)]).all()           # nothing past the scored pages is written
+    # every row: the k best of its own scored pages in (score descending, page ascending) order, then the last page
+    masked = torch.where(valid, scores + 0.0, float("-inf"))
+    order = torch.sort(-masked, dim=2, stable=True).indices[:, :, :k]
+    assert int(n_full.min()) >= k                                        # every sequence here has more than k pages
+    assert torch.equal(logical[:, :, :k].long(), order)
+    assert torch.equal(logical[:, :, k].long(), nf[:, None].expand(B, Hkv))
+    flat = indptr[:-1].long()[:, None, None] + logical.long()
+    assert torch.equal(phys.long(), indices.long()[flat])
+
+    out = ops.sparse_decode(q, cache, phys, indptr, last, status=status)
+    ops.raise_on_status(status)
+    # fp32 torch attention over the listed pages for a sample of sequences (both page-boundary and mid-page ones)
+    sample = torch.cat([pick[:4], torch.arange(0, B, 37)]).tolist()
+    for b in sample:
+        kv = cache[phys[b].long()]                                       # [Hkv, k+1, 2, 16, Hkv, 128]
+        ntok = k * 16 + int(last[b])
+        for h in range(Hkv):
+            keys = kv[h, :, 0, :, h, :].reshape(-1, 128)[:ntok].float()
+            vals = kv[h, :, 1, :, h, :].reshape(-1, 128)[:ntok].float()
+            qq = q[b, h * G:(h + 1) * G].float()
+            p = torch.softmax(qq @ keys.t() / math.sqrt(128), dim=-1)
+            torch.testing.assert_close(out[b, h * G:(h + 1) * G].float(), p @ vals, rtol=2e-2, atol=2e-2)
