@@ -71,6 +71,10 @@ def parse():
                          "+ RMSNorm in one launch), or with NCCL followed by the add + norm kernel.  auto: fused "
                          "from 4 ranks up (at 2 ranks both directions of the link carry 1.5x NCCL's bytes and the "
                          "two measure the same)")
+    ap.add_argument("--flashinfer", action="store_true",
+                    help="also time, on the same cache and lists, the library kernels the reference uses on a GPU: "
+                         "flashinfer's paged batch decode (sparse list and dense table) and the reference's torch "
+                         "selection statements; reported under \"library_bar\", never part of the headline")
     ap.add_argument("--micro", default="", choices=["", "select"],
                     help="time one kernel alone on the workload's shapes (select: only the page summaries are "
                          "allocated, so the full batch fits in a few GB)")
@@ -230,6 +234,65 @@ def workload_config(args, wl, n_gpus):
                           else "NCCL")
                        if n_gpus > 1 else f"tp{wl['tp']} by KV head, 1 shard resident",
     }
+
+
+# ------------------------------------------------------------------------------------------
+# the reference's GPU statements and library, for comparison (not the product, not the headline)
+# ------------------------------------------------------------------------------------------
+
+def library_bar_run(layer, hidden, B, hkv, hq, topk, device, with_dense=True, iters=10):
+    """Times, with CUDA events, what the reference executes on a GPU for the same step:
+    its selection statements in torch (benchmark/blocktopk_decoder.py:216-221, one KV head) and
+    flashinfer's BatchDecodeWithPagedKVCacheWrapper (:153-160,176-178,255-265) over the selected list and,
+    for the dense layer (dense_decoder.py:149-156,168-170), over the whole page table."""
+    import flashinfer
+    layer.capture = {}
+    layer.forward(hidden)
+    q = layer.capture["q"].contiguous()                        # [B, Hq, D]
+    layer.capture = None
+    n = layer.num_pages_per_req
+    G = hq // hkv
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    out = {"flashinfer": flashinfer.__version__}
+    summ = layer.compressed_key_cache[:, 0, :n].contiguous()   # [B, n, D], KV head 0
+    qg = q.view(B, hkv, G, -1)[:, 0]                           # [B, G, D]
+    table = layer.page_table.long()                            # [B, n+1]
+
+    def torch_select():
+        csim = torch.einsum("bgd,bnd->bgn", qg, summ).mean(dim=1)
+        idx = csim.topk(k=topk, dim=-1).indices
+        phys = torch.gather(table[:, :n], 1, idx)
+        return torch.cat([phys, table[:, n:]], dim=-1).to(torch.int32)
+
+    out["torch_select_ms"] = timed(torch_select)
+    ws = torch.empty(128 * 1024 * 1024, dtype=torch.uint8, device=device)
+    sel = layer.topk_page_indices.view(B, hkv, topk + 1)[:, 0].contiguous().view(-1)
+    sel_indptr = torch.arange(B + 1, dtype=torch.int32, device=device) * (topk + 1)
+    for name, tc in (("cuda_cores", False), ("tensor_cores", True)):
+        try:
+            w = flashinfer.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD", use_tensor_cores=tc)
+            w.plan(sel_indptr, sel, layer.last_kv_lens, hq, hkv, HEAD_DIM, PAGE, pos_encoding_mode="NONE",
+                   q_data_type=q.dtype, kv_data_type=layer.kv_cache.dtype)
+            out[f"flashinfer_sparse_decode_ms_{name}"] = timed(lambda: w.run(q, layer.kv_cache))
+            if with_dense:
+                w.plan(layer.full_kv_indptr, layer.paged_kv_indices, layer.last_kv_lens, hq, hkv, HEAD_DIM, PAGE,
+                       pos_encoding_mode="NONE", q_data_type=q.dtype, kv_data_type=layer.kv_cache.dtype)
+                out[f"flashinfer_dense_decode_ms_{name}"] = timed(lambda: w.run(q, layer.kv_cache))
+        except Exception as e:                                  # the library could not build or run its kernel
+            out[f"flashinfer_{name}_error"] = str(e)[:200]
+    return out
 
 
 # ------------------------------------------------------------------------------------------
@@ -459,6 +522,12 @@ def run_ours(args):
         dense.check_status()
         del dense
 
+    # ---- the library kernels the reference itself runs on a GPU, on the same cache (comparison only) ----
+    library_bar = None
+    if args.flashinfer and world == 1 and ctx_lens is None:
+        library_bar = library_bar_run(sparse, static_in, B, hkv, cfg.num_attention_heads // tp, topk, device,
+                                      with_dense=not args.no_dense)
+
     # ---- CPU baseline (rank 0, single-GPU run only) ----
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu and ctx_lens is None:
@@ -474,7 +543,7 @@ def run_ours(args):
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(args, wl, world), "roofline": roofline, "kernels": kernels,
-            "cpu_baseline": cpu, "e2e": e2e, "dense": dense_info,
+            "cpu_baseline": cpu, "e2e": e2e, "dense": dense_info, "library_bar": library_bar,
             "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
             "clocks": sampler.summary(),
         }

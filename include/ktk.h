@@ -66,6 +66,10 @@ extern "C" {
 #define KTK_VARIANT_SIMT 1       /* fp32 FMA path (the only one for KTK_F32)     */
 #define KTK_VARIANT_MMA 2        /* bf16 tensor-core path with TMA-staged pages  */
 
+/* num_splits value: cut the concatenated page lists evenly over one CTA per resident slot
+ * (bf16 tensor-core path only); see ktk_decode_num_splits */
+#define KTK_SPLITS_BALANCED (-1)
+
 typedef struct ktk_shape {
     int32_t batch;          /* B: sequences in this step                         */
     int32_t num_kv_heads;   /* Hkv, local to this GPU                            */
@@ -166,6 +170,12 @@ KTK_API int ktk_select(const void* q, const void* summaries, int64_t summary_str
  * the workspace size that count needs.  `max_entries` = largest number of pages
  * one (sequence, kv head) attends (topk+1 for sparse, max pages per sequence
  * for dense).  Host-only, no CUDA call except a cached device-attribute query.
+ * For bf16 the answer is KTK_SPLITS_BALANCED: the grid is one CTA per resident slot
+ * and the concatenation of all page lists (each padded to `max_entries`) is cut into
+ * equal chunks, so that every SM finishes at the same time whatever the batch size;
+ * a list that crosses a cut is merged by a second small launch.  Its workspace is a
+ * few MB (two partial slots per CTA) and does not depend on the batch.  For fp32 the
+ * answer is a per-list split count >= 1.
  * flashinfer's analogue is the 128 MB workspace + plan()
  * (benchmark/blocktopk_decoder.py:152, :255-265).
  */
@@ -181,8 +191,9 @@ KTK_API size_t ktk_decode_workspace_bytes(const ktk_shape* shape, int32_t num_sp
  * o[b, h*G+g, :] = softmax_s(q . K_s * sm_scale) . V_s over the tokens of the
  * pages listed in sel_pages[b, h, 0..cnt), cnt = min(topk, n_pages-1) + 1; the last
  * listed page is masked to kv_last_page_len[b] tokens.  fp32 accumulation.
- *   num_splits 0 = ktk_decode_num_splits(); >1 needs `workspace` of
- *   ktk_decode_workspace_bytes() bytes (partials + a second combine launch).
+ *   num_splits 0 = ktk_decode_num_splits(); > 1 (that many CTAs per list) and
+ *   KTK_SPLITS_BALANCED need `workspace` of ktk_decode_workspace_bytes() bytes
+ *   (partials + a second combine launch); 1 needs none.
  */
 KTK_API int ktk_sparse_decode(const void* q, const void* kv_cache, const int32_t* sel_pages,
                       int32_t topk, const int32_t* kv_indptr,
@@ -222,7 +233,8 @@ KTK_API int ktk_sparse_decode_noalloc(const void* q, const void* kv_cache, const
 
 /*
  * Dense paged decode over all pages of each sequence (the baseline the sparse
- * path is compared with).
+ * path is compared with).  max_pages_per_seq must be >= every sequence's page count
+ * (a longer list is clipped and flagged KTK_STATUS_BAD_TABLE by the balanced partition).
  * Replaces: benchmark/dense_decoder.py:149-156, :168-170, :178-189.
  */
 KTK_API int ktk_dense_decode(const void* q, const void* kv_cache, const int32_t* kv_indices,

@@ -7,7 +7,7 @@
 // row is one coalesced 256-byte (bf16) warp load straight from HBM, and the
 // next page of the warp is already in flight in registers while the current
 // one is being reduced.  The four warps merge through shared memory.
-#include "ktk_decode.cuh"
+#include "ktk_decode_mma.cuh"
 
 namespace ktk {
 
@@ -294,8 +294,8 @@ static int decode_common(const char* who, const void* q, const void* cache, cons
         set_error("%s: null pointer argument", who);
         return KTK_ERR_ARG;
     }
-    if (num_splits < 0 || num_splits > 256) {
-        set_error("%s: num_splits %d outside [0, 256]", who, num_splits);
+    if (num_splits < KTK_SPLITS_BALANCED || num_splits > 256) {
+        set_error("%s: num_splits %d outside [0, 256] and not KTK_SPLITS_BALANCED", who, num_splits);
         return KTK_ERR_ARG;
     }
     if (variant != KTK_VARIANT_AUTO && variant != KTK_VARIANT_SIMT && variant != KTK_VARIANT_MMA) {
@@ -306,8 +306,14 @@ static int decode_common(const char* who, const void* q, const void* cache, cons
         set_error("%s: the tensor-core variant is bf16 only", who);
         return KTK_ERR_UNSUPPORTED;
     }
-    if (num_splits == 0) num_splits = ktk_decode_num_splits(s, max_entries);
-    const int64_t ctas = (int64_t)s->batch * s->num_kv_heads * num_splits;
+    const bool tensor_cores = s->dtype == KTK_BF16 && variant != KTK_VARIANT_SIMT;
+    if (num_splits == KTK_SPLITS_BALANCED && !tensor_cores) {
+        set_error("%s: the balanced partition exists for the bf16 tensor-core variant only", who);
+        return KTK_ERR_UNSUPPORTED;
+    }
+    if (num_splits == 0) num_splits = policy_num_splits(s, variant, max_entries);
+    const bool balanced = num_splits == KTK_SPLITS_BALANCED;
+    const int64_t ctas = balanced ? 1 : (int64_t)s->batch * s->num_kv_heads * num_splits;
     if (ctas > 2147483647LL) {
         set_error("%s: batch * num_kv_heads * num_splits exceeds the grid limit", who);
         return KTK_ERR_TOO_LARGE;
@@ -320,18 +326,21 @@ static int decode_common(const char* who, const void* q, const void* cache, cons
     p.topk = topk; p.batch = s->batch; p.Hkv = s->num_kv_heads; p.num_pages = s->num_pages;
     p.scale_log2 = sm_scale * kLog2e;
     p.num_splits = num_splits; p.ws_ml = nullptr; p.ws_o = nullptr; p.status = status;
-    if (num_splits > 1) {
+    if (num_splits > 1 || balanced) {
         const size_t need = ktk_decode_workspace_bytes(s, num_splits);
         if (workspace == nullptr || workspace_bytes < need) {
             set_error("%s: workspace of %zu bytes needed for %d splits, got %zu", who, need,
                       num_splits, workspace ? workspace_bytes : (size_t)0);
             return KTK_ERR_WORKSPACE;
         }
-        const int64_t rows = (int64_t)s->batch * s->num_kv_heads * s->group_size * num_splits;
+        const int64_t rows = balanced ? (int64_t)(need / ((2 + kHeadDim) * sizeof(float)))
+                                      : (int64_t)s->batch * s->num_kv_heads * s->group_size * num_splits;
         p.ws_ml = (float*)workspace;
         p.ws_o = (float*)workspace + rows * 2;
     }
     cudaStream_t st = (cudaStream_t)stream;
+    if (balanced)
+        return launch_decode_stream(p, s->group_size, topk >= 0 ? row_width : max_entries, st);
     if (variant == KTK_VARIANT_AUTO)
         variant = (s->dtype == KTK_BF16) ? KTK_VARIANT_MMA : KTK_VARIANT_SIMT;
     if (variant == KTK_VARIANT_MMA)
@@ -348,6 +357,16 @@ static int decode_common(const char* who, const void* q, const void* cache, cons
 using namespace ktk;
 
 extern "C" int32_t ktk_decode_num_splits(const ktk_shape* shape, int32_t max_entries) {
+    if (shape != nullptr && shape->dtype == KTK_BF16) return KTK_SPLITS_BALANCED;
+    return legacy_num_splits(shape, max_entries);
+}
+
+int32_t ktk::policy_num_splits(const ktk_shape* shape, int variant, int32_t max_entries) {
+    const bool tensor_cores = shape != nullptr && shape->dtype == KTK_BF16 && variant != KTK_VARIANT_SIMT;
+    return tensor_cores ? KTK_SPLITS_BALANCED : legacy_num_splits(shape, max_entries);
+}
+
+int32_t ktk::legacy_num_splits(const ktk_shape* shape, int32_t max_entries) {
     if (shape == nullptr || shape->batch <= 0 || shape->num_kv_heads <= 0 || max_entries <= 0) return 1;
     // enough CTAs for four per SM, but never fewer than 8 pages per split
     const int64_t items = (int64_t)shape->batch * shape->num_kv_heads;
@@ -361,6 +380,7 @@ extern "C" int32_t ktk_decode_num_splits(const ktk_shape* shape, int32_t max_ent
 }
 
 extern "C" size_t ktk_decode_workspace_bytes(const ktk_shape* shape, int32_t num_splits) {
+    if (shape != nullptr && num_splits == KTK_SPLITS_BALANCED) return stream_workspace_bytes(shape->group_size);
     if (shape == nullptr || num_splits <= 1) return 0;
     const size_t rows = (size_t)shape->batch * shape->num_kv_heads * shape->group_size * num_splits;
     return rows * (2 + kHeadDim) * sizeof(float);
@@ -453,7 +473,7 @@ extern "C" int ktk_sparse_decode_noalloc(const void* q, const void* kv_cache, co
         set_error("ktk_sparse_decode_noalloc: num_splits %d outside [0, 256]", num_splits);
         return KTK_ERR_ARG;
     }
-    if (num_splits == 0) num_splits = ktk_decode_num_splits(shape, topk + 1);
+    if (num_splits == 0) num_splits = policy_num_splits(shape, variant, topk + 1);
     const size_t need = ktk_decode_workspace_bytes(shape, num_splits);
     if (need > kNoAllocScratchBytes) {
         set_error("ktk_sparse_decode_noalloc: %d splits of this batch need %zu bytes of scratch, the built-in "

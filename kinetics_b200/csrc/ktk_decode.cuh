@@ -100,5 +100,7 @@ __device__ __forceinline__ int entry_tokens(const EntryList& el, int e) {
 int launch_decode_simt(const DecodeParams& p, int dtype, int G, cudaStream_t st);
 int launch_decode_mma(const DecodeParams& p, int G, cudaStream_t st);
 int launch_combine(const DecodeParams& p, int dtype, int G, cudaStream_t st);
+int32_t legacy_num_splits(const ktk_shape* shape, int32_t max_entries);          // per-list split count
+int32_t policy_num_splits(const ktk_shape* shape, int variant, int32_t max_entries);   // what num_splits = 0 means
 
 }  // namespace ktk

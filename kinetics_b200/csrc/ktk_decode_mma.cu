@@ -13,32 +13,14 @@
 // S^T accumulators through movmatrix.  Softmax runs in base 2 with an online
 // maximum per head; each warp keeps its own (m, l, O^T) and the four warps merge
 // through shared memory at the end.  HBM traffic is exactly the listed pages.
-#include "ktk_decode.cuh"
-#include "ktk_pipeline.cuh"
+#include "ktk_decode_mma.cuh"
 
 namespace ktk {
-
-constexpr int kMmaConsumers = 4;                       // consumer warps
-constexpr int kMmaThreads = (kMmaConsumers + 1) * 32;  // + one producer warp
-constexpr int kStageBytes = 2 * kPageSize * kHeadDim * 2;   // K + V of one page, bf16: 8 KiB
-constexpr int kHalfTile = kPageSize * 128;                   // 16 rows x 128 B
-// Ring depth.  A multiple of the consumer count, so that a stage is always drained by the same
-// warp: that warp then sees every phase of the stage's barrier in turn.  (A warp that only
-// saw every other phase could mistake the completion of phase k-1 for that of phase k+1 --
-// an mbarrier wait only tells two consecutive phases apart.)
-constexpr int kMmaStages = 8;
-static_assert(kMmaStages % kMmaConsumers == 0, "a stage must belong to one consumer warp");
 
 struct MmaParams {
     DecodeParams d;
     int G;
 };
-
-// byte offset of 16-byte chunk `c16` (0..15 across the 256-byte row) of token row `tok`
-// inside a K or V tile stored as two 128-byte-swizzled half tiles
-__device__ __forceinline__ uint32_t tile_off(int tok, int c16) {
-    return (uint32_t)((c16 >> 3) * kHalfTile + tok * 128 + (((c16 & 7) ^ (tok & 7)) << 4));
-}
 
 __global__ void __launch_bounds__(kMmaThreads, 3)
 decode_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap kv_map) {
@@ -82,12 +64,8 @@ decode_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap kv_map)
     __syncthreads();
 
     const int gid = lane >> 2, tig = lane & 3;
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;   // heads 2*tig and 2*tig+1
-    float acc[8][4];
-#pragma unroll
-    for (int mt = 0; mt < 8; ++mt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[mt][i] = 0.0f;
+    MmaState ms;                                                   // heads 2*tig and 2*tig+1
+    ms.reset();
 
     if (warp == kMmaConsumers) {
         // ---------------- producer warp ----------------
@@ -113,13 +91,7 @@ decode_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap kv_map)
                         issued = i + 1;
                     } else {
                         stage_tag[s] = i + 1;
-                        uint8_t* dst = stages + s * kStageBytes;
-                        const int y = (int)(page * (2 * kPageSize));      // token row of K slot 0
-                        mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
-                        tma_load_3d(dst, &kv_map, &full_bar[s], 0, h, y);
-                        tma_load_3d(dst + kHalfTile, &kv_map, &full_bar[s], 64, h, y);
-                        tma_load_3d(dst + 2 * kHalfTile, &kv_map, &full_bar[s], 0, h, y + kPageSize);
-                        tma_load_3d(dst + 3 * kHalfTile, &kv_map, &full_bar[s], 64, h, y + kPageSize);
+                        tma_load_page(stages + s * kStageBytes, &kv_map, &full_bar[s], page, h);
                         issued = i + 1;
                     }
                 }
@@ -129,22 +101,8 @@ decode_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap kv_map)
         if (lane == 0) issued_total = issued;
     } else {
         // ---------------- consumer warps ----------------
-        // Q^T fragments: head gid, elements 16*ks + 2*tig (+8); heads past the group are zero
         uint32_t qb[8][2];
-        {
-            const uint32_t* qp = reinterpret_cast<const uint32_t*>(
-                (const __nv_bfloat16*)d.q + ((int64_t)b * Hq + (int64_t)h * G + gid) * kHeadDim);
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-                qb[ks][0] = (gid < G) ? __ldg(qp + ks * 8 + tig) : 0u;
-                qb[ks][1] = (gid < G) ? __ldg(qp + ks * 8 + 4 + tig) : 0u;
-            }
-        }
-        const uint32_t stage_base = smem_u32(stages);
-        // per-lane ldmatrix row addresses (relative to the tile): lane supplies row (lane & 7) of matrix lane >> 3
-        const int mj = lane >> 3, mr = lane & 7;
-        const int k_tok = mr + 8 * (mj & 1), k_c = mj >> 1;     // K:  matrices (tok 0-7 | 8-15) x (chunk 2ks | 2ks+1)
-        const int v_tok = mr + 8 * (mj >> 1), v_c = mj & 1;     // V^T: matrices (chunk 2mt | 2mt+1) x (tok 0-7 | 8-15)
+        load_q_frags(qb, d.q, (int64_t)b * Hq + (int64_t)h * G, G, lane);
 
         for (int i = warp; i < n_entries; i += kMmaConsumers) {
             const int s = i % kMmaStages;
@@ -156,69 +114,8 @@ decode_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap kv_map)
                 if (lane == 0) { report(d.status, KTK_STATUS_INTERNAL); abort_flag = 1; }
                 break;
             }
-            if (tag > 0) {
-                const int e = e0 + i;
-                const int ntok = entry_tokens(el, e);
-                const uint32_t kt = stage_base + s * kStageBytes;
-                const uint32_t vt = kt + 2 * kHalfTile;
-                if (ntok < kPageSize) {
-                    // rows past the fill level may hold anything: clear them in V so that 0 * x stays 0
-                    uint8_t* vrow = stages + s * kStageBytes + 2 * kHalfTile;
-                    for (int c = lane; c < (kPageSize - ntok) * 16; c += 32) {
-                        const int t = ntok + (c >> 4), cc = c & 15;
-                        *reinterpret_cast<uint4*>(vrow + (cc >> 3) * kHalfTile + t * 128 + ((cc & 7) << 4)) =
-                            make_uint4(0, 0, 0, 0);
-                    }
-                    __syncwarp();
-                }
-                // S^T = K . Q^T, two accumulators to shorten the dependency chain
-                float s_a[4] = {0.f, 0.f, 0.f, 0.f}, s_b[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int ks = 0; ks < 8; ks += 2) {
-                    uint32_t ka[4], kb[4];
-                    ldmatrix_x4(ka, kt + tile_off(k_tok, 2 * ks + k_c));
-                    ldmatrix_x4(kb, kt + tile_off(k_tok, 2 * ks + 2 + k_c));
-                    mma_bf16(s_a, ka, qb[ks][0], qb[ks][1]);
-                    mma_bf16(s_b, kb, qb[ks + 1][0], qb[ks + 1][1]);
-                }
-                // scores of tokens gid and gid+8 for heads 2*tig, 2*tig+1 (log2 domain)
-                float s00 = (s_a[0] + s_b[0]) * d.scale_log2, s01 = (s_a[1] + s_b[1]) * d.scale_log2;
-                float s10 = (s_a[2] + s_b[2]) * d.scale_log2, s11 = (s_a[3] + s_b[3]) * d.scale_log2;
-                if (gid >= ntok) { s00 = -INFINITY; s01 = -INFINITY; }
-                if (gid + 8 >= ntok) { s10 = -INFINITY; s11 = -INFINITY; }
-                float mx0 = fmaxf(s00, s10), mx1 = fmaxf(s01, s11);
-#pragma unroll
-                for (int off = 4; off <= 16; off <<= 1) {
-                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
-                }
-                const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);   // finite: token 0 is valid
-                const float al0 = exp2f(m0 - mn0), al1 = exp2f(m1 - mn1);
-                // probabilities, rounded to bf16 once so that the normaliser matches what multiplies V
-                const uint32_t p_lo = pack_bf16(exp2f(s00 - mn0), exp2f(s01 - mn1));   // tokens 0-7
-                const uint32_t p_hi = pack_bf16(exp2f(s10 - mn0), exp2f(s11 - mn1));   // tokens 8-15
-                float sum0 = __uint_as_float(p_lo << 16) + __uint_as_float(p_hi << 16);
-                float sum1 = __uint_as_float(p_lo & 0xffff0000u) + __uint_as_float(p_hi & 0xffff0000u);
-#pragma unroll
-                for (int off = 4; off <= 16; off <<= 1) {
-                    sum0 += __shfl_xor_sync(0xffffffffu, sum0, off);
-                    sum1 += __shfl_xor_sync(0xffffffffu, sum1, off);
-                }
-                m0 = mn0; m1 = mn1;
-                l0 = l0 * al0 + sum0;
-                l1 = l1 * al1 + sum1;
-                // P^T as the B operand: transpose the two 8x8 (token x head) blocks
-                const uint32_t pb0 = movmatrix_trans(p_lo);
-                const uint32_t pb1 = movmatrix_trans(p_hi);
-#pragma unroll
-                for (int mt = 0; mt < 8; ++mt) {
-                    uint32_t va[4];
-                    ldmatrix_x4_trans(va, vt + tile_off(v_tok, 2 * mt + v_c));
-                    acc[mt][0] *= al0; acc[mt][1] *= al1; acc[mt][2] *= al0; acc[mt][3] *= al1;
-                    mma_bf16(acc[mt], va, pb0, pb1);
-                }
-                if (ntok < kPageSize) fence_proxy_async();   // the cleared rows were written by ordinary stores
-            }
+            if (tag > 0)
+                mma_consume_page(ms, stages + s * kStageBytes, entry_tokens(el, e0 + i), qb, d.scale_log2, lane);
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[s]);
         }
@@ -241,16 +138,16 @@ decode_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap kv_map)
     float* red_o = reinterpret_cast<float*>(stages);          // [warp][head][128]
     if (warp < kMmaConsumers) {
         if (gid == 0) {
-            red_m[warp][2 * tig] = m0; red_m[warp][2 * tig + 1] = m1;
-            red_l[warp][2 * tig] = l0; red_l[warp][2 * tig + 1] = l1;
+            red_m[warp][2 * tig] = ms.m0; red_m[warp][2 * tig + 1] = ms.m1;
+            red_l[warp][2 * tig] = ms.l0; red_l[warp][2 * tig + 1] = ms.l1;
         }
 #pragma unroll
         for (int mt = 0; mt < 8; ++mt) {
             float* o0 = red_o + ((warp * 8 + 2 * tig) * kHeadDim) + 16 * mt + gid;
-            o0[0] = acc[mt][0];
-            o0[kHeadDim] = acc[mt][1];
-            o0[8] = acc[mt][2];
-            o0[kHeadDim + 8] = acc[mt][3];
+            o0[0] = ms.acc[mt][0];
+            o0[kHeadDim] = ms.acc[mt][1];
+            o0[8] = ms.acc[mt][2];
+            o0[kHeadDim + 8] = ms.acc[mt][3];
         }
     }
     __syncthreads();
@@ -283,9 +180,7 @@ decode_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap kv_map)
     }
 }
 
-int launch_decode_mma(const DecodeParams& p, int G, cudaStream_t st) {
-    // tensor map over the cache seen as [token rows = pages*2*16][Hkv][128], innermost first
-    CUtensorMap map;
+int make_kv_tensor_map(CUtensorMap* map, const DecodeParams& p) {
     const uint64_t dims[3] = {(uint64_t)kHeadDim, (uint64_t)p.Hkv, (uint64_t)p.num_pages * 2 * kPageSize};
     const uint64_t strides[2] = {(uint64_t)kHeadDim * 2, (uint64_t)p.Hkv * kHeadDim * 2};
     const uint32_t box[3] = {64, 1, (uint32_t)kPageSize};
@@ -293,8 +188,13 @@ int launch_decode_mma(const DecodeParams& p, int G, cudaStream_t st) {
         set_error("ktk decode: %lld pages exceed the tensor-core variant's 2^26-page limit", (long long)p.num_pages);
         return KTK_ERR_TOO_LARGE;
     }
-    int rc = make_tensor_map_3d(&map, p.cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, dims, strides, box,
-                                CU_TENSOR_MAP_SWIZZLE_128B, "ktk decode");
+    return make_tensor_map_3d(map, p.cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, dims, strides, box,
+                              CU_TENSOR_MAP_SWIZZLE_128B, "ktk decode");
+}
+
+int launch_decode_mma(const DecodeParams& p, int G, cudaStream_t st) {
+    CUtensorMap map;
+    int rc = make_kv_tensor_map(&map, p);
     if (rc != KTK_OK) return rc;
     const int smem = kMmaStages * kStageBytes + 1024;
     KTK_CUDA_TRY(cudaFuncSetAttribute(decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),

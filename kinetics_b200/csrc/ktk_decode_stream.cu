@@ -1,0 +1,336 @@
+// Paged flash-decode attention, bf16 tensor cores, balanced partition of the page lists.
+//
+// The per-unit kernel (ktk_decode_mma.cu) launches one CTA per (sequence, kv head): with
+// 4096 units on 444 resident CTAs the last wave runs 22 % full, and every CTA pays the fill
+// and the drain of its pipeline.  Here the grid is one CTA per resident slot and the
+// concatenation of all page lists is cut into equal chunks instead:
+//
+//   position = unit * wmax + entry        unit = b * Hkv + h,  wmax = entries per list (padded)
+//   CTA c owns positions [c * chunk, (c + 1) * chunk)
+//
+// so a CTA runs a few whole units and at most two pieces of units that cross into a neighbour.
+// The producer warp keeps the TMA ring full across unit boundaries; the four consumer warps
+// merge at the end of each unit (through 8 KiB of shared memory next to the ring) and write
+// either the output row (the CTA saw every entry of the unit) or an un-normalised partial
+// (m, l, O) into one of the CTA's two workspace slots: "tail" for a unit that starts in this
+// CTA and continues into the next, "head" for a unit that started in an earlier CTA.
+// stream_combine_kernel then merges the pieces of every cut unit (at most one per CTA).
+// Which CTA holds which piece follows from the shapes alone, so results are deterministic.
+#include <mutex>
+
+#include "ktk_decode_mma.cuh"
+
+namespace ktk {
+
+constexpr int kStreamCtasPerSm = 3;
+constexpr int kStreamMinChunk = 16;                       // pages: below this a CTA is not worth its start-up
+constexpr int kExchangeHeads = 4;                         // heads merged per pass through shared memory
+constexpr int kExchangeBytes = kMmaConsumers * kExchangeHeads * kHeadDim * 4;   // 8 KiB
+constexpr int kStreamSmem = kMmaStages * kStageBytes + 1024 + kExchangeBytes;
+
+struct StreamParams {
+    DecodeParams d;
+    int G;
+    int wmax;        // positions per unit
+    int chunk;       // positions per CTA
+    int64_t total;   // units * wmax
+};
+
+// The part of unit u that falls into the position range [p0, p1).
+struct Piece {
+    int b, h;
+    EntryList el;
+    int e_lo, e_hi;   // entries of the unit this CTA runs
+    bool first;       // the unit's positions start inside the range
+    bool bad;
+};
+
+__device__ __forceinline__ Piece get_piece(const StreamParams& p, int64_t u, int64_t p0, int64_t p1) {
+    Piece pc;
+    pc.b = (int)(u / p.d.Hkv);
+    pc.h = (int)(u % p.d.Hkv);
+    pc.el = entry_list(p.d, pc.b, pc.h, pc.bad);
+    if (pc.el.cnt > p.wmax) {          // a list longer than the caller's bound: flagged by the producer, clipped here
+        pc.el.cnt = p.wmax;
+        pc.bad = true;
+    }
+    const int64_t start = u * p.wmax;
+    const int lo = (p0 > start) ? (int)(p0 - start) : 0;
+    const int hi = (p1 - start < p.wmax) ? (int)(p1 - start) : p.wmax;
+    pc.first = (p0 <= start);
+    pc.e_lo = lo < pc.el.cnt ? lo : pc.el.cnt;
+    pc.e_hi = hi < pc.el.cnt ? hi : pc.el.cnt;
+    return pc;
+}
+
+__device__ __forceinline__ void consumer_bar() {          // the four consumer warps only
+    asm volatile("bar.sync 1, %0;" ::"n"(kMmaConsumers * 32) : "memory");
+}
+
+__global__ void __launch_bounds__(kMmaThreads, kStreamCtasPerSm)
+decode_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap kv_map) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kMmaStages];
+    __shared__ __align__(8) uint64_t empty_bar[kMmaStages];
+    __shared__ int stage_tag[kMmaStages];     // issue index + 1 of the page in the stage, negated if skipped
+    __shared__ int abort_flag;
+    __shared__ int issued_total;
+    __shared__ float red_m[kMmaConsumers][8], red_l[kMmaConsumers][8];
+
+    // the swizzle pattern is a function of the shared-memory address: stages start on 1 KiB
+    uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float* red_o = reinterpret_cast<float*>(stages + kMmaStages * kStageBytes);   // [warp][head of the pass][128]
+
+    const DecodeParams& d = p.d;
+    const int G = p.G;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int Hq = d.Hkv * G;
+    const int64_t p0 = (int64_t)blockIdx.x * p.chunk;
+    const int64_t p1 = (p0 + p.chunk < p.total) ? p0 + p.chunk : p.total;
+    const int64_t u_first = p0 / p.wmax;
+    const int64_t u_last = (p1 - 1) / p.wmax;              // p1 > p0: the grid has no empty CTA
+
+    if (tid == 0) {
+        for (int s = 0; s < kMmaStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        abort_flag = 0;
+        issued_total = 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    if (warp == kMmaConsumers) {
+        // ---------------- producer warp: one ring across all of the CTA's units ----------------
+        if (lane == 0) prefetch_tensormap(&kv_map);
+        int issued = 0;
+        bool alive = true;
+        for (int64_t u = u_first; u <= u_last && alive; ++u) {
+            const Piece pc = get_piece(p, u, p0, p1);
+            if (pc.bad && pc.first && lane == 0) report(d.status, KTK_STATUS_BAD_TABLE);
+            const int e0 = pc.e_lo, e1 = pc.e_hi;
+            int next_ids = (e0 + lane < e1) ? pc.el.ptr[e0 + lane] : -1;
+            for (int base = e0; base < e1 && alive; base += 32) {
+                const int ids = next_ids;
+                next_ids = (base + 32 + lane < e1) ? pc.el.ptr[base + 32 + lane] : -1;   // one chunk ahead
+                const int n = (e1 - base < 32) ? e1 - base : 32;
+                for (int j = 0; j < n && alive; ++j) {
+                    const int64_t page = __shfl_sync(0xffffffffu, ids, j);
+                    if (lane == 0) {
+                        const int i = issued;
+                        const int s = i % kMmaStages;
+                        if (i >= kMmaStages && !mbar_wait(&empty_bar[s], ((i / kMmaStages) - 1) & 1, &abort_flag)) {
+                            alive = false;
+                        } else if (page < 0 || page >= d.num_pages) {
+                            report(d.status, KTK_STATUS_BAD_PAGE);
+                            stage_tag[s] = -(i + 1);
+                            mbar_arrive(&full_bar[s]);          // nothing to load: release the consumer
+                            issued = i + 1;
+                        } else {
+                            stage_tag[s] = i + 1;
+                            tma_load_page(stages + s * kStageBytes, &kv_map, &full_bar[s], page, pc.h);
+                            issued = i + 1;
+                        }
+                    }
+                    alive = __shfl_sync(0xffffffffu, (int)alive, 0) != 0;
+                }
+            }
+        }
+        if (lane == 0) issued_total = issued;
+    } else {
+        // ---------------- consumer warps ----------------
+        const int gid = lane >> 2, tig = lane & 3;
+        MmaState ms;
+        int base_i = 0;            // issue index of the unit's first page
+        bool dead = false;         // gave up: keep walking (the barriers below must stay matched), compute nothing
+        for (int64_t u = u_first; u <= u_last; ++u) {
+            const Piece pc = get_piece(p, u, p0, p1);
+            const int n = pc.e_hi - pc.e_lo;
+            // what this CTA owes the unit: nothing, the output row, or a partial in its tail / head slot
+            const bool whole = pc.first && pc.e_hi == pc.el.cnt;
+            const bool partial = !whole && (pc.first || n > 0);
+            if (!whole && !partial) continue;
+            ms.reset();
+            if (n > 0 && !dead) {
+                uint32_t qb[8][2];
+                load_q_frags(qb, d.q, (int64_t)pc.b * Hq + (int64_t)pc.h * G, G, lane);
+                for (int j = (warp - base_i) & (kMmaConsumers - 1); j < n; j += kMmaConsumers) {
+                    const int i = base_i + j;
+                    const int s = i % kMmaStages;
+                    // the vote keeps the warp together should a single lane give up
+                    if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], (i / kMmaStages) & 1, &abort_flag))) {
+                        dead = true;
+                        break;
+                    }
+                    const int tag = stage_tag[s];
+                    if (tag != i + 1 && tag != -(i + 1)) {
+                        // the stage does not hold the page this warp is waiting for: stop rather than compute on it
+                        if (lane == 0) { report(d.status, KTK_STATUS_INTERNAL); abort_flag = 1; }
+                        dead = true;
+                        break;
+                    }
+                    if (tag > 0)
+                        mma_consume_page(ms, stages + s * kStageBytes, entry_tokens(pc.el, pc.e_lo + j), qb,
+                                         d.scale_log2, lane);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty_bar[s]);
+                }
+            }
+            base_i += n;
+
+            // ---- end of the unit: merge the four warps, kExchangeHeads heads per pass ----
+            if (gid == 0) {
+                red_m[warp][2 * tig] = ms.m0; red_m[warp][2 * tig + 1] = ms.m1;
+                red_l[warp][2 * tig] = ms.l0; red_l[warp][2 * tig + 1] = ms.l1;
+            }
+            const int slot = blockIdx.x * 2 + (pc.first ? 1 : 0);      // head slot 0, tail slot 1
+            for (int pass = 0; pass * kExchangeHeads < G; ++pass) {
+                if ((tig >> 1) == pass) {
+                    const int hl = 2 * (tig & 1);
+#pragma unroll
+                    for (int mt = 0; mt < 8; ++mt) {
+                        float* o0 = red_o + ((warp * kExchangeHeads + hl) * kHeadDim) + 16 * mt + gid;
+                        o0[0] = ms.acc[mt][0];
+                        o0[kHeadDim] = ms.acc[mt][1];
+                        o0[8] = ms.acc[mt][2];
+                        o0[kHeadDim + 8] = ms.acc[mt][3];
+                    }
+                }
+                consumer_bar();
+                const int dd = tid;                                    // 128 consumer threads = 128 head dims
+                const int g_end = (G < (pass + 1) * kExchangeHeads) ? G : (pass + 1) * kExchangeHeads;
+                for (int g = pass * kExchangeHeads; g < g_end; ++g) {
+                    float M = red_m[0][g];
+#pragma unroll
+                    for (int w = 1; w < kMmaConsumers; ++w) M = fmaxf(M, red_m[w][g]);
+                    float L = 0.0f, O = 0.0f;
+                    if (M != -INFINITY) {
+#pragma unroll
+                        for (int w = 0; w < kMmaConsumers; ++w) {
+                            const float wt = exp2f(red_m[w][g] - M);
+                            L += wt * red_l[w][g];
+                            O += wt * red_o[(w * kExchangeHeads + (g - pass * kExchangeHeads)) * kHeadDim + dd];
+                        }
+                    }
+                    if (abort_flag) continue;                          // the CTA gave up: write nothing
+                    if (whole) {
+                        const int64_t qh = (int64_t)pc.b * Hq + (int64_t)pc.h * G + g;
+                        ((__nv_bfloat16*)d.o)[qh * kHeadDim + dd] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+                    } else {
+                        const int64_t row = (int64_t)slot * G + g;
+                        d.ws_o[row * kHeadDim + dd] = O;
+                        if (dd == 0) { d.ws_ml[row * 2] = M; d.ws_ml[row * 2 + 1] = L; }
+                    }
+                }
+                consumer_bar();                                        // red_o / red_m are free again
+            }
+        }
+    }
+
+    __syncthreads();   // every page consumed (or the CTA gave up): stage memory is free
+    if (abort_flag && tid == 0) {
+        report(d.status, KTK_STATUS_TIMEOUT);
+        // wait, again bounded, for copies still in flight before the CTA's shared memory is released
+        volatile int never = 0;
+        const int total = issued_total;
+        for (int i = (total > kMmaStages ? total - kMmaStages : 0); i < total; ++i)
+            mbar_wait(&full_bar[i % kMmaStages], (i / kMmaStages) & 1, &never);
+    }
+}
+
+// One CTA per CTA of the decode grid: merges the pieces of the unit that starts in that CTA's
+// range and continues beyond it (if there is one), and writes its output rows.
+__global__ void __launch_bounds__(kHeadDim)
+stream_combine_kernel(const StreamParams p) {
+    const DecodeParams& d = p.d;
+    const int G = p.G, dd = threadIdx.x;
+    const int64_t c = blockIdx.x;
+    const int64_t p1 = (c + 1) * p.chunk;
+    if (p1 >= p.total) return;                                 // the last CTA: nothing continues
+    const int64_t u = (p1 - 1) / p.wmax;
+    const int64_t start = u * p.wmax;
+    if (start < c * p.chunk) return;                           // the unit began in an earlier CTA: merged there
+    const Piece pc = get_piece(p, u, c * p.chunk, p1);
+    if (start + pc.el.cnt <= p1) return;                       // every entry of the unit lies in CTA c
+    const int64_t end = start + pc.el.cnt;
+    for (int g = 0; g < G; ++g) {
+        float M = -INFINITY, L = 0.0f, O = 0.0f;
+        for (int64_t c2 = c; c2 * p.chunk < end; ++c2) {
+            const int64_t row = (c2 * 2 + (c2 == c ? 1 : 0)) * G + g;   // tail slot of c, head slots after it
+            const float m = d.ws_ml[row * 2], l = d.ws_ml[row * 2 + 1];
+            if (m == -INFINITY) continue;
+            const float Mn = fmaxf(M, m);
+            const float a = exp2f(M - Mn), bsc = exp2f(m - Mn);
+            L = L * a + l * bsc;
+            O = O * a + d.ws_o[row * kHeadDim + dd] * bsc;
+            M = Mn;
+        }
+        const int64_t qh = ((int64_t)pc.b * d.Hkv + pc.h) * G + g;
+        ((__nv_bfloat16*)d.o)[qh * kHeadDim + dd] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+    }
+}
+
+// resident CTAs of decode_stream_kernel on the current device
+static int stream_slots() {
+    static std::mutex mu;
+    static int slots[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return kStreamCtasPerSm * sm_count();
+    std::lock_guard<std::mutex> lock(mu);
+    if (slots[dev] == 0) {
+        int per_sm = 0;
+        cudaFuncSetAttribute(decode_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stream_kernel, kMmaThreads, kStreamSmem) !=
+                cudaSuccess || per_sm < 1)
+            per_sm = 1;
+        if (per_sm > kStreamCtasPerSm) per_sm = kStreamCtasPerSm;
+        slots[dev] = per_sm * sm_count();
+    }
+    return slots[dev];
+}
+
+int stream_grid(int64_t units, int max_entries) {
+    const int64_t total = units * (int64_t)max_entries;
+    int64_t grid = (total + kStreamMinChunk - 1) / kStreamMinChunk;
+    const int64_t slots = stream_slots();
+    if (grid > slots) grid = slots;
+    if (grid < 1) grid = 1;
+    return (int)grid;
+}
+
+size_t stream_workspace_bytes(int G) {
+    // two slots per CTA of the largest grid, each G rows of (m, l) + 128 floats
+    return (size_t)kStreamCtasPerSm * sm_count() * 2 * G * (2 + kHeadDim) * sizeof(float);
+}
+
+int launch_decode_stream(const DecodeParams& p, int G, int max_entries, cudaStream_t st) {
+    CUtensorMap map;
+    int rc = make_kv_tensor_map(&map, p);
+    if (rc != KTK_OK) return rc;
+    StreamParams sp;
+    sp.d = p;
+    sp.G = G;
+    sp.wmax = max_entries;
+    const int64_t units = (int64_t)p.batch * p.Hkv;
+    sp.total = units * max_entries;
+    int grid = stream_grid(units, max_entries);
+    const int64_t chunk = (sp.total + grid - 1) / grid;
+    if (chunk > 2147483647LL) {
+        set_error("ktk decode: %lld page positions per CTA exceed the balanced partition's limit", (long long)chunk);
+        return KTK_ERR_TOO_LARGE;
+    }
+    sp.chunk = (int)chunk;
+    grid = (int)((sp.total + chunk - 1) / chunk);            // no empty CTA
+    KTK_CUDA_TRY(cudaFuncSetAttribute(decode_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem),
+                 "ktk decode (balanced)");
+    decode_stream_kernel<<<grid, kMmaThreads, kStreamSmem, st>>>(sp, map);
+    KTK_CUDA_TRY(cudaGetLastError(), "ktk decode (balanced)");
+    if (grid > 1) {
+        stream_combine_kernel<<<grid, kHeadDim, 0, st>>>(sp);
+        KTK_CUDA_TRY(cudaGetLastError(), "ktk decode (balanced, combine)");
+    }
+    return KTK_OK;
+}
+
+}  // namespace ktk

@@ -26,6 +26,8 @@ from ._lib import Shape, check
 
 HEAD_DIM = 128
 PAGE_SIZE = 16
+SPLITS_BALANCED = -1     # KTK_SPLITS_BALANCED: the library's policy for bf16 (see include/ktk.h)
+VARIANT_SIMT = 1
 
 _LAUNCHES = 0
 
@@ -239,18 +241,34 @@ def decode_workspace_bytes(batch: int, num_kv_heads: int, group_size: int, num_s
     return int(_lib.load().ktk_decode_workspace_bytes(ctypes.byref(shp), num_splits))
 
 
-def _decode_args(q, kv_cache, max_entries, workspace, num_splits):
+def _decode_args(q, kv_cache, max_entries, workspace, num_splits, variant=0):
     B, Hq, _ = q.shape
     shp = _shape(B, kv_cache, Hq)
     if q.dtype != kv_cache.dtype:
         raise TypeError("q and kv_cache must share a dtype")
     if num_splits == 0:
-        num_splits = int(_lib.load().ktk_decode_num_splits(ctypes.byref(shp), max_entries))
+        # the fp32-FMA variant has no balanced partition: ask for the per-list policy
+        num_splits = decode_num_splits(B, shp.num_kv_heads, shp.group_size, max_entries,
+                                       torch.float32 if variant == VARIANT_SIMT else q.dtype)
     need = int(_lib.load().ktk_decode_workspace_bytes(ctypes.byref(shp), num_splits))
+    if need and workspace is None and num_splits == SPLITS_BALANCED:
+        workspace = _shared_workspace(q.device, need)      # a few MB, independent of the batch
     if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
         raise RuntimeError(f"decode with {num_splits} splits needs a {need}-byte workspace "
                            "(decode_workspace_bytes); pass one, or num_splits=1")
-    return shp, num_splits
+    return shp, num_splits, workspace
+
+
+_WORKSPACES: dict = {}
+
+
+def _shared_workspace(device, nbytes: int) -> torch.Tensor:
+    """Per-device scratch for calls of the functional API that pass no workspace (kernels of one stream
+    run in order, so they can share it; `DecodePlan` owns its own)."""
+    ws = _WORKSPACES.get(device)
+    if ws is None or ws.numel() < nbytes:
+        ws = _WORKSPACES[device] = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    return ws
 
 
 def sparse_decode(q, kv_cache, sel_pages, kv_indptr, kv_last_page_len, sm_scale: Optional[float] = None,
@@ -267,7 +285,7 @@ def sparse_decode(q, kv_cache, sel_pages, kv_indptr, kv_last_page_len, sm_scale:
         if view is not None:
             raise ValueError("sparse_decode: pass topk together with a view")
         topk = width - 1
-    shp, num_splits = _decode_args(q, kv_cache, width, workspace, num_splits)
+    shp, num_splits, workspace = _decode_args(q, kv_cache, width, workspace, num_splits, variant)
     if sel_pages.dtype != torch.int32 or sel_pages.numel() != shp.batch * shp.num_kv_heads * width:
         raise ValueError("sel_pages must be int32 [B, Hkv, row width]")
     if out is None:
@@ -279,7 +297,7 @@ def sparse_decode(q, kv_cache, sel_pages, kv_indptr, kv_last_page_len, sm_scale:
     check(_lib.load().ktk_sparse_decode_v(_ptr(q), _ptr(kv_cache), _ptr(sel_pages), topk, vp, width, _ptr(kv_indptr),
                                           _ptr(kv_last_page_len), sm_scale, _ptr(out), _ptr(workspace), wsb,
                                           num_splits, variant, ctypes.byref(shp), _ptr(status), _stream()))
-    _launched(2 if num_splits > 1 else 1)
+    _launched(1 if num_splits == 1 else 2)
     return out
 
 
@@ -288,7 +306,7 @@ def dense_decode(q, kv_cache, kv_indices, kv_indptr, kv_last_page_len, max_pages
                  out=None, status=None, view=None):
     """Attention of q over every page of each sequence (benchmark/dense_decoder.py:168-170)."""
     _cuda(q, kv_cache, kv_indices, kv_indptr, kv_last_page_len, workspace, out, status)
-    shp, num_splits = _decode_args(q, kv_cache, max_pages_per_seq, workspace, num_splits)
+    shp, num_splits, workspace = _decode_args(q, kv_cache, max_pages_per_seq, workspace, num_splits, variant)
     if out is None:
         out = torch.empty_like(q)
     if sm_scale is None:
@@ -386,7 +404,8 @@ class DecodePlan:
         hkv = self.kv_cache.shape[3]
         entries = self.sel_pages.shape[-1] if self.sel_pages is not None else self.max_pages_per_seq
         if self.num_splits == 0:
-            self.num_splits = decode_num_splits(B, hkv, Hq // hkv, entries, q.dtype)
+            self.num_splits = decode_num_splits(B, hkv, Hq // hkv, entries,
+                                                torch.float32 if self.variant == VARIANT_SIMT else q.dtype)
         need = decode_workspace_bytes(B, hkv, Hq // hkv, self.num_splits)
         if need and (self.workspace is None or self.workspace.numel() < need):
             self.workspace = torch.empty(need, dtype=torch.uint8, device=q.device)

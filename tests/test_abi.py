@@ -74,13 +74,20 @@ def test_empty_batch_is_a_no_op():
 
 
 def test_split_policy():
+    import torch
     from kinetics_b200 import ops
-    # many sequences: one CTA each is already plenty
-    assert ops.decode_num_splits(4096, 1, 4, 129) == 1
+    # bf16: the balanced partition, whatever the batch; its workspace does not depend on the batch
+    assert ops.decode_num_splits(4096, 1, 4, 129) == ops.SPLITS_BALANCED
+    assert ops.decode_num_splits(1, 1, 4, 5) == ops.SPLITS_BALANCED
+    ws = ops.decode_workspace_bytes(8, 1, 4, ops.SPLITS_BALANCED)
+    assert 0 < ws < (8 << 20) and ws == ops.decode_workspace_bytes(4096, 1, 4, ops.SPLITS_BALANCED)
+    assert ws % (2 * 4 * 130 * 4) == 0                     # two slots per CTA, G rows of (m, l) + 128 floats
+    # fp32, per-list splits.  Many sequences: one CTA each is already plenty
+    assert ops.decode_num_splits(4096, 1, 4, 129, torch.float32) == 1
     # few sequences: split, but never below 8 pages per split
-    s = ops.decode_num_splits(8, 1, 4, 129)
+    s = ops.decode_num_splits(8, 1, 4, 129, torch.float32)
     assert 1 < s <= 17
-    assert ops.decode_num_splits(1, 1, 4, 5) == 1
+    assert ops.decode_num_splits(1, 1, 4, 5, torch.float32) == 1
     assert ops.decode_workspace_bytes(8, 1, 4, 1) == 0
     assert ops.decode_workspace_bytes(8, 1, 4, 4) == 8 * 4 * 4 * 130 * 4
 
