@@ -210,7 +210,7 @@ def run_reference(args):
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def use_fused_allreduce(args, world):
@@ -547,7 +547,7 @@ def run_ours(args):
             "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
             "clocks": sampler.summary(),
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         # Leave without tearing the communicator down: the captured graphs still reference its kernels,
         # and destroy_process_group() has been seen to wait forever in that state.  Every rank has
@@ -594,12 +594,31 @@ def run_micro_select(args):
     ops.raise_on_status(status)
     ms = e0.elapsed_time(e1) / args.steps
     nbytes = B * hkv * n * HEAD_DIM * 2
-    print(json.dumps({"micro": "select", "batch": B, "pages_scored": n, "topk": topk, "ms": ms,
-                      "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / (ms * 1e-3) / 1e9}), flush=True)
+    emit({"micro": "select", "batch": B, "pages_scored": n, "topk": topk, "ms": ms,
+          "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / (ms * 1e-3) / 1e9})
+
+
+_RESULT_FD = None
+
+
+def emit(line: dict) -> None:
+    """The one JSON line of the run, on the process's original stdout."""
+    text = json.dumps(line) + "\n"
+    if _RESULT_FD is None:
+        sys.stdout.write(text)
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, text.encode())
 
 
 def main():
+    global _RESULT_FD
     args = parse()
+    # Libraries print to stdout too (NCCL's version banner when NCCL_DEBUG is set): send everything
+    # but the result line to stderr, so that stdout carries exactly one JSON line.
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     if args.micro == "select":
         return run_micro_select(args)
     if args.impl == "reference":
