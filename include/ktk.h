@@ -352,6 +352,36 @@ KTK_API int ktk_dense_decode_v(const void* q, const void* kv_cache, const int32_
                                void* workspace, size_t workspace_bytes, int32_t num_splits,
                                int32_t variant, const ktk_shape* shape, int32_t* status, void* stream);
 
+/*
+ * Host-side page pool for continuous batching.  No CUDA call, no device memory: the pool decides
+ * which physical pages of the KV cache a sequence slot owns and writes the CSR arrays the kernels
+ * read.  The reference has no counterpart: its benchmark uses one static interleaved table
+ * (benchmark/blocktopk_decoder.py:141) and its engine reserves max_seq_len tokens of cache per slot
+ * (LiteSys/litesys/attention/batch_cache.py:32-40); the engine loop it serves is
+ * LiteSys/litesys/engine/engine.py:167-242.
+ *   admit    slot takes ceil(n_tokens / page) pages now and is promised ceil(max_total_tokens / page):
+ *            pages promised to one sequence are not handed to another, so `extend` inside the promise
+ *            cannot fail.  KTK_ERR_TOO_LARGE (nothing changed) when the pool cannot promise that much.
+ *   extend   every listed slot grows by tokens_each tokens (a decode step: 1), taking a new page when it
+ *            crosses a page boundary; all or nothing.
+ *   release  the slot's pages go back to the pool.
+ *   export   for the listed slots, in that order: kv_indices (their pages, concatenated), kv_indptr
+ *            [n + 1], kv_last_page_len [n] into host memory of the caller; returns the number of
+ *            entries written to kv_indices, or a negative error.
+ * Not thread-safe: one pool, one scheduling thread.
+ */
+typedef struct ktk_pool ktk_pool;
+KTK_API ktk_pool* ktk_pool_create(int64_t num_pages, int32_t max_slots, int32_t page_size);
+KTK_API void ktk_pool_destroy(ktk_pool* pool);
+KTK_API int64_t ktk_pool_free_pages(const ktk_pool* pool);               /* free and not promised */
+KTK_API int64_t ktk_pool_slot_tokens(const ktk_pool* pool, int32_t slot);  /* -1: slot not in use */
+KTK_API int64_t ktk_pool_slot_pages(const ktk_pool* pool, int32_t slot);
+KTK_API int ktk_pool_admit(ktk_pool* pool, int32_t slot, int64_t n_tokens, int64_t max_total_tokens);
+KTK_API int ktk_pool_extend(ktk_pool* pool, const int32_t* slots, int32_t n, int32_t tokens_each);
+KTK_API int ktk_pool_release(ktk_pool* pool, int32_t slot);
+KTK_API int64_t ktk_pool_export(const ktk_pool* pool, const int32_t* slots, int32_t n, int32_t* kv_indices,
+                                int64_t indices_capacity, int32_t* kv_indptr, int32_t* kv_last_page_len);
+
 #ifdef __cplusplus
 }
 #endif

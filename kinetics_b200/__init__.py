@@ -13,5 +13,7 @@ from . import ops  # noqa: E402  (registers the torch ops)
 from .config import LayerConfig, get_config  # noqa: E402
 from .layers import BlockTopkDecoderLayer, DecoderLayer, init_weights  # noqa: E402
 from .batch_cache import BatchKVManager  # noqa: E402
+from .engine import Engine, PagePool, PooledKVManager, PoolExhausted  # noqa: E402
 
-__all__ = ["ops", "LayerConfig", "get_config", "BlockTopkDecoderLayer", "DecoderLayer", "init_weights", "BatchKVManager"]
+__all__ = ["ops", "LayerConfig", "get_config", "BlockTopkDecoderLayer", "DecoderLayer", "init_weights",
+           "BatchKVManager", "Engine", "PagePool", "PooledKVManager", "PoolExhausted"]

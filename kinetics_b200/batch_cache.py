@@ -89,16 +89,12 @@ class BatchKVManager:
                 raise NotImplementedError(f"attn_block_size must be {PAGE} and attn_stride unset")
         self.layer_skip = list(sk["attn_layer_skip"])
 
-        # pages: slot b owns physical pages [b * P_max, (b + 1) * P_max); the table is the identity
         self.pages_per_slot = 1 + (max(max_seq_len - SINK, 0) + PAGE - 1) // PAGE
-        total = self.pages_per_slot * max_batch_size
-        self.kv_pages = [torch.zeros(total, 2, PAGE, self.num_key_value_heads, self.head_dim, device=self.device,
-                                     dtype=dtype) for _ in range(self.num_layers)]
+        self._alloc_pages()
         self.summaries = [torch.zeros(max_batch_size, self.num_key_value_heads, self.pages_per_slot, self.head_dim,
                                       device=self.device, dtype=dtype) for _ in range(self.num_layers)]
         self.kv_offset = [torch.zeros(max_batch_size, device=self.device, dtype=torch.int32)
                           for _ in range(self.num_layers)]
-        self.kv_indices = torch.arange(total, device=self.device, dtype=torch.int32)
         self.status = ops.new_status(self.device)
         self.row_width = ops.PageView(SINK, self.local).row_width(self.block_topk) if self.block_topk else 0
         self._sel = None
@@ -106,6 +102,13 @@ class BatchKVManager:
         self.sm_scale = 1.0 / math.sqrt(self.head_dim)
 
     # ------------------------------------------------------------------ page bookkeeping
+    def _alloc_pages(self):
+        """Slot b owns physical pages [b * P_max, (b + 1) * P_max); the table is the identity."""
+        total = self.pages_per_slot * self.max_batch_size
+        self.kv_pages = [torch.zeros(total, 2, PAGE, self.num_key_value_heads, self.head_dim, device=self.device,
+                                     dtype=self.dtype) for _ in range(self.num_layers)]
+        self.kv_indices = torch.arange(total, device=self.device, dtype=torch.int32)
+
     def _table(self, batch_idx: torch.Tensor, lengths: torch.Tensor):
         """Per active row: start of its page list, page count, tokens in its last page, view."""
         slot = batch_idx.to(torch.int32).contiguous()
