@@ -14,7 +14,7 @@ import ctypes
 import torch
 import torch.distributed as dist
 
-from . import _lib
+from . import _lib, ops
 from ._lib import check
 
 
@@ -61,4 +61,5 @@ class FusedAllReduceNorm:
             ctypes.c_void_p(self._hf.buffer_ptrs_dev),
             ctypes.c_void_p(self.launch_count.data_ptr()), self.rank, self.world, self.rows, self.cols, eps,
             ctypes.c_void_p(self.status.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        ops._launched()
         return self.sum, self.norm
