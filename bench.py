@@ -68,9 +68,8 @@ def parse():
     ap.add_argument("--cpu-sample", type=int, default=32, help="sequences in the CPU sample")
     ap.add_argument("--allreduce", default="auto", choices=["auto", "fused", "nccl"],
                     help="N > 1: sum the o_proj partials with the fused multicast kernel (all-reduce + residual add "
-                         "+ RMSNorm in one launch), or with NCCL followed by the add + norm kernel.  auto: fused "
-                         "from 4 ranks up (at 2 ranks both directions of the link carry 1.5x NCCL's bytes and the "
-                         "two measure the same)")
+                         "+ RMSNorm in one launch: peer loads at 2 and 4 ranks, NVSwitch multicast above), or with NCCL "
+                         "followed by the add + norm kernel.  auto: fused")
     ap.add_argument("--flashinfer", action="store_true",
                     help="also time, on the same cache and lists, the library kernels the reference uses on a GPU: "
                          "flashinfer's paged batch decode (sparse list and dense table) and the reference's torch "
@@ -216,7 +215,7 @@ def run_reference(args):
 def use_fused_allreduce(args, world):
     if world < 2 or args.allreduce == "nccl":
         return False
-    return args.allreduce == "fused" or world >= 4
+    return True
 
 
 def workload_config(args, wl, n_gpus):
@@ -230,8 +229,9 @@ def workload_config(args, wl, n_gpus):
         "tp_shards_total": wl["tp"], "shards_resident": n_gpus, "page_table": args.page_table,
         "l2": "per-step traffic (summaries + selected pages) exceeds the 126 MB L2; no flush needed",
         "parallelism": f"tp{wl['tp']} by KV head, {n_gpus} shard(s) resident, o_proj all-reduce: "
-                       + ("fused multicast kernel (all-reduce + add + RMSNorm)" if use_fused_allreduce(args, n_gpus)
-                          else "NCCL")
+                       + (("fused kernel (all-reduce + add + RMSNorm), "
+                           + ("peer loads and stores" if n_gpus in (2, 4) else "NVSwitch multicast"))
+                          if use_fused_allreduce(args, n_gpus) else "NCCL")
                        if n_gpus > 1 else f"tp{wl['tp']} by KV head, 1 shard resident",
     }
 

@@ -274,29 +274,40 @@ KTK_API int ktk_qkv_norm(const void* proj, const void* wq, const void* wk, float
                          void* stream);
 
 /*
- * o_proj all-reduce + residual add + RMSNorm in one kernel over NVSwitch multicast (bf16).
+ * o_proj all-reduce + residual add + RMSNorm in one kernel over NVLink (bf16).
  * Replaces `dist.all_reduce(hidden_states)` followed by the residual add and the layer norm
  * (LiteSys/litesys/models/qwen3_dist.py:111-114).
- *   x_multicast      multicast address of the ranks' partial outputs [rows, cols]; each rank's own
- *                    buffer (written by its o_proj GEMM) is bound to that multicast object
+ * Every rank holds its partial o_proj output [rows, cols] in a buffer the others can reach, and a
+ * `sum` buffer of the same shape.  Two forms, chosen by `mode`:
+ *   KTK_ALLREDUCE_MULTICAST  the buffers are bound to NVSwitch multicast objects; the switch adds the
+ *                            partials (multimem.ld_reduce) and replicates the sums (multimem.st).
+ *                            Needs x_multicast, sum_multicast.
+ *   KTK_ALLREDUCE_PEER       plain peer loads and stores; needs x_peer_ptrs, sum_peer_ptrs: device
+ *                            arrays of `world` pointers to every rank's buffer (own included).
+ *                            Built for 2 and 4 ranks.
+ *   KTK_ALLREDUCE_AUTO       peer form at 2 and 4 ranks (a rank's own share would otherwise cross the
+ *                            switch and come back), multicast form above, given the pointers each needs.
  *   residual, w      local [rows, cols] (identical on all ranks), [cols]
- *   sum_multicast    multicast address of [rows, cols]: receives residual + sum of the partials
- *   sum_local        this rank's own mapping of the same buffer (read back for the other ranks' rows)
+ *   sum_local        this rank's own `sum` buffer: receives residual + sum of the partials, all rows
  *   norm_local       local [rows, cols]: receives RMSNorm of that sum (computed on every rank)
  *   flag_ptrs        device array of `world` pointers: rank p's flag words, uint32[grid * world],
  *                    zero before the first launch, reachable from every rank (peer memory)
  *   launch_count     local uint32[grid], zero before the first launch (kept by the kernel)
  * grid = ktk_allreduce_grid(rows, world).  rows must divide by world; cols a multiple of 8, <= 8192.
- * Rank r reduces rows [r*rows/world, (r+1)*rows/world) and multicasts their sum; every rank normalises
- * all rows into its own `norm_local`.  The ranks meet in bounded flag barriers before the reduction
- * and after the multicast (expiry: KTK_STATUS_TIMEOUT in `status`).
- * All ranks must launch it the same number of times with the same shape.
+ * Rank r reduces rows [r*rows/world, (r+1)*rows/world) and sends their sum to every rank; every rank
+ * normalises all rows into its own `norm_local`.  The ranks meet in bounded flag waits before the
+ * reduction and after the sums were sent (expiry: KTK_STATUS_TIMEOUT in `status`).
+ * All ranks must launch it the same number of times with the same shape and mode.
  */
+#define KTK_ALLREDUCE_AUTO 0
+#define KTK_ALLREDUCE_MULTICAST 1
+#define KTK_ALLREDUCE_PEER 2
 KTK_API int32_t ktk_allreduce_grid(int64_t rows, int32_t world);
-KTK_API int ktk_allreduce_add_rmsnorm(const void* x_multicast, const void* residual, const void* w,
-                                      void* sum_multicast, const void* sum_local, void* norm_local,
-                                      const void* flag_ptrs, void* launch_count, int32_t rank, int32_t world, int64_t rows,
-                                      int32_t cols, float eps, int32_t* status, void* stream);
+KTK_API int ktk_allreduce_add_rmsnorm(const void* x_multicast, const void* x_peer_ptrs, const void* residual,
+                                      const void* w, void* sum_multicast, const void* sum_peer_ptrs,
+                                      const void* sum_local, void* norm_local, const void* flag_ptrs,
+                                      void* launch_count, int32_t rank, int32_t world, int64_t rows,
+                                      int32_t cols, float eps, int32_t mode, int32_t* status, void* stream);
 
 /*
  * SwiGLU gate: out = silu(gate) * up, elementwise, fp32 arithmetic.

@@ -13,6 +13,7 @@ LIB_PATH = _PKG / "libktk.so"
 
 KTK_F32, KTK_BF16 = 0, 1
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_MMA = 0, 1, 2
+ALLREDUCE_AUTO, ALLREDUCE_MULTICAST, ALLREDUCE_PEER = 0, 1, 2
 KTK_OK, KTK_ERR_ARG, KTK_ERR_UNSUPPORTED, KTK_ERR_WORKSPACE, KTK_ERR_CUDA, KTK_ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5
 STATUS_TEXT = {0: "ok", 1: "physical page id outside the cache", 2: "malformed page table",
                3: "a bounded wait on an asynchronous copy gave up",
@@ -79,7 +80,7 @@ _SIGNATURES = {
                                c_int32, c_int32, c_void_p]),
     "ktk_allreduce_grid": (c_int32, [c_int64, c_int32]),
     "ktk_allreduce_add_rmsnorm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                            c_void_p, c_int32, c_int32, c_int64, c_int32, c_float, _i32p, c_void_p]),
+                                            c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_int32, c_float, c_int32, _i32p, c_void_p]),
     "ktk_pool_create": (c_void_p, [c_int64, c_int32, c_int32]),
     "ktk_pool_destroy": (None, [c_void_p]),
     "ktk_pool_free_pages": (c_int64, [c_void_p]),

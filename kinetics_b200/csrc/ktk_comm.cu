@@ -110,11 +110,16 @@ __device__ __forceinline__ void norm_row_store(const float (&v)[NV][8], float ss
     }
 }
 
-// NV: vectors per thread, cols <= NV * 8 * kCommThreads
-template <int NV>
+// NV: vectors per thread, cols <= NV * 8 * kCommThreads.
+// PEERS = 0: the switch reduces and multicasts (x_mc / sum_mc are multicast addresses).
+// PEERS = world (2 or 4): plain peer loads and stores instead (x_peer / sum_peer hold every rank's
+// buffer address): a rank's own data then stays off the links, which at 2 ranks is a third of the
+// multicast form's traffic.
+template <int NV, int PEERS>
 __global__ void __launch_bounds__(kCommThreads, 4)
-allreduce_add_rmsnorm_kernel(const __nv_bfloat16* x_mc, const __nv_bfloat16* __restrict__ residual,
-                             const __nv_bfloat16* __restrict__ w, __nv_bfloat16* sum_mc,
+allreduce_add_rmsnorm_kernel(const __nv_bfloat16* x_mc, const __nv_bfloat16* const* x_peer,
+                             const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ w,
+                             __nv_bfloat16* sum_mc, __nv_bfloat16* const* sum_peer,
                              const __nv_bfloat16* sum_local, __nv_bfloat16* norm_local, uint32_t* const* flags,
                              uint32_t* launch_count, int rank, int world, int rows, int cols, float eps,
                              int32_t* status) {
@@ -134,13 +139,19 @@ allreduce_add_rmsnorm_kernel(const __nv_bfloat16* x_mc, const __nv_bfloat16* __r
     for (int r = rank * per + blockIdx.x; r < (rank + 1) * per; r += gridDim.x) {
         float v[NV][8];
         float ss = 0.0f;
-        uint4 xr[NV], tr[NV];
+        constexpr int kSrc = PEERS > 0 ? PEERS : 1;
+        uint4 xr[NV][kSrc], tr[NV];
 #pragma unroll
         for (int i = 0; i < NV; ++i) {          // all of the row's loads first
             const int c = threadIdx.x + i * kCommThreads;
             if (c < nvec) {
                 const size_t off = (size_t)r * cols + (size_t)c * 8;
-                xr[i] = multimem_ld_reduce_bf16x8(x_mc + off);
+                if constexpr (PEERS > 0) {
+#pragma unroll
+                    for (int p = 0; p < PEERS; ++p) xr[i][p] = __ldcg(reinterpret_cast<const uint4*>(x_peer[p] + off));
+                } else {
+                    xr[i][0] = multimem_ld_reduce_bf16x8(x_mc + off);
+                }
                 tr[i] = __ldg(reinterpret_cast<const uint4*>(residual + off));
             }
         }
@@ -150,7 +161,22 @@ allreduce_add_rmsnorm_kernel(const __nv_bfloat16* x_mc, const __nv_bfloat16* __r
             if (c < nvec) {
                 const size_t off = (size_t)r * cols + (size_t)c * 8;
                 float x[8], t[8];
-                unpack8(xr[i], x);
+                unpack8(xr[i][0], x);
+                if constexpr (PEERS > 1) {           // fp32 sum of the partials in rank order, rounded once
+#pragma unroll
+                    for (int p = 1; p < PEERS; ++p) {
+                        float y[8];
+                        unpack8(xr[i][p], y);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) x[e] += y[e];
+                    }
+#pragma unroll
+                    for (int e = 0; e < 8; e += 2) {     // what the switch hands back: the sum as bf16
+                        const __nv_bfloat162 two = __floats2bfloat162_rn(x[e], x[e + 1]);
+                        x[e] = __low2float(two);
+                        x[e + 1] = __high2float(two);
+                    }
+                }
                 unpack8(tr[i], t);
                 uint4 packed;
                 uint32_t* pw = &packed.x;
@@ -159,7 +185,12 @@ allreduce_add_rmsnorm_kernel(const __nv_bfloat16* x_mc, const __nv_bfloat16* __r
                     const __nv_bfloat162 two = __floats2bfloat162_rn(x[e] + t[e], x[e + 1] + t[e + 1]);
                     pw[e / 2] = *reinterpret_cast<const uint32_t*>(&two);
                 }
-                multimem_st_16(sum_mc + off, packed);
+                if constexpr (PEERS > 0) {
+#pragma unroll
+                    for (int p = 0; p < PEERS; ++p) *reinterpret_cast<uint4*>(sum_peer[p] + off) = packed;
+                } else {
+                    multimem_st_16(sum_mc + off, packed);
+                }
                 unpack8(packed, v[i]);                     // normalise the rounded sum, as a reader of `sum` would
 #pragma unroll
                 for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
@@ -211,17 +242,30 @@ extern "C" int32_t ktk_allreduce_grid(int64_t rows, int32_t world) {
     return (int32_t)(per < cap ? per : cap);
 }
 
-extern "C" int ktk_allreduce_add_rmsnorm(const void* x_multicast, const void* residual, const void* w,
-                                         void* sum_multicast, const void* sum_local, void* norm_local,
-                                         const void* flag_ptrs,
+extern "C" int ktk_allreduce_add_rmsnorm(const void* x_multicast, const void* x_peer_ptrs, const void* residual,
+                                         const void* w, void* sum_multicast, const void* sum_peer_ptrs,
+                                         const void* sum_local, void* norm_local, const void* flag_ptrs,
                                          void* launch_count, int32_t rank, int32_t world, int64_t rows,
-                                         int32_t cols, float eps, int32_t* status, void* stream) {
+                                         int32_t cols, float eps, int32_t mode, int32_t* status, void* stream) {
     if (world < 2 || world > kCommMaxWorld || rank < 0 || rank >= world || rows <= 0 || cols <= 0) {
         set_error("ktk_allreduce_add_rmsnorm: bad arguments rank=%d world=%d rows=%lld cols=%d", rank, world,
                   (long long)rows, cols);
         return KTK_ERR_ARG;
     }
-    if (!x_multicast || !residual || !w || !sum_multicast || !sum_local || !norm_local || !flag_ptrs || !launch_count) {
+    if (mode != KTK_ALLREDUCE_AUTO && mode != KTK_ALLREDUCE_MULTICAST && mode != KTK_ALLREDUCE_PEER) {
+        set_error("ktk_allreduce_add_rmsnorm: unknown mode %d", mode);
+        return KTK_ERR_ARG;
+    }
+    const bool have_peer = x_peer_ptrs != nullptr && sum_peer_ptrs != nullptr;
+    const bool have_mc = x_multicast != nullptr && sum_multicast != nullptr;
+    if (mode == KTK_ALLREDUCE_AUTO)       // few ranks: a rank's own share would cross the switch and come back
+        mode = (have_peer && (world == 2 || world == 4)) ? KTK_ALLREDUCE_PEER : KTK_ALLREDUCE_MULTICAST;
+    if (mode == KTK_ALLREDUCE_PEER && world != 2 && world != 4) {
+        set_error("ktk_allreduce_add_rmsnorm: the peer-load form is built for 2 and 4 ranks (got %d)", world);
+        return KTK_ERR_UNSUPPORTED;
+    }
+    if ((mode == KTK_ALLREDUCE_PEER && !have_peer) || (mode == KTK_ALLREDUCE_MULTICAST && !have_mc) || !residual ||
+        !w || !sum_local || !norm_local || !flag_ptrs || !launch_count) {
         set_error("ktk_allreduce_add_rmsnorm: null pointer argument");
         return KTK_ERR_ARG;
     }
@@ -235,14 +279,23 @@ extern "C" int ktk_allreduce_add_rmsnorm(const void* x_multicast, const void* re
     if ((al & 15u) != 0) { set_error("ktk_allreduce_add_rmsnorm: pointers must be 16-byte aligned"); return KTK_ERR_ARG; }
     const int grid = ktk_allreduce_grid(rows, world);
     const int nv = (cols + 8 * kCommThreads - 1) / (8 * kCommThreads);
-#define KTK_COMM_LAUNCH(NV)                                                                                   \
-    allreduce_add_rmsnorm_kernel<NV><<<grid, kCommThreads, 0, (cudaStream_t)stream>>>(                        \
-        (const __nv_bfloat16*)x_multicast, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w,           \
-        (__nv_bfloat16*)sum_multicast, (const __nv_bfloat16*)sum_local, (__nv_bfloat16*)norm_local,           \
+    const int peers = (mode == KTK_ALLREDUCE_PEER) ? world : 0;
+#define KTK_COMM_LAUNCH(NV, PEERS)                                                                            \
+    allreduce_add_rmsnorm_kernel<NV, PEERS><<<grid, kCommThreads, 0, (cudaStream_t)stream>>>(                 \
+        (const __nv_bfloat16*)x_multicast, (const __nv_bfloat16* const*)x_peer_ptrs,                          \
+        (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w, (__nv_bfloat16*)sum_multicast,               \
+        (__nv_bfloat16* const*)sum_peer_ptrs, (const __nv_bfloat16*)sum_local, (__nv_bfloat16*)norm_local,    \
         (uint32_t* const*)flag_ptrs, (uint32_t*)launch_count, rank, world, (int)rows, cols, eps, status)
-    if (nv <= 1) KTK_COMM_LAUNCH(1);
-    else if (nv == 2) KTK_COMM_LAUNCH(2);
-    else KTK_COMM_LAUNCH(4);
+#define KTK_COMM_NV(PEERS)                                                                                    \
+    do {                                                                                                      \
+        if (nv <= 1) KTK_COMM_LAUNCH(1, PEERS);                                                               \
+        else if (nv == 2) KTK_COMM_LAUNCH(2, PEERS);                                                          \
+        else KTK_COMM_LAUNCH(4, PEERS);                                                                       \
+    } while (0)
+    if (peers == 0) KTK_COMM_NV(0);
+    else if (peers == 2) KTK_COMM_NV(2);
+    else KTK_COMM_NV(4);
+#undef KTK_COMM_NV
 #undef KTK_COMM_LAUNCH
     KTK_CUDA_TRY(cudaGetLastError(), "ktk_allreduce_add_rmsnorm");
     return KTK_OK;
