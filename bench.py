@@ -545,6 +545,9 @@ def run_ours(args):
             "config": workload_config(args, wl, world), "roofline": roofline, "kernels": kernels,
             "cpu_baseline": cpu, "e2e": e2e, "dense": dense_info, "library_bar": library_bar,
             "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
+            # what benchmark/blocktopk.py:60,82 prints for one shard: B / t / (world_size * num_hidden_layers)
+            "reference_normalisation": {"tokens_per_s": B / (ms_step * 1e-3) / (tp * cfg.num_hidden_layers),
+                                        "world_size": tp, "num_hidden_layers": cfg.num_hidden_layers},
             "clocks": sampler.summary(),
         }
         emit(line)
