@@ -108,7 +108,7 @@ int make_tensor_map_3d(CUtensorMap* out, const void* base, CUtensorMapDataType d
 }  // namespace ktk
 
 extern "C" const char* ktk_last_error(void) { return ktk::g_err; }
-extern "C" const char* ktk_version(void) { return "0.2"; }
+extern "C" const char* ktk_version(void) { return "0.3"; }
 extern "C" int32_t ktk_view_row_width(int32_t topk, const ktk_view* view) {
     if (ktk::check_view(view, "ktk_view_row_width") != KTK_OK || topk < 0) return -1;
     return ktk::view_row_width(topk, ktk::make_view(view));
