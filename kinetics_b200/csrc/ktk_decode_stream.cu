@@ -31,12 +31,93 @@ constexpr int kStreamSmem = kMmaStages * kStageBytes + 1024 + kExchangeBytes;
 struct StreamParams {
     DecodeParams d;
     int G;
-    int wmax;        // positions per unit
-    int chunk;       // positions per CTA
-    int64_t total;   // units * wmax
+    int wmax;        // padded mode: positions per unit
+    int chunk;       // padded mode: positions per CTA
+    int64_t total;   // padded mode: units * wmax
+    int exact;       // 1: dense CSR lists without a page_count view -- positions are the CSR entries themselves,
+                     //    unit (b, h) covers [(indptr[b] - indptr[0]) * Hkv + h * n(b), ... + n(b)), so ragged
+                     //    batches are cut evenly too; total and chunk are computed on the device
 };
 
-// The part of unit u that falls into the position range [p0, p1).
+// positions [p0, p1) of CTA c; empty if p1 <= p0
+struct Range {
+    int64_t p0, p1;
+};
+
+// number of positions and positions per CTA
+__device__ __forceinline__ void stream_extent(const StreamParams& p, int64_t& total, int64_t& chunk) {
+    total = p.total;
+    chunk = p.chunk;
+    if (p.exact) {
+        total = (int64_t)(p.d.kv_indptr[p.d.batch] - p.d.kv_indptr[0]) * p.d.Hkv;
+        chunk = (total + gridDim.x - 1) / gridDim.x;
+        if (chunk < kStreamMinChunk) chunk = kStreamMinChunk;
+    }
+}
+
+__device__ __forceinline__ Range cta_range(const StreamParams& p, int64_t c) {
+    Range r;
+    int64_t total, chunk;
+    stream_extent(p, total, chunk);
+    r.p0 = c * chunk;
+    r.p1 = (r.p0 + chunk < total) ? r.p0 + chunk : total;
+    return r;
+}
+
+// The unit (b, h) whose positions are [start, start + len)
+struct Cursor {
+    int b, h, len;
+    int64_t start;
+};
+
+// exact mode: the sequence whose CSR entries contain entry q (relative to indptr[0]); all lanes of the
+// warp take part, 32 probes per round
+__device__ __forceinline__ int find_sequence(const int32_t* indptr, int B, int64_t q) {
+    const int lane = threadIdx.x & 31;
+    const int64_t base = indptr[0];
+    int lo = 0, hi = B;                                   // invariant: indptr[lo] - base <= q, answer in [lo, hi)
+    while (hi - lo > 1) {
+        const int step = (hi - lo + 31) / 32;
+        const int idx = lo + lane * step;
+        const bool ok = idx < hi && (int64_t)indptr[idx] - base <= q;
+        const unsigned m = __ballot_sync(0xffffffffu, ok);            // a prefix of the lanes: lane 0 always holds
+        const int k = 31 - __clz((int)m);
+        lo += k * step;
+        hi = (lo + step < hi) ? lo + step : hi;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ Cursor cursor_at(const StreamParams& p, int64_t pos) {
+    Cursor c;
+    if (!p.exact) {
+        const int64_t u = pos / p.wmax;
+        c.b = (int)(u / p.d.Hkv);
+        c.h = (int)(u % p.d.Hkv);
+        c.start = u * p.wmax;
+        c.len = p.wmax;
+        return c;
+    }
+    const int32_t* ip = p.d.kv_indptr;
+    c.b = find_sequence(ip, p.d.batch, pos / p.d.Hkv);
+    c.len = ip[c.b + 1] - ip[c.b];
+    const int64_t first = (int64_t)(ip[c.b] - ip[0]) * p.d.Hkv;
+    c.h = (int)((pos - first) / c.len);
+    c.start = first + (int64_t)c.h * c.len;
+    return c;
+}
+
+__device__ __forceinline__ void cursor_next(const StreamParams& p, Cursor& c) {
+    c.start += c.len;
+    if (++c.h < p.d.Hkv) return;
+    c.h = 0;
+    ++c.b;
+    if (p.exact) {
+        while (c.b < p.d.batch && (c.len = p.d.kv_indptr[c.b + 1] - p.d.kv_indptr[c.b]) == 0) ++c.b;   // no positions
+    }
+}
+
+// The part of the cursor's unit that falls into the position range [p0, p1).
 struct Piece {
     int b, h;
     EntryList el;
@@ -45,19 +126,18 @@ struct Piece {
     bool bad;
 };
 
-__device__ __forceinline__ Piece get_piece(const StreamParams& p, int64_t u, int64_t p0, int64_t p1) {
+__device__ __forceinline__ Piece get_piece(const StreamParams& p, const Cursor& c, int64_t p0, int64_t p1) {
     Piece pc;
-    pc.b = (int)(u / p.d.Hkv);
-    pc.h = (int)(u % p.d.Hkv);
+    pc.b = c.b;
+    pc.h = c.h;
     pc.el = entry_list(p.d, pc.b, pc.h, pc.bad);
-    if (pc.el.cnt > p.wmax) {          // a list longer than the caller's bound: flagged by the producer, clipped here
-        pc.el.cnt = p.wmax;
+    if (pc.el.cnt > c.len) {          // a list longer than the caller's bound: flagged by the producer, clipped here
+        pc.el.cnt = c.len;
         pc.bad = true;
     }
-    const int64_t start = u * p.wmax;
-    const int lo = (p0 > start) ? (int)(p0 - start) : 0;
-    const int hi = (p1 - start < p.wmax) ? (int)(p1 - start) : p.wmax;
-    pc.first = (p0 <= start);
+    const int lo = (p0 > c.start) ? (int)(p0 - c.start) : 0;
+    const int hi = (p1 - c.start < c.len) ? (int)(p1 - c.start) : c.len;
+    pc.first = (p0 <= c.start);
     pc.e_lo = lo < pc.el.cnt ? lo : pc.el.cnt;
     pc.e_hi = hi < pc.el.cnt ? hi : pc.el.cnt;
     return pc;
@@ -85,10 +165,9 @@ decode_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap k
     const int G = p.G;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Hq = d.Hkv * G;
-    const int64_t p0 = (int64_t)blockIdx.x * p.chunk;
-    const int64_t p1 = (p0 + p.chunk < p.total) ? p0 + p.chunk : p.total;
-    const int64_t u_first = p0 / p.wmax;
-    const int64_t u_last = (p1 - 1) / p.wmax;              // p1 > p0: the grid has no empty CTA
+    const Range rg = cta_range(p, blockIdx.x);
+    if (rg.p1 <= rg.p0) return;                            // nothing left for this CTA (exact mode, small batches)
+    const int64_t p0 = rg.p0, p1 = rg.p1;
 
     if (tid == 0) {
         for (int s = 0; s < kMmaStages; ++s) {
@@ -106,8 +185,8 @@ decode_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap k
         if (lane == 0) prefetch_tensormap(&kv_map);
         int issued = 0;
         bool alive = true;
-        for (int64_t u = u_first; u <= u_last && alive; ++u) {
-            const Piece pc = get_piece(p, u, p0, p1);
+        for (Cursor cur = cursor_at(p, p0); cur.start < p1 && cur.b < d.batch && alive; cursor_next(p, cur)) {
+            const Piece pc = get_piece(p, cur, p0, p1);
             if (pc.bad && pc.first && lane == 0) report(d.status, KTK_STATUS_BAD_TABLE);
             const int e0 = pc.e_lo, e1 = pc.e_hi;
             int next_ids = (e0 + lane < e1) ? pc.el.ptr[e0 + lane] : -1;
@@ -144,8 +223,8 @@ decode_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap k
         MmaState ms;
         int base_i = 0;            // issue index of the unit's first page
         bool dead = false;         // gave up: keep walking (the barriers below must stay matched), compute nothing
-        for (int64_t u = u_first; u <= u_last; ++u) {
-            const Piece pc = get_piece(p, u, p0, p1);
+        for (Cursor cur = cursor_at(p, p0); cur.start < p1 && cur.b < d.batch; cursor_next(p, cur)) {
+            const Piece pc = get_piece(p, cur, p0, p1);
             const int n = pc.e_hi - pc.e_lo;
             // what this CTA owes the unit: nothing, the output row, or a partial in its tail / head slot
             const bool whole = pc.first && pc.e_hi == pc.el.cnt;
@@ -240,23 +319,34 @@ decode_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap k
 }
 
 // One CTA per CTA of the decode grid: merges the pieces of the unit that starts in that CTA's
-// range and continues beyond it (if there is one), and writes its output rows.
+// range and continues beyond it (if there is one), and writes its output rows.  In exact mode it
+// also writes the zero rows of sequences without pages (they own no position, so no decode CTA
+// meets them).
 __global__ void __launch_bounds__(kHeadDim)
 stream_combine_kernel(const StreamParams p) {
     const DecodeParams& d = p.d;
     const int G = p.G, dd = threadIdx.x;
+    if (p.exact) {
+        for (int b = blockIdx.x; b < d.batch; b += gridDim.x) {
+            if (d.kv_indptr[b + 1] - d.kv_indptr[b] > 0) continue;
+            for (int hq = 0; hq < d.Hkv * G; ++hq)
+                ((__nv_bfloat16*)d.o)[((int64_t)b * d.Hkv * G + hq) * kHeadDim + dd] = __float2bfloat16_rn(0.0f);
+        }
+    }
     const int64_t c = blockIdx.x;
-    const int64_t p1 = (c + 1) * p.chunk;
-    if (p1 >= p.total) return;                                 // the last CTA: nothing continues
-    const int64_t u = (p1 - 1) / p.wmax;
-    const int64_t start = u * p.wmax;
-    if (start < c * p.chunk) return;                           // the unit began in an earlier CTA: merged there
-    const Piece pc = get_piece(p, u, c * p.chunk, p1);
-    if (start + pc.el.cnt <= p1) return;                       // every entry of the unit lies in CTA c
-    const int64_t end = start + pc.el.cnt;
+    const Range rg = cta_range(p, c);
+    if (rg.p1 <= rg.p0) return;
+    int64_t total, chunk;
+    stream_extent(p, total, chunk);
+    if (rg.p1 >= total) return;                                // the last CTA: nothing continues
+    const Cursor cur = cursor_at(p, rg.p1 - 1);                // the last unit of CTA c
+    if (cur.start < rg.p0) return;                             // it began in an earlier CTA: merged there
+    const Piece pc = get_piece(p, cur, rg.p0, rg.p1);
+    if (cur.start + pc.el.cnt <= rg.p1) return;                // every entry of the unit lies in CTA c
+    const int64_t end = cur.start + pc.el.cnt;
     for (int g = 0; g < G; ++g) {
         float M = -INFINITY, L = 0.0f, O = 0.0f;
-        for (int64_t c2 = c; c2 * p.chunk < end; ++c2) {
+        for (int64_t c2 = c; c2 * chunk < end; ++c2) {
             const int64_t row = (c2 * 2 + (c2 == c ? 1 : 0)) * G + g;   // tail slot of c, head slots after it
             const float m = d.ws_ml[row * 2], l = d.ws_ml[row * 2 + 1];
             if (m == -INFINITY) continue;
@@ -312,6 +402,9 @@ int launch_decode_stream(const DecodeParams& p, int G, int max_entries, cudaStre
     sp.d = p;
     sp.G = G;
     sp.wmax = max_entries;
+    // dense CSR lists: cut the entries themselves (ragged batches stay balanced); selected-page tables
+    // and page_count views: cut the padded rows
+    sp.exact = (p.topk < 0 && p.page_count == nullptr) ? 1 : 0;
     const int64_t units = (int64_t)p.batch * p.Hkv;
     sp.total = units * max_entries;
     int grid = stream_grid(units, max_entries);
@@ -321,12 +414,12 @@ int launch_decode_stream(const DecodeParams& p, int G, int max_entries, cudaStre
         return KTK_ERR_TOO_LARGE;
     }
     sp.chunk = (int)chunk;
-    grid = (int)((sp.total + chunk - 1) / chunk);            // no empty CTA
+    if (!sp.exact) grid = (int)((sp.total + chunk - 1) / chunk);            // no empty CTA
     KTK_CUDA_TRY(cudaFuncSetAttribute(decode_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem),
                  "ktk decode (balanced)");
     decode_stream_kernel<<<grid, kMmaThreads, kStreamSmem, st>>>(sp, map);
     KTK_CUDA_TRY(cudaGetLastError(), "ktk decode (balanced)");
-    if (grid > 1) {
+    if (grid > 1 || sp.exact) {
         stream_combine_kernel<<<grid, kHeadDim, 0, st>>>(sp);
         KTK_CUDA_TRY(cudaGetLastError(), "ktk decode (balanced, combine)");
     }

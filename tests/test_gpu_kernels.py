@@ -245,6 +245,9 @@ def test_sparse_decode_on_golden_cases(cuda_device, name):
     (torch.float32, 4, 2, [300, 45]),
     (torch.float32, 1, 1, [64, 65]),
     (torch.bfloat16, 2, 4, [31, 32, 33]),
+    (torch.bfloat16, 4, 2, [40, 0, 17, 0]),              # sequences without pages: zero rows
+    (torch.bfloat16, 8, 1, [0, 0, 5000, 3, 0, 700]),     # one long list among short ones: cut many times
+    (torch.float32, 2, 2, [0, 33, 0]),
 ])
 def test_dense_decode_vs_oracle(cuda_device, dtype, G, Hkv, lens):
     ops = _ops()
