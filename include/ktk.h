@@ -364,6 +364,41 @@ KTK_API int ktk_dense_decode_v(const void* q, const void* kv_cache, const int32_
                                int32_t variant, const ktk_shape* shape, int32_t* status, void* stream);
 
 /*
+ * The LiteSys decode chain function by function, on its own layout: unpaged key / value caches
+ * [max_batch, Hkv, max_len, D] and an fp32 logits buffer [rows, Hq, max_len] handed from step to step.
+ * For code written against those functions; they read every key and value of a sequence, which the
+ * paged kernels above avoid.  `offset` is indexed by the row of the active batch, the cache slot is
+ * batch_idx[row], exactly as in the reference kernels (cache_utils.py:67,106,149).
+ *   ktk_copy_to_cache    copy_to_cache (LiteSys/litesys/attention/cache_utils.py:5-51): src row `row`, head h
+ *                        (strides in elements) -> cache[batch_id[row], h, offset[row], :]
+ *   ktk_qk               qk (:54-93, :173-190): logits[row, hq, s] = q . K[s] / sqrt(D) for s < offset[row],
+ *                        -inf up to the end of the last block of `block_seq` positions it touches
+ *   ktk_block_topk_mask  blockwise_topk_sparsity (sparsity_utils.py:24-47), block size 16: rows longer than
+ *                        ceil16(sink + local + 16 * topk_block) keep the sink, the topk_block best blocks of the
+ *                        region behind it (mean logit over the query group and the block; ties to the lower
+ *                        block) and the tail; the rest of the region becomes -inf
+ *   ktk_softmax_rows     softmax (cache_utils.py:97-130, :216-226): in place over s < offset[row]
+ *   ktk_sv               sv (:135-169, :193-212): out[row, hq, :] = sum_s p[row, hq, s] * V[s, :], in the cache dtype
+ * A slot or position outside the cache sets KTK_STATUS_BAD_TABLE and skips the access.
+ */
+KTK_API int ktk_copy_to_cache(void* cache, const void* src, const int64_t* batch_id, const int32_t* offset,
+                              int32_t rows, int32_t num_kv_heads, int64_t max_batch, int64_t max_len,
+                              int32_t head_dim, int64_t src_row_stride, int64_t src_head_stride, int32_t dtype,
+                              int32_t* status, void* stream);
+KTK_API int ktk_qk(const void* q, const void* key_cache, const int64_t* batch_idx, const int32_t* offset,
+                   float* logits, int32_t rows, int32_t num_q_heads, int32_t num_kv_heads, int64_t max_batch,
+                   int64_t max_len, int32_t head_dim, int32_t block_seq, int32_t dtype, int32_t* status,
+                   void* stream);
+KTK_API int ktk_block_topk_mask(float* logits, const int32_t* offset, int32_t rows, int32_t num_q_heads,
+                                int32_t num_kv_heads, int64_t max_len, int32_t topk_block, int32_t local,
+                                int32_t sink, int32_t* status, void* stream);
+KTK_API int ktk_softmax_rows(float* logits, const int32_t* offset, int32_t rows, int32_t num_q_heads,
+                             int64_t max_len, void* stream);
+KTK_API int ktk_sv(const void* value_cache, const int64_t* batch_idx, const int32_t* offset, const float* probs,
+                   void* out, int32_t rows, int32_t num_q_heads, int32_t num_kv_heads, int64_t max_batch,
+                   int64_t max_len, int32_t head_dim, int32_t dtype, int32_t* status, void* stream);
+
+/*
  * Host-side page pool for continuous batching.  No CUDA call, no device memory: the pool decides
  * which physical pages of the KV cache a sequence slot owns and writes the CSR arrays the kernels
  * read.  The reference has no counterpart: its benchmark uses one static interleaved table

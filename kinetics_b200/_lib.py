@@ -81,6 +81,15 @@ _SIGNATURES = {
     "ktk_allreduce_grid": (c_int32, [c_int64, c_int32]),
     "ktk_allreduce_add_rmsnorm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_int32, c_float, c_int32, _i32p, c_void_p]),
+    "ktk_copy_to_cache": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_int64,
+                                    c_int32, c_int64, c_int64, c_int32, _i32p, c_void_p]),
+    "ktk_qk": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int64,
+                         c_int64, c_int32, c_int32, c_int32, _i32p, c_void_p]),
+    "ktk_block_topk_mask": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int64, c_int32, c_int32,
+                                      c_int32, _i32p, c_void_p]),
+    "ktk_softmax_rows": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int64, c_void_p]),
+    "ktk_sv": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int64,
+                         c_int64, c_int32, c_int32, _i32p, c_void_p]),
     "ktk_pool_create": (c_void_p, [c_int64, c_int32, c_int32]),
     "ktk_pool_destroy": (None, [c_void_p]),
     "ktk_pool_free_pages": (c_int64, [c_void_p]),
