@@ -274,6 +274,18 @@ KTK_API int ktk_qkv_norm(const void* proj, const void* wq, const void* wk, float
                          void* stream);
 
 /*
+ * The same with the rotary position embedding applied to the normalised query and key heads:
+ * x * cos[pos] + rotate_half(x) * sin[pos], rotate_half(x) = (-x[64:], x[:64]), pos = position_ids[b]
+ * (clamped to the table).  cos_table / sin_table: [max_positions, 128] in `dtype`; one token per row.
+ * Replaces qk_norm + apply_rotary_pos_emb of the LiteSys decode step
+ * (LiteSys/litesys/models/qwen3.py:96-102, models/model_utils.py:17-50).
+ */
+KTK_API int ktk_qkv_norm_rope(const void* proj, const void* wq, const void* wk, float eps, const void* cos_table,
+                              const void* sin_table, const int64_t* position_ids, int64_t max_positions, void* q,
+                              void* k, void* v, int64_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                              int32_t dtype, void* stream);
+
+/*
  * o_proj all-reduce + residual add + RMSNorm in one kernel over NVLink (bf16).
  * Replaces `dist.all_reduce(hidden_states)` followed by the residual add and the layer norm
  * (LiteSys/litesys/models/qwen3_dist.py:111-114).

@@ -90,6 +90,8 @@ _SIGNATURES = {
     "ktk_softmax_rows": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int64, c_void_p]),
     "ktk_sv": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int64,
                          c_int64, c_int32, c_int32, _i32p, c_void_p]),
+    "ktk_qkv_norm_rope": (c_int32, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int64,
+                                    c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int32, c_void_p]),
     "ktk_pool_create": (c_void_p, [c_int64, c_int32, c_int32]),
     "ktk_pool_destroy": (None, [c_void_p]),
     "ktk_pool_free_pages": (c_int64, [c_void_p]),

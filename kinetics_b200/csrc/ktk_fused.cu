@@ -90,11 +90,15 @@ add_rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ residual, cons
 
 // One warp per head row of the fused projection [B, (Hq + 2 Hkv) * 128]:
 // query heads -> RMSNorm with wq -> q[B, Hq, 128]; key heads -> RMSNorm with wk -> k[B, Hkv, 128];
-// value heads -> copied to v[B, Hkv, 128].
-template <typename T>
+// value heads -> copied to v[B, Hkv, 128].  With kRope the normalised query and key heads are then
+// rotated, x * cos[pos] + rotate_half(x) * sin[pos] with rotate_half(x) = (-x[64:], x[:64]) and
+// pos = position_ids[b]; cos / sin are [max_positions, 128] tables in the model dtype.
+template <typename T, bool kRope>
 __global__ void __launch_bounds__(128)
 qkv_norm_kernel(const T* __restrict__ proj, const T* __restrict__ wq, const T* __restrict__ wk, float eps,
-                T* __restrict__ q, T* __restrict__ k, T* __restrict__ v, int64_t rows, int Hq, int Hkv) {
+                T* __restrict__ q, T* __restrict__ k, T* __restrict__ v, int64_t rows, int Hq, int Hkv,
+                const T* __restrict__ cos_tab, const T* __restrict__ sin_tab,
+                const int64_t* __restrict__ position_ids, int64_t max_positions) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -117,6 +121,19 @@ qkv_norm_kernel(const T* __restrict__ proj, const T* __restrict__ wq, const T* _
         const float inv = rsqrtf(ss * (1.0f / 128.0f) + eps);
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[i] = xv[i] * inv * wv[i];
+        if constexpr (kRope) {
+            int64_t pos = position_ids[b];
+            pos = pos < 0 ? 0 : (pos >= max_positions ? max_positions - 1 : pos);
+            float c[4], sn[4];
+            load4(cos_tab + pos * kHeadDim + lane * 4, c);
+            load4(sin_tab + pos * kHeadDim + lane * 4, sn);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float x = to_f32(from_f32<T>(o[i]));            // the norm's output is a tensor of the model dtype
+                const float other = __shfl_xor_sync(0xffffffffu, x, 16);   // element i +- 64
+                o[i] = x * c[i] + (lane < 16 ? -other : other) * sn[i];
+            }
+        }
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) dst[lane * 4 + i] = from_f32<T>(o[i]);
@@ -148,9 +165,16 @@ static int add_rmsnorm_launch(const void* x, const void* residual, const void* w
 
 template <typename T>
 static int qkv_norm_launch(const void* proj, const void* wq, const void* wk, float eps, void* q, void* k, void* v,
-                           int64_t rows, int Hq, int Hkv, cudaStream_t st) {
-    qkv_norm_kernel<T><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>((const T*)proj, (const T*)wq, (const T*)wk, eps,
-                                                                   (T*)q, (T*)k, (T*)v, rows, Hq, Hkv);
+                           int64_t rows, int Hq, int Hkv, const void* cos_tab, const void* sin_tab,
+                           const int64_t* position_ids, int64_t max_positions, cudaStream_t st) {
+    const unsigned grid = (unsigned)((rows + 3) / 4);
+    if (cos_tab != nullptr)
+        qkv_norm_kernel<T, true><<<grid, 128, 0, st>>>((const T*)proj, (const T*)wq, (const T*)wk, eps, (T*)q, (T*)k,
+                                                       (T*)v, rows, Hq, Hkv, (const T*)cos_tab, (const T*)sin_tab,
+                                                       position_ids, max_positions);
+    else
+        qkv_norm_kernel<T, false><<<grid, 128, 0, st>>>((const T*)proj, (const T*)wq, (const T*)wk, eps, (T*)q, (T*)k,
+                                                        (T*)v, rows, Hq, Hkv, nullptr, nullptr, nullptr, 0);
     KTK_CUDA_TRY(cudaGetLastError(), "ktk_qkv_norm");
     return KTK_OK;
 }
@@ -208,7 +232,33 @@ extern "C" int ktk_qkv_norm(const void* proj, const void* wq, const void* wk, fl
     const int64_t rows = batch * (num_q_heads + 2 * num_kv_heads);
     if ((rows + 3) / 4 > 2147483647LL) { set_error("ktk_qkv_norm: too many rows"); return KTK_ERR_TOO_LARGE; }
     cudaStream_t st = (cudaStream_t)stream;
-    return dtype == KTK_F32 ? qkv_norm_launch<float>(proj, wq, wk, eps, q, k, v, rows, num_q_heads, num_kv_heads, st)
+    return dtype == KTK_F32 ? qkv_norm_launch<float>(proj, wq, wk, eps, q, k, v, rows, num_q_heads, num_kv_heads,
+                                                     nullptr, nullptr, nullptr, 0, st)
                             : qkv_norm_launch<__nv_bfloat16>(proj, wq, wk, eps, q, k, v, rows, num_q_heads,
-                                                             num_kv_heads, st);
+                                                             num_kv_heads, nullptr, nullptr, nullptr, 0, st);
+}
+
+extern "C" int ktk_qkv_norm_rope(const void* proj, const void* wq, const void* wk, float eps, const void* cos_table,
+                                 const void* sin_table, const int64_t* position_ids, int64_t max_positions, void* q,
+                                 void* k, void* v, int64_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                                 int32_t dtype, void* stream) {
+    if (batch < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || max_positions <= 0 ||
+        (dtype != KTK_F32 && dtype != KTK_BF16)) {
+        set_error("ktk_qkv_norm_rope: bad arguments batch=%lld Hq=%d Hkv=%d positions=%lld dtype=%d", (long long)batch,
+                  num_q_heads, num_kv_heads, (long long)max_positions, dtype);
+        return KTK_ERR_ARG;
+    }
+    if (batch == 0) return KTK_OK;
+    if (!proj || !wq || !wk || !q || !k || !v || !cos_table || !sin_table || !position_ids) {
+        set_error("ktk_qkv_norm_rope: null pointer argument");
+        return KTK_ERR_ARG;
+    }
+    const int64_t rows = batch * (num_q_heads + 2 * num_kv_heads);
+    if ((rows + 3) / 4 > 2147483647LL) { set_error("ktk_qkv_norm_rope: too many rows"); return KTK_ERR_TOO_LARGE; }
+    cudaStream_t st = (cudaStream_t)stream;
+    return dtype == KTK_F32
+               ? qkv_norm_launch<float>(proj, wq, wk, eps, q, k, v, rows, num_q_heads, num_kv_heads, cos_table,
+                                        sin_table, position_ids, max_positions, st)
+               : qkv_norm_launch<__nv_bfloat16>(proj, wq, wk, eps, q, k, v, rows, num_q_heads, num_kv_heads, cos_table,
+                                                sin_table, position_ids, max_positions, st);
 }

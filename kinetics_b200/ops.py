@@ -349,17 +349,31 @@ def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], weight: torch
     return (out_sum if residual is not None else x), out_norm
 
 
-def qkv_norm(proj: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor, eps: float, num_q_heads: int, num_kv_heads: int):
+def qkv_norm(proj: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor, eps: float, num_q_heads: int, num_kv_heads: int,
+             cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
+             position_ids: Optional[torch.Tensor] = None):
     """Fused projection [B, (Hq + 2 Hkv) * 128] -> (q-normed q [B, Hq, 128], k-normed k [B, Hkv, 128], v).
 
-    One launch for the split / contiguous / qk_norm sequence of benchmark/blocktopk_decoder.py:197-207."""
+    One launch for the split / contiguous / qk_norm sequence of benchmark/blocktopk_decoder.py:197-207.  With
+    `cos`, `sin` ([max_positions, 128] tables) and `position_ids` [B], the rotary embedding of
+    LiteSys/litesys/models/qwen3.py:102 is applied to q and k in the same launch."""
     _cuda(proj, wq, wk)
     B = proj.numel() // ((num_q_heads + 2 * num_kv_heads) * HEAD_DIM)
     q = torch.empty(B, num_q_heads, HEAD_DIM, dtype=proj.dtype, device=proj.device)
     k = torch.empty(B, num_kv_heads, HEAD_DIM, dtype=proj.dtype, device=proj.device)
     v = torch.empty(B, num_kv_heads, HEAD_DIM, dtype=proj.dtype, device=proj.device)
-    check(_lib.load().ktk_qkv_norm(_ptr(proj), _ptr(wq), _ptr(wk), eps, _ptr(q), _ptr(k), _ptr(v), B, num_q_heads,
-                                   num_kv_heads, _dtype_code(proj), _stream()))
+    if cos is None:
+        check(_lib.load().ktk_qkv_norm(_ptr(proj), _ptr(wq), _ptr(wk), eps, _ptr(q), _ptr(k), _ptr(v), B, num_q_heads,
+                                       num_kv_heads, _dtype_code(proj), _stream()))
+    else:
+        _cuda(cos, sin, position_ids)
+        if cos.shape != sin.shape or cos.shape[-1] != HEAD_DIM or cos.dtype != proj.dtype or sin.dtype != proj.dtype \
+                or not cos.is_contiguous() or not sin.is_contiguous() or position_ids.numel() != B:
+            raise ValueError("qkv_norm: cos / sin [max_positions, 128] in the dtype of proj, one position per row")
+        pos = position_ids.reshape(-1).to(torch.int64).contiguous()
+        check(_lib.load().ktk_qkv_norm_rope(_ptr(proj), _ptr(wq), _ptr(wk), eps, _ptr(cos), _ptr(sin), _ptr(pos),
+                                            cos.numel() // HEAD_DIM, _ptr(q), _ptr(k), _ptr(v), B, num_q_heads,
+                                            num_kv_heads, _dtype_code(proj), _stream()))
     _launched()
     return q, k, v
 

@@ -126,3 +126,40 @@ def test_ragged_contexts_select_like_the_oracle(cuda_device):
     got = kb.ops.sparse_decode(layer.capture["q"], layer.kv_cache, layer.topk_page_indices.view(6, 2, 9),
                                layer.full_kv_indptr, layer.last_kv_lens, num_splits=1)
     torch.testing.assert_close(got.float().cpu(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_qkv_norm_with_rotary_embedding(cuda_device, dtype):
+    # split + q-norm + k-norm + rotary embedding in one launch, against the reference's statements in fp32
+    # (LiteSys/litesys/models/qwen3.py:96-102, models/model_utils.py:17-50)
+    import kinetics_b200 as kb
+    g = torch.Generator().manual_seed(17)
+    B, Hq, Hkv, D, eps, max_pos = 37, 8, 2, 128, 1e-6, 500
+    proj = torch.randn(B, (Hq + 2 * Hkv) * D, generator=g).to(dtype).to(cuda_device)
+    wq = (torch.rand(D, generator=g) + 0.5).to(dtype).to(cuda_device)
+    wk = (torch.rand(D, generator=g) + 0.5).to(dtype).to(cuda_device)
+    inv_freq = 1.0 / (1e6 ** (torch.arange(0, D, 2).float() / D))
+    ang = torch.outer(torch.arange(max_pos).float(), inv_freq)
+    emb = torch.cat([ang, ang], dim=-1)
+    cos, sin = emb.cos().to(dtype).to(cuda_device), emb.sin().to(dtype).to(cuda_device)
+    pos = torch.randint(0, max_pos, (B,), generator=g).to(cuda_device)
+    q, k, v = kb.ops.qkv_norm(proj, wq, wk, eps, Hq, Hkv, cos=cos, sin=sin, position_ids=pos)
+
+    def norm(x, w):
+        x = x.float()
+        return (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(dtype).float()
+
+    def rope(x):
+        c, s = cos[pos].float()[:, None, :], sin[pos].float()[:, None, :]
+        rot = torch.cat([-x[..., D // 2:], x[..., :D // 2]], dim=-1)
+        return x * c + rot * s
+
+    p3 = proj.view(B, Hq + 2 * Hkv, D)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    torch.testing.assert_close(q.float(), rope(norm(p3[:, :Hq], wq)), rtol=tol, atol=tol)
+    torch.testing.assert_close(k.float(), rope(norm(p3[:, Hq:Hq + Hkv], wk)), rtol=tol, atol=tol)
+    assert torch.equal(v, p3[:, Hq + Hkv:])
+    # without tables the kernel is the plain split + norms
+    q0, k0, v0 = kb.ops.qkv_norm(proj, wq, wk, eps, Hq, Hkv)
+    torch.testing.assert_close(q0.float(), norm(p3[:, :Hq], wq), rtol=tol, atol=tol)
+    assert torch.equal(v0, v)
