@@ -92,6 +92,22 @@ def test_split_policy():
     assert ops.decode_workspace_bytes(8, 1, 4, 4) == 8 * 4 * 4 * 130 * 4
 
 
+def test_function_level_chain_refuses_cpu_tensors():
+    import torch
+    from kinetics_b200 import cache_utils as cu
+    k_cache = torch.zeros(2, 1, 128, 128)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        cu.copy_to_cache(k_cache, torch.zeros(1, 1, 1, 128), torch.zeros(1, dtype=torch.long),
+                         torch.zeros(1, dtype=torch.int32))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        cu.qk(torch.zeros(1, 4, 1, 128), k_cache, torch.zeros(1, dtype=torch.long), torch.ones(1, dtype=torch.int32),
+              torch.zeros(2, 4, 128), 128)
+    kw = cu.preprocess_sparse_args(attn_block_topk=4, attn_local=16)
+    assert kw["use_sparsity"] == 2 and kw["use_nonlocal_sparsity"] == 1 and kw["attn_layer_skip"] == [0]
+    with pytest.raises(AssertionError):
+        cu.preprocess_sparse_args(attn_block_topk=4)            # a non-local mask needs attn_local
+
+
 def test_ops_refuse_cpu_tensors():
     import torch
     from kinetics_b200 import ops
