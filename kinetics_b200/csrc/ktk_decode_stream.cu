@@ -8,6 +8,9 @@
 //   position = unit * wmax + entry        unit = b * Hkv + h,  wmax = entries per list (padded)
 //   CTA c owns positions [c * chunk, (c + 1) * chunk)
 //
+// (dense CSR lists are cut entry by entry instead, position = (indptr[b] - indptr[0]) * Hkv + h * n(b)
+// + entry, so that batches of very different lengths are balanced as well)
+//
 // so a CTA runs a few whole units and at most two pieces of units that cross into a neighbour.
 // The producer warp keeps the TMA ring full across unit boundaries; the four consumer warps
 // merge at the end of each unit (through 8 KiB of shared memory next to the ring) and write
