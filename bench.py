@@ -447,9 +447,11 @@ def run_ours(args):
 
         # With several ranks the layer input is the same on every rank (tensor parallelism replicates
         # the hidden states) and the layer output is the sum of the ranks' partial results: rank 0 alone
-        # talks to the host, a broadcast hands the input to the others and a reduce brings the sum back,
-        # each on a communicator of its own, so that the broadcast of the next step, the reduce of the
-        # previous one and the all-reduce inside the current step are three independent queues.
+        # talks to the host, a broadcast hands the input to the others and a reduce brings the sum back.
+        # The two collectives run IN LINE with the step, on the compute stream: on streams of their own
+        # their kernels had to wait for SM slots behind the persistent attention kernels of the step in
+        # flight and then held those slots while waiting for the other ranks (2.1 ms/step at every N);
+        # only the host copies overlap the neighbouring steps.
         pg_in = dist.new_group() if world > 1 else None
         pg_out = dist.new_group() if world > 1 else None
 
@@ -463,18 +465,18 @@ def run_ours(args):
                         s_in.wait_event(ev_comp[j])          # the graph that read this buffer has finished
                     if rank == 0:
                         buf_in.copy_(host_in[j], non_blocking=True)
-                    if world > 1:
-                        dist.broadcast(buf_in, src=0, group=pg_in)
                     ev_in[j] = torch.cuda.Event(); ev_in[j].record(s_in)
                 s_comp.wait_event(ev_in[j])
                 if ev_out[j] is not None:
                     s_comp.wait_event(ev_out[j])             # its previous output has left the device
+                if world > 1:
+                    dist.broadcast(buf_in, src=0, group=pg_in)
                 g.replay()
+                if world > 1:
+                    dist.reduce(buf_out, dst=0, group=pg_out)
                 ev_comp[j] = torch.cuda.Event(); ev_comp[j].record(s_comp)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(ev_comp[j])
-                    if world > 1:
-                        dist.reduce(buf_out, dst=0, group=pg_out)
                     if rank == 0:
                         host_out[j].copy_(buf_out, non_blocking=True)
                     ev_out[j] = torch.cuda.Event(); ev_out[j].record(s_out)
@@ -495,7 +497,7 @@ def run_ours(args):
                "how": "pinned host input -> device, layer step, output -> pinned host, every step; copies of "
                       "neighbouring steps overlap the compute on separate streams"
                       + ("; rank 0 holds the host buffers, the input is broadcast and the partial outputs are "
-                         "reduced to it over NVLink" if world > 1 else "")}
+                         "reduced to it over NVLink, in line with the step" if world > 1 else "")}
     sparse.check_status()
 
     # ---- the repository's dense paged decode at the same shape, sharing the KV cache ----
