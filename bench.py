@@ -8,7 +8,8 @@ Workload (default ``cfg3-shard``): one Qwen3-8B-shaped decoder layer at the pape
 -- batch 4096, 32768-token context, page size 16, block top-k budget of 128 pages, bf16 -- sharded
 8-way by KV head the way the reference benchmark does it (``--world_size 8``: one KV head, four
 query heads and 1/8 of the MLP per GPU, benchmark/blocktopk_decoder.py:101-106).  Every rank of an
-N-GPU run holds one such shard (weak scaling) and all-reduces the o_proj partial sums over NCCL.
+N-GPU run holds one such shard (weak scaling) and sums the o_proj partial results with the ranks' fused
+all-reduce + residual + RMSNorm kernel over NVLink (``--allreduce nccl`` for NCCL instead).
 A step is one forward of the layer: RMSNorm, QKV projection, q/k-norm, paged append (+ page
 summary), page scoring + top-k selection, attention over the selected pages, o_proj (+ all-reduce),
 MLP.  The reported value is decode tokens/s in full-layer equivalents, ``batch * N / 8 / t_step``:
