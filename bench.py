@@ -49,6 +49,12 @@ WORKLOADS = {
 }
 PAGE = 16
 HEAD_DIM = 128
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_stream_kernel launch over its algorithmic bytes,
+# from a profiler capture of the same kernel and shape at batch 296 (one CTA per resident slot, every page
+# read once: the traffic grows with the batch in proportion)
+DECODE_TRAFFIC_RATIO = 1.019
+DECODE_TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of decode_stream_kernel at batch 296 of "
+                         "this shape = 1.019 x algorithmic bytes, applied to this run's bytes")
 
 
 def parse():
@@ -71,13 +77,26 @@ def parse():
                     help="N > 1: sum the o_proj partials with the fused multicast kernel (all-reduce + residual add "
                          "+ RMSNorm in one launch: peer loads at 2 and 4 ranks, NVSwitch multicast above), or with NCCL "
                          "followed by the add + norm kernel.  auto: fused")
-    ap.add_argument("--flashinfer", action="store_true",
-                    help="also time, on the same cache and lists, the library kernels the reference uses on a GPU: "
-                         "flashinfer's paged batch decode (sparse list and dense table) and the reference's torch "
-                         "selection statements; reported under \"library_bar\", never part of the headline")
-    ap.add_argument("--micro", default="", choices=["", "select"],
+    ap.add_argument("--down-exchange", default="scatter", choices=["scatter", "allreduce"],
+                    help="N > 1: what the down_proj exchange leaves on a rank: its row slice of the layer output "
+                         "(reduce-scatter + residual) or all rows (all-reduce + residual, the reference's form)")
+    ap.add_argument("--exchange-schedule", default="pipelined", choices=["pipelined", "lockstep"],
+                    help="schedule of the fused o_proj exchange kernel")
+    ap.add_argument("--reps", type=int, default=5, help="repetitions of the --steps loop; the median is reported")
+    ap.add_argument("--no-flashinfer", action="store_true",
+                    help="skip the library comparison.  By default a one-GPU run also times, on the same cache and "
+                         "lists, the library kernels the reference uses on a GPU: flashinfer's paged batch decode "
+                         "(sparse list and dense table) and the reference's torch selection statements; reported "
+                         "under \"library_bar\", never part of the headline")
+    ap.add_argument("--flashinfer", action="store_true", help="(default now; kept for old command lines)")
+    ap.add_argument("--flashinfer-cuda-cores", action="store_true",
+                    help="library comparison: also flashinfer's CUDA-core decode (one more kernel to build)")
+    ap.add_argument("--library-timeout", type=float, default=420.0,
+                    help="seconds the library comparison may take (flashinfer builds its kernels on first use)")
+    ap.add_argument("--micro", default="", choices=["", "select", "exchange"],
                     help="time one kernel alone on the workload's shapes (select: only the page summaries are "
-                         "allocated, so the full batch fits in a few GB)")
+                         "allocated, so the full batch fits in a few GB; exchange: the NVLink exchange kernels "
+                         "on [batch, hidden] under torchrun, every form, beside NCCL)")
     return ap.parse_args()
 
 
@@ -149,7 +168,13 @@ class ClockSampler:
 def cpu_reference_run(wl, sample_batch: int, steps: int, warmup: int, seed: int, budget_s: float = 20.0):
     """Times oracle/reference_layer.py (torch on CPU, all host threads) on `sample_batch` sequences of the
     workload's shape.  Returns (tokens_per_s in full-layer equivalents, ms_per_step, threads, steps_run)."""
-    from kinetics_b200.config import get_config
+    # by path: importing the package would map libktk.so, which has no part in this arm
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_ktk_config", os.path.join(ROOT, "kinetics_b200", "config.py"))
+    cfgmod = importlib.util.module_from_spec(spec)
+    sys.modules["_ktk_config"] = cfgmod
+    spec.loader.exec_module(cfgmod)
+    get_config = cfgmod.get_config
     from oracle.reference_layer import ReferenceLayerCPU
 
     threads = os.cpu_count() or 1
@@ -205,7 +230,7 @@ def run_reference(args):
         "impl": "reference", "metric": "block-top-k decode tokens/s (Qwen3-8B layer, B=4096, 32K ctx)",
         "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": done, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": workload_config(args, wl, args.gpus),
+        "data": "synthetic", "config": dict(workload_config(args, wl, args.gpus), sample_batch=args.cpu_sample),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -241,7 +266,7 @@ def workload_config(args, wl, n_gpus):
 # the reference's GPU statements and library, for comparison (not the product, not the headline)
 # ------------------------------------------------------------------------------------------
 
-def library_bar_run(layer, hidden, B, hkv, hq, topk, device, with_dense=True, iters=10):
+def library_bar_run(layer, hidden, B, hkv, hq, topk, device, with_dense=True, iters=10, cuda_cores=False):
     """Times, with CUDA events, what the reference executes on a GPU for the same step:
     its selection statements in torch (benchmark/blocktopk_decoder.py:216-221, one KV head) and
     flashinfer's BatchDecodeWithPagedKVCacheWrapper (:153-160,176-178,255-265) over the selected list and,
@@ -281,7 +306,7 @@ def library_bar_run(layer, hidden, B, hkv, hq, topk, device, with_dense=True, it
     ws = torch.empty(128 * 1024 * 1024, dtype=torch.uint8, device=device)
     sel = layer.topk_page_indices.view(B, hkv, topk + 1)[:, 0].contiguous().view(-1)
     sel_indptr = torch.arange(B + 1, dtype=torch.int32, device=device) * (topk + 1)
-    for name, tc in (("cuda_cores", False), ("tensor_cores", True)):
+    for name, tc in ((("cuda_cores", False),) if cuda_cores else ()) + (("tensor_cores", True),):
         try:
             w = flashinfer.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD", use_tensor_cores=tc)
             w.plan(sel_indptr, sel, layer.last_kv_lens, hq, hkv, HEAD_DIM, PAGE, pos_encoding_mode="NONE",
@@ -302,6 +327,56 @@ def library_bar_run(layer, hidden, B, hkv, hq, topk, device, with_dense=True, it
 
 def mean_ms(pairs):
     return sum(a.elapsed_time(b) for a, b in pairs) / max(len(pairs), 1)
+
+
+def median(xs):
+    xs = sorted(xs)
+    return xs[len(xs) // 2]
+
+
+def sampled_attention_check(layer, hidden, rows: int = 64, seed: int = 0):
+    """One eager forward with the layer's intermediate tensors kept; for `rows` sampled sequences the
+    attention output of every local KV head is recomputed in fp32 torch over the pages the step selected
+    (last page masked to its fill level), and the selection is recomputed as the reference states it
+    (benchmark/blocktopk_decoder.py:216-217: einsum, mean over the group, k largest) in fp32."""
+    layer.capture = {}
+    layer.forward(hidden)
+    torch.cuda.synchronize()
+    q, o = layer.capture["q"].float(), layer.capture["o"].float()          # [B, Hq, D]
+    layer.capture = None
+    B, hkv, k1 = layer.batch_size, layer.num_kv_heads, layer.topk_page + 1
+    G = layer.num_key_value_groups
+    sel = layer.topk_page_indices.view(B, hkv, k1)
+    gsel = torch.Generator().manual_seed(seed)
+    picks = torch.randperm(B, generator=gsel)[:rows].tolist()
+    indptr = layer.full_kv_indptr.tolist()
+    worst, pages_checked, sets_equal, set_rows = 0.0, 0, 0, 0
+    for b in picks:
+        n_pages = indptr[b + 1] - indptr[b]
+        n_scored = n_pages - 1
+        cnt = min(layer.topk_page, n_scored) + 1
+        last = int(layer.last_kv_lens[b])
+        table = layer.paged_kv_indices[indptr[b]:indptr[b + 1]].long()
+        for h in range(hkv):
+            pages = sel[b, h, :cnt].long()
+            kv = layer.kv_cache[pages][:, :, :, h].float()                  # [cnt, 2, P, D]
+            ntok = (cnt - 1) * PAGE + last
+            kk = kv[:, 0].reshape(cnt * PAGE, HEAD_DIM)[:ntok]
+            vv = kv[:, 1].reshape(cnt * PAGE, HEAD_DIM)[:ntok]
+            qg = q[b, h * G:(h + 1) * G]
+            p_ = torch.softmax(qg @ kk.t() / HEAD_DIM ** 0.5, dim=-1)
+            ref = p_ @ vv
+            worst = max(worst, (ref - o[b, h * G:(h + 1) * G]).abs().max().item())
+            pages_checked += cnt
+            if n_scored > layer.topk_page:
+                summ = layer.compressed_key_cache[b, h, :n_scored].float()
+                csim = torch.einsum("gd,nd->gn", qg, summ).mean(0)
+                want = set(table[csim.topk(layer.topk_page).indices].tolist())
+                sets_equal += int(want == set(pages[:-1].tolist()))
+                set_rows += 1
+    return {"rows": len(picks), "kv_heads": hkv, "pages_checked": pages_checked, "max_abs_err": worst,
+            "tolerance": 2e-2, "selected_sets_equal_torch_fp32": f"{sets_equal}/{set_rows}",
+            "how": "fp32 torch attention over the pages the step selected; selection vs einsum+mean+topk in fp32"}
 
 
 def run_ours(args):
@@ -329,6 +404,8 @@ def run_ours(args):
     tp, B, ctx, topk = wl["tp"], wl["batch"], wl["ctx"], wl["topk"]
     dtype = torch.bfloat16
     torch.manual_seed(args.seed * 1000 + rank)
+    fused = use_fused_allreduce(args, world)
+    scatter = world > 1 and args.down_exchange == "scatter"
 
     ctx_lens = None
     if "ragged" in wl:
@@ -342,10 +419,12 @@ def run_ours(args):
         args.page_table = "random"
 
     def make(cls, **kw):
+        if world > 1:
+            kw.update(down_exchange=args.down_exchange, exchange_schedule=args.exchange_schedule)
         layer = cls(config=cfg, world_size=tp, batch_size=B, prefix_len=ctx, max_len=ctx + 512, page_size=PAGE,
                     device=device, dtype=dtype, page_table=args.page_table, process_group=pg,
                     seed=args.seed + rank, variant=args.variant, context_lens=ctx_lens,
-                    fused_allreduce=use_fused_allreduce(args, world), **kw)
+                    fused_allreduce=fused, **kw)
         for m in layer.modules():
             if isinstance(m, torch.nn.Linear):
                 torch.nn.init.normal_(m.weight, 0.0, 0.02)
@@ -358,6 +437,8 @@ def run_ours(args):
     sparse = make(kb.BlockTopkDecoderLayer, topk_page=topk)
     sparse.decode_plan.num_splits = args.splits
     hidden = torch.randn(B, 1, cfg.hidden_size, device=device, dtype=dtype)
+    if world > 1:
+        dist.broadcast(hidden, src=0)                            # tensor parallelism replicates the hidden states
     static_in, static_out, graph = sparse.make_graphed(hidden)
     sparse.check_status()
 
@@ -375,18 +456,21 @@ def run_ours(args):
 
     sampler = ClockSampler(local)
 
-    # ---- timed region: K graph replays, inputs resident in HBM ----
+    # ---- timed region: `reps` passes of K graph replays, inputs resident in HBM; the median pass is the value ----
     for _ in range(args.warmup):
         graph.replay()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    passes = []
     with sampler:
-        e0.record()
-        for _ in range(args.steps):
-            graph.replay()
-        e1.record()
-        barrier()
-    ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+        for _ in range(max(1, args.reps)):
+            e0.record()
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record()
+            barrier()
+            passes.append(max_over_ranks(e0.elapsed_time(e1) / args.steps))
+    ms_step = median(passes)
     value = B * world / tp / (ms_step * 1e-3)
 
     # ---- per-kernel durations, CUDA events around each of our kernels in an eager pass ----
@@ -418,12 +502,12 @@ def run_ours(args):
     ach_decode = bytes_decode / (t_decode * 1e-3) / 1e9
     ach_select = bytes_select / (t_select * 1e-3) / 1e9
     ach_attn = (bytes_decode + bytes_select) / ((t_decode + t_select) * 1e-3) / 1e9
-    # DRAM traffic per launch: ncu dram__bytes_read+write of this kernel on a B=296 capture of the same shape
-    # came to 1.002x the algorithmic bytes (profiles/decode_mma_kernel_cfg3_b296.md); it grows with the batch
-    # in proportion (one CTA per sequence, each page read once), so it is scaled to this run's batch.
-    traffic = int(bytes_decode * 1.002) + B * hkv * (cfg.num_attention_heads // cfg.num_key_value_heads) * HEAD_DIM * esz
-    roofline = {"bound": "hbm", "kernel": "sparse decode (selected K/V pages)", "achieved": ach_decode,
-                "peak": peak_gbs, "unit": "GB/s", "frac": ach_decode / peak_gbs, "traffic": traffic,
+    # DRAM traffic of one launch of the decode kernel: not measurable inside this run (it needs the
+    # profiler), so the ratio of a profiler capture of the same kernel is applied to this run's bytes.
+    traffic = int(bytes_decode * DECODE_TRAFFIC_RATIO)
+    roofline = {"bound": "hbm", "kernel": "sparse decode (decode_stream_kernel + stream_combine_kernel)",
+                "achieved": ach_decode, "peak": peak_gbs, "unit": "GB/s", "frac": ach_decode / peak_gbs,
+                "traffic": traffic, "traffic_source": DECODE_TRAFFIC_SOURCE,
                 "peak_kind": peak_kind, "ms": t_decode, "algorithmic_bytes": bytes_decode}
     kernels = {
         "select": {"ms": t_select, "algorithmic_bytes": bytes_select, "achieved_gbs": ach_select,
@@ -434,71 +518,27 @@ def run_ours(args):
         "attention_total": {"ms": t_select + t_decode, "achieved_gbs": ach_attn, "frac": ach_attn / peak_gbs,
                             "frac_of_8TBs_nominal": ach_attn / 8000.0},
     }
+    if world > 1:
+        # the two exchanges as the eager pass saw them (a rank's wait for the slowest rank included)
+        hid_bytes = B * cfg.hidden_size * esz
+        for name in ("exchange_o_proj", "exchange_down_proj"):
+            if name in timers:
+                t = max_over_ranks(mean_ms(timers[name][2:]))
+                kernels[name] = {"ms": t, "payload_bytes": hid_bytes}
+        kernels["exchange_exposed_ms_per_step"] = sum(kernels[n]["ms"] for n in ("exchange_o_proj", "exchange_down_proj")
+                                                      if n in kernels)
+
+    # ---- the attention output of the step against fp32 torch over the pages it selected (sampled rows) ----
+    parity = sampled_attention_check(sparse, static_in) if rank == 0 or world > 1 else None
 
     # ---- end to end: host buffers in, host buffers out, every step ----
     # Three streams: the next step's input is copied in and the previous step's output is copied
     # out while the current step computes; two captured graphs alternate so that each has its own
-    # input and output buffer.
+    # input buffer.
     e2e = None
     if not args.no_e2e:
-        sets = [(static_in, static_out, graph), sparse.make_graphed(hidden)]
-        host_in = [torch.randn(B, 1, cfg.hidden_size, dtype=dtype).pin_memory() for _ in range(2)]
-        host_out = [torch.empty(B, 1, cfg.hidden_size, dtype=dtype).pin_memory() for _ in range(2)]
-        s_in, s_out, s_comp = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
-
-        # With several ranks the layer input is the same on every rank (tensor parallelism replicates
-        # the hidden states) and the layer output is the sum of the ranks' partial results: rank 0 alone
-        # talks to the host, a broadcast hands the input to the others and a reduce brings the sum back.
-        # The two collectives run IN LINE with the step, on the compute stream: on streams of their own
-        # their kernels had to wait for SM slots behind the persistent attention kernels of the step in
-        # flight and then held those slots while waiting for the other ranks (2.1 ms/step at every N);
-        # only the host copies overlap the neighbouring steps.
-        pg_in = dist.new_group() if world > 1 else None
-        pg_out = dist.new_group() if world > 1 else None
-
-        def run_steps(n):
-            ev_in = [None, None]; ev_comp = [None, None]; ev_out = [None, None]
-            for i in range(n):
-                j = i & 1
-                buf_in, buf_out, g = sets[j]
-                with torch.cuda.stream(s_in):
-                    if ev_comp[j] is not None:
-                        s_in.wait_event(ev_comp[j])          # the graph that read this buffer has finished
-                    if rank == 0:
-                        buf_in.copy_(host_in[j], non_blocking=True)
-                    ev_in[j] = torch.cuda.Event(); ev_in[j].record(s_in)
-                s_comp.wait_event(ev_in[j])
-                if ev_out[j] is not None:
-                    s_comp.wait_event(ev_out[j])             # its previous output has left the device
-                if world > 1:
-                    dist.broadcast(buf_in, src=0, group=pg_in)
-                g.replay()
-                if world > 1:
-                    dist.reduce(buf_out, dst=0, group=pg_out)
-                ev_comp[j] = torch.cuda.Event(); ev_comp[j].record(s_comp)
-                with torch.cuda.stream(s_out):
-                    s_out.wait_event(ev_comp[j])
-                    if rank == 0:
-                        host_out[j].copy_(buf_out, non_blocking=True)
-                    ev_out[j] = torch.cuda.Event(); ev_out[j].record(s_out)
-            s_comp.wait_stream(s_out)
-            s_comp.wait_stream(s_in)
-
-        run_steps(4)
-        barrier()
-        with sampler:
-            e0.record()
-            run_steps(args.steps)
-            e1.record()
-            barrier()
-        ms_e2e = max_over_ranks(e0.elapsed_time(e1) / args.steps)
-        nbytes = host_in[0].numel() * host_in[0].element_size()
-        e2e = {"value": B * world / tp / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
-               "how": "pinned host input -> device, layer step, output -> pinned host, every step; copies of "
-                      "neighbouring steps overlap the compute on separate streams"
-                      + ("; rank 0 holds the host buffers, the input is broadcast and the partial outputs are "
-                         "reduced to it over NVLink, in line with the step" if world > 1 else "")}
+        e2e = run_e2e(args, sparse, hidden, (static_in, static_out, graph), world, rank, pg, device, B, cfg, dtype,
+                      tp, sampler, barrier, max_over_ranks, scatter)
     sparse.check_status()
 
     # ---- the repository's dense paged decode at the same shape, sharing the KV cache ----
@@ -527,9 +567,17 @@ def run_ours(args):
 
     # ---- the library kernels the reference itself runs on a GPU, on the same cache (comparison only) ----
     library_bar = None
-    if args.flashinfer and world == 1 and ctx_lens is None:
-        library_bar = library_bar_run(sparse, static_in, B, hkv, cfg.num_attention_heads // tp, topk, device,
-                                      with_dense=not args.no_dense)
+    if not args.no_flashinfer and world == 1 and ctx_lens is None:
+        library_bar = bounded_library_bar(args, sparse, static_in, B, hkv, cfg.num_attention_heads // tp, topk, device,
+                                          with_dense=not args.no_dense)
+        if library_bar and "flashinfer_sparse_decode_ms_tensor_cores" in library_bar:
+            lib_sel = library_bar["torch_select_ms"]
+            lib_dec = library_bar["flashinfer_sparse_decode_ms_tensor_cores"]
+            vs = {"select": lib_sel / t_select, "sparse_decode": lib_dec / t_decode,
+                  "select_plus_sparse_decode": (lib_sel + lib_dec) / (t_select + t_decode)}
+            if dense_info and "flashinfer_dense_decode_ms_tensor_cores" in library_bar:
+                vs["dense_decode"] = library_bar["flashinfer_dense_decode_ms_tensor_cores"] / dense_info["decode_ms"]
+            library_bar["vs_library"] = dict(vs, meaning="library time / this repository's time (> 1: faster here)")
 
     # ---- CPU baseline (rank 0, single-GPU run only) ----
     cpu = None
@@ -544,10 +592,13 @@ def run_ours(args):
         line = {
             "metric": "block-top-k decode tokens/s (Qwen3-8B layer, B=4096, 32K ctx)", "value": value,
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "ms_per_step_passes": {"reps": len(passes), "min": min(passes), "median": ms_step, "max": max(passes)},
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(args, wl, world), "roofline": roofline, "kernels": kernels,
-            "cpu_baseline": cpu, "e2e": e2e, "dense": dense_info, "library_bar": library_bar,
-            "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
+            "parity_check": parity, "cpu_baseline": cpu, "e2e": e2e, "dense": dense_info,
+            "library_bar": library_bar,
+            "gpu_launches": launches_per_step * args.steps * max(1, args.reps),
+            "gpu_launches_per_step": launches_per_step,
             # what benchmark/blocktopk.py:60,82 prints for one shard: B / t / (world_size * num_hidden_layers)
             "reference_normalisation": {"tokens_per_s": B / (ms_step * 1e-3) / (tp * cfg.num_hidden_layers),
                                         "world_size": tp, "num_hidden_layers": cfg.num_hidden_layers},
@@ -555,14 +606,156 @@ def run_ours(args):
         }
         emit(line)
     if world > 1:
-        # Leave without tearing the communicator down: the captured graphs still reference its kernels,
-        # and destroy_process_group() has been seen to wait forever in that state.  Every rank has
-        # finished its work once it passes this barrier.
-        dist.barrier()
-        torch.cuda.synchronize()
-        sys.stdout.flush()
+        leave_group(dist, [graph, sparse])
+
+
+def leave_group(dist, holders):
+    """Tear the process group down after the graphs and exchange buffers that use it are gone.  A watchdog
+    ends the process if the teardown does not return (it has been seen to wait forever with captured
+    graphs alive); every rank has finished its work once it passes the barrier."""
+    dist.barrier()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    holders.clear()
+    import gc
+    gc.collect()
+    torch.cuda.synchronize()
+
+    def give_up():
+        sys.stderr.write("bench.py: destroy_process_group() did not return within 20 s; leaving\n")
         sys.stderr.flush()
         os._exit(0)
+
+    t = threading.Timer(20.0, give_up)
+    t.daemon = True
+    t.start()
+    dist.destroy_process_group()
+    t.cancel()
+
+
+def run_e2e(args, sparse, hidden, first_set, world, rank, pg, device, B, cfg, dtype, tp, sampler, barrier,
+            max_over_ranks, scatter):
+    H = cfg.hidden_size
+    s_in, s_out, s_comp = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world == 1:
+        sets = [first_set, sparse.make_graphed(hidden)]
+        host_in = [torch.randn(B, 1, H, dtype=dtype).pin_memory() for _ in range(2)]
+        host_out = [torch.empty(B, 1, H, dtype=dtype).pin_memory() for _ in range(2)]
+
+        def run_steps(n):
+            ev_in = [None, None]; ev_comp = [None, None]; ev_out = [None, None]
+            for i in range(n):
+                j = i & 1
+                buf_in, buf_out, g = sets[j]
+                with torch.cuda.stream(s_in):
+                    if ev_comp[j] is not None:
+                        s_in.wait_event(ev_comp[j])          # the graph that read this buffer has finished
+                    buf_in.copy_(host_in[j], non_blocking=True)
+                    ev_in[j] = torch.cuda.Event(); ev_in[j].record(s_in)
+                s_comp.wait_event(ev_in[j])
+                if ev_out[j] is not None:
+                    s_comp.wait_event(ev_out[j])             # its previous output has left the device
+                g.replay()
+                ev_comp[j] = torch.cuda.Event(); ev_comp[j].record(s_comp)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_comp[j])
+                    host_out[j].copy_(buf_out, non_blocking=True)
+                    ev_out[j] = torch.cuda.Event(); ev_out[j].record(s_out)
+            s_comp.wait_stream(s_out)
+            s_comp.wait_stream(s_in)
+
+        nbytes_in = nbytes_out = host_in[0].numel() * host_in[0].element_size()
+        how = ("pinned host input -> device, layer step, output -> pinned host, every step; copies of "
+               "neighbouring steps overlap the compute on separate streams")
+    else:
+        # Tensor parallelism replicates the hidden states, so the host data is split by rows instead: rank r
+        # copies rows [r*B/N, (r+1)*B/N) of the step's input from its pinned host memory, the ranks hand their
+        # slices to one another with copy-engine peer copies (an all-gather that needs no SM), and each rank
+        # copies back the row slice of the layer output it owns after the down_proj reduce-scatter.  Two
+        # one-CTA barrier kernels per step order the peer copies against the other ranks' graphs.
+        from kinetics_b200.comm import RankBarrier, SharedRows
+        per = B // world
+        shared = [SharedRows(pg, B, H, dtype, device) for _ in range(2)]
+        meet = RankBarrier(pg, device)
+        sets = []
+        for j in range(2):
+            shared[j].local.copy_(hidden.view(B, H))
+            g_in, g_out, g = sparse.make_graphed(hidden, static_in=shared[j].local.view(B, 1, H))
+            sets.append((g_in, g_out, g))
+        r0 = rank * per
+        host_in = [torch.randn(per, H, dtype=dtype).pin_memory() for _ in range(2)]
+        host_out = [torch.empty(per, H, dtype=dtype).pin_memory() for _ in range(2)]
+        stage_out = [torch.empty(per, H, dtype=dtype, device=device) for _ in range(2)]
+
+        def run_steps(n):
+            ev_in = [None, None]; ev_comp = [None, None]; ev_out = [None, None]
+            for i in range(n):
+                j = i & 1
+                _, buf_out, g = sets[j]
+                with torch.cuda.stream(s_in):
+                    if ev_comp[j] is not None:
+                        s_in.wait_event(ev_comp[j])          # this rank's graph that read the buffer has finished
+                    shared[j].mine.copy_(host_in[j], non_blocking=True)
+                    meet()                                   # ... and so has every other rank's
+                    shared[j].push()
+                    meet()                                   # every rank's slice has landed here
+                    ev_in[j] = torch.cuda.Event(); ev_in[j].record(s_in)
+                s_comp.wait_event(ev_in[j])
+                if ev_out[j] is not None:
+                    s_comp.wait_event(ev_out[j])             # the staging buffer has left the device
+                g.replay()
+                out_rows = buf_out.view(-1, H) if scatter else buf_out.view(B, H)[r0:r0 + per]
+                stage_out[j].copy_(out_rows, non_blocking=True)      # the exchange's output buffer is reused next step
+                ev_comp[j] = torch.cuda.Event(); ev_comp[j].record(s_comp)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_comp[j])
+                    host_out[j].copy_(stage_out[j], non_blocking=True)
+                    ev_out[j] = torch.cuda.Event(); ev_out[j].record(s_out)
+            s_comp.wait_stream(s_out)
+            s_comp.wait_stream(s_in)
+
+        nbytes_in = nbytes_out = world * host_in[0].numel() * host_in[0].element_size()
+        how = ("every rank copies its row slice of the step's input from pinned host memory, the slices are "
+               "all-gathered with copy-engine peer copies between two barrier kernels, layer step, every rank "
+               "copies its row slice of the output back; neighbouring steps overlap on separate streams")
+
+    run_steps(4)
+    barrier()
+    with sampler:
+        e0.record()
+        run_steps(args.steps)
+        e1.record()
+        barrier()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    if world > 1:
+        ops_mod = __import__("kinetics_b200").ops
+        ops_mod.raise_on_status(meet.status)
+    return {"value": B * world / tp / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+            "h2d_bytes_per_step": nbytes_in, "d2h_bytes_per_step": nbytes_out, "how": how}
+
+
+def bounded_library_bar(args, layer, hidden, B, hkv, hq, topk, device, with_dense):
+    """library_bar_run in a worker thread with a time limit: flashinfer compiles its kernels with nvcc on
+    first use, which can take minutes on a fresh machine."""
+    box = {}
+
+    def work():
+        try:
+            torch.cuda.set_device(device)
+            box["out"] = library_bar_run(layer, hidden, B, hkv, hq, topk, device, with_dense=with_dense,
+                                         cuda_cores=args.flashinfer_cuda_cores)
+        except Exception as e:                                  # the library is missing or could not build
+            box["out"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+
+    t = threading.Thread(target=work, daemon=True)
+    t.start()
+    t.join(args.library_timeout)
+    if t.is_alive():
+        return {"skipped": f"the library comparison did not finish within {args.library_timeout:.0f} s "
+                           "(flashinfer builds its kernels on first use)"}
+    return box.get("out")
 
 
 def run_micro_select(args):
@@ -604,6 +797,65 @@ def run_micro_select(args):
           "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / (ms * 1e-3) / 1e9})
 
 
+def run_micro_exchange(args):
+    """The NVLink exchange kernels alone on [batch, hidden] bf16 (under torchrun): every form, schedule and
+    result, beside NCCL all-reduce (+ the add / norm kernel) and NCCL reduce-scatter."""
+    import torch.distributed as dist
+    import kinetics_b200 as kb
+    from kinetics_b200 import _lib, ops
+    from kinetics_b200.comm import FusedExchange
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    wl = dict(WORKLOADS[args.workload])
+    rows = args.batch or wl["batch"]
+    cols = kb.get_config(wl["model"]).hidden_size
+    res = torch.randn(rows, cols, device=dev).to(torch.bfloat16)
+    wb = torch.ones(cols, device=dev, dtype=torch.bfloat16)
+    part = torch.randn(rows, cols, device=dev).to(torch.bfloat16)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        dist.barrier(); torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) * 1e3                         # microseconds
+
+    out = {"micro": "exchange", "ranks": world, "rows": rows, "cols": cols, "bytes": rows * cols * 2, "us": {}}
+    forms = [("multicast", _lib.ALLREDUCE_MULTICAST)] + ([("peer", _lib.ALLREDUCE_PEER)] if world in (2, 4) else [])
+    for fname, mode in forms:
+        for schedule, result in (("lockstep", "allreduce_norm"), ("pipelined", "allreduce_norm"),
+                                 ("pipelined", "allreduce"), ("pipelined", "scatter")):
+            ex = FusedExchange(dist.group.WORLD, rows, cols, torch.bfloat16, dev, mode=mode, result=result,
+                               schedule=schedule)
+            ex.x.copy_(part)
+            w = wb if result == "allreduce_norm" else None
+            out["us"][f"{fname}/{schedule}/{result}"] = timed(lambda: ex(res, w, 1e-6))
+            ops.raise_on_status(ex.status)
+            del ex
+
+    def nccl_allreduce_norm():
+        dist.all_reduce(part)
+        ops.add_rmsnorm(part, res, wb, 1e-6)
+
+    mine = torch.empty(rows // world, cols, device=dev, dtype=torch.bfloat16)
+    out["us"]["nccl all_reduce + add_rmsnorm kernel"] = timed(nccl_allreduce_norm)
+    out["us"]["nccl all_reduce"] = timed(lambda: dist.all_reduce(part))
+    out["us"]["nccl reduce_scatter"] = timed(lambda: dist.reduce_scatter_tensor(mine, part))
+    if rank == 0:
+        emit(out)
+    leave_group(dist, [])
+
+
 _RESULT_FD = None
 
 
@@ -627,6 +879,8 @@ def main():
     os.dup2(2, 1)
     if args.micro == "select":
         return run_micro_select(args)
+    if args.micro == "exchange":
+        return run_micro_exchange(args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -322,6 +322,51 @@ KTK_API int ktk_allreduce_add_rmsnorm(const void* x_multicast, const void* x_pee
                                       int32_t cols, float eps, int32_t mode, int32_t* status, void* stream);
 
 /*
+ * Both exchanges of the tensor-parallel layer, row-pipelined (the loads of a CTA's next row are in
+ * flight while it sends the sums of the current one, and rows received from the other ranks are
+ * normalised as their flags arrive).  Same buffers, pointer tables and rank/row ownership as
+ * ktk_allreduce_add_rmsnorm; `result` chooses what every rank ends up with:
+ *   KTK_EXCHANGE_ALLREDUCE_NORM  out_local = residual + sum of the partials (all rows, `out_local` is this
+ *                                rank's own `sum` buffer), norm_local = its RMSNorm.  Replaces
+ *                                dist.all_reduce + residual add + layer_norm
+ *                                (LiteSys/litesys/models/qwen3_dist.py:111-114); between stacked layers also the
+ *                                down_proj all-reduce + residual add (:120-122) followed by the next layer's
+ *                                input layer_norm (:91).
+ *   KTK_EXCHANGE_ALLREDUCE       the same without the norm (w, norm_local may be null): the down_proj
+ *                                all-reduce + residual add (:120-122).
+ *   KTK_EXCHANGE_SCATTER         reduce-scatter: out_local (any local [rows, cols] buffer) receives
+ *                                residual + sum for the rows [rank*rows/world, (rank+1)*rows/world) only;
+ *                                nothing is sent back.  sum_multicast / sum_peer_ptrs may be null.
+ * flag_ptrs: rank p's flag words, uint32[ktk_exchange_grid() * world], zero before the first launch;
+ * launch_count: local uint32[ktk_exchange_grid()], zero before the first launch (ktk_exchange_grid is an
+ * upper bound of the CTAs any form launches).  A set of flags belongs
+ * to one (shape, mode, result) for its whole life.  cols a multiple of 8, <= 8192.
+ */
+#define KTK_EXCHANGE_ALLREDUCE_NORM 0
+#define KTK_EXCHANGE_ALLREDUCE 1
+#define KTK_EXCHANGE_SCATTER 2
+KTK_API int32_t ktk_exchange_grid(int64_t rows, int32_t world);
+KTK_API int ktk_exchange_rows(const void* x_multicast, const void* x_peer_ptrs, const void* residual,
+                              const void* w, void* sum_multicast, const void* sum_peer_ptrs, void* out_local,
+                              void* norm_local, const void* flag_ptrs, void* launch_count, int32_t rank,
+                              int32_t world, int64_t rows, int32_t cols, float eps, int32_t mode,
+                              int32_t result, int32_t* status, void* stream);
+
+/*
+ * A barrier of the ranks as a one-CTA kernel in `stream`: work enqueued after it on any rank starts only
+ * when every rank's stream has reached its own barrier launch (and that rank's earlier writes, peer
+ * copies included, are visible).  For host-side pipelines that hand buffers between ranks with copy
+ * engines; the layer kernels carry their own flags.  No reference counterpart (the reference's ranks
+ * meet inside NCCL collectives, LiteSys/litesys/models/qwen3_dist.py:112,121).
+ *   flag_ptrs     device array of `world` pointers: rank p's uint32[world] flag words, zero before the
+ *                 first launch, reachable from every rank
+ *   launch_count  local uint32[1], zero before the first launch
+ * The wait is bounded (about a second): on expiry KTK_STATUS_TIMEOUT goes to `status` and the kernel returns.
+ */
+KTK_API int ktk_rank_barrier(const void* flag_ptrs, void* launch_count, int32_t rank, int32_t world,
+                             int32_t* status, void* stream);
+
+/*
  * SwiGLU gate: out = silu(gate) * up, elementwise, fp32 arithmetic.
  * Replaces the activation + multiply of benchmark/blocktopk_decoder.py:235-236.
  */

@@ -14,6 +14,7 @@ LIB_PATH = _PKG / "libktk.so"
 KTK_F32, KTK_BF16 = 0, 1
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_MMA = 0, 1, 2
 ALLREDUCE_AUTO, ALLREDUCE_MULTICAST, ALLREDUCE_PEER = 0, 1, 2
+EXCHANGE_ALLREDUCE_NORM, EXCHANGE_ALLREDUCE, EXCHANGE_SCATTER = 0, 1, 2
 KTK_OK, KTK_ERR_ARG, KTK_ERR_UNSUPPORTED, KTK_ERR_WORKSPACE, KTK_ERR_CUDA, KTK_ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5
 STATUS_TEXT = {0: "ok", 1: "physical page id outside the cache", 2: "malformed page table",
                3: "a bounded wait on an asynchronous copy gave up",
@@ -81,6 +82,11 @@ _SIGNATURES = {
     "ktk_allreduce_grid": (c_int32, [c_int64, c_int32]),
     "ktk_allreduce_add_rmsnorm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_int32, c_float, c_int32, _i32p, c_void_p]),
+    "ktk_exchange_grid": (c_int32, [c_int64, c_int32]),
+    "ktk_exchange_rows": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_int32, c_float,
+                                    c_int32, c_int32, _i32p, c_void_p]),
+    "ktk_rank_barrier": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, _i32p, c_void_p]),
     "ktk_copy_to_cache": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_int64,
                                     c_int32, c_int64, c_int64, c_int32, _i32p, c_void_p]),
     "ktk_qk": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int64,

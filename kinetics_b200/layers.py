@@ -13,8 +13,10 @@ same constructor arguments, ``forward(hidden_states[B, 1, H]) -> [B, 1, H]`` and
   ``self.topk_page_indices`` at :221 while flashinfer keeps the buffer from :157);
 * ``last_kv_lens`` starts at 1 (the token the step appends) instead of 0 (:149);
 * the torch ops are registered once at import, so dense and sparse layers share a process;
-* with ``process_group`` set, the o_proj partial sums are all-reduced (LiteSys
-  litesys/models/qwen3_dist.py:111-112); the reference benchmark only divides head counts.
+* with ``process_group`` set, the o_proj and the down_proj partial sums are reduced over the ranks
+  (LiteSys litesys/models/qwen3_dist.py:111-112 and :120-121) and the residual is added once; the
+  reference benchmark only divides head counts.  ``down_exchange="scatter"`` leaves rank r with the rows
+  [r*B/N, (r+1)*B/N) of the layer output (a reduce-scatter) instead of all rows on every rank.
 """
 from __future__ import annotations
 
@@ -75,7 +77,8 @@ class _PagedDecoderLayer(nn.Module):
 
     def __init__(self, config, world_size, batch_size, prefix_len, max_len, page_size, device, dtype,
                  page_table: str = "interleaved", process_group=None, seed: int = 0, variant: int = 0,
-                 kv_cache: Optional[torch.Tensor] = None, context_lens=None, fused_allreduce: bool = False):
+                 kv_cache: Optional[torch.Tensor] = None, context_lens=None, fused_allreduce: bool = False,
+                 down_exchange: str = "allreduce", exchange_schedule: str = "pipelined"):
         super().__init__()
         self.num_heads = config.num_attention_heads // world_size
         self.num_kv_heads = config.num_key_value_heads // world_size
@@ -114,12 +117,18 @@ class _PagedDecoderLayer(nn.Module):
         self.dtype = dtype
         self.process_group = process_group
         self.variant = variant
-        # with a process group: sum the o_proj partials either with NCCL followed by the add + norm
-        # kernel, or (fused_allreduce) with the one multicast kernel of comm.py
-        self.fused = None
+        # with a process group: sum the o_proj and down_proj partials either with NCCL followed by the
+        # add (+ norm) kernel, or (fused_allreduce) with the exchange kernels of comm.py
+        if down_exchange not in ("allreduce", "scatter"):
+            raise ValueError("down_exchange: 'allreduce' or 'scatter'")
+        self.down_exchange = down_exchange
+        self.fused = self.fused_down = None
         if process_group is not None and fused_allreduce:
-            from .comm import FusedAllReduceNorm
-            self.fused = FusedAllReduceNorm(process_group, batch_size, self.dim, dtype, device)
+            from .comm import FusedExchange
+            self.fused = FusedExchange(process_group, batch_size, self.dim, dtype, device,
+                                       result="allreduce_norm", schedule=exchange_schedule)
+            self.fused_down = FusedExchange(process_group, batch_size, self.dim, dtype, device,
+                                            result=down_exchange)
         if page_size != ops.PAGE_SIZE or self.head_dim != ops.HEAD_DIM:
             raise ValueError(f"only page_size={ops.PAGE_SIZE}, head_dim={ops.HEAD_DIM} are built")
 
@@ -188,7 +197,9 @@ class _PagedDecoderLayer(nn.Module):
         raise NotImplementedError
 
     def _mlp(self, hidden_states, residual):
-        """SwiGLU MLP; the residual add rides in the epilogue of the down projection GEMM."""
+        """SwiGLU MLP.  One rank: the residual add rides in the epilogue of the down projection GEMM.
+        Several ranks: the down_proj partials are summed over the ranks and the residual is added once
+        (litesys/models/qwen3_dist.py:120-122)."""
         up = self.up_proj(hidden_states)
         gate = self.gate_proj(hidden_states)
         if self.hidden_act == "silu":
@@ -196,7 +207,24 @@ class _PagedDecoderLayer(nn.Module):
         else:
             from transformers.activations import ACT2FN
             hidden_states = ACT2FN[self.hidden_act](gate) * up
-        return torch.addmm(residual, hidden_states, self.down_proj.weight.t())
+        if self.process_group is None:
+            return torch.addmm(residual, hidden_states, self.down_proj.weight.t())
+        if self.fused_down is not None:
+            torch.mm(hidden_states, self.down_proj.weight.t(), out=self.fused_down.x)
+            with self._timed("exchange_down_proj"):
+                out, _ = self.fused_down(residual.contiguous())
+            return out
+        part = torch.mm(hidden_states, self.down_proj.weight.t())
+        with self._timed("exchange_down_proj"):
+            if self.down_exchange == "scatter":
+                world = torch.distributed.get_world_size(self.process_group)
+                rank = torch.distributed.get_rank(self.process_group)
+                per = part.shape[0] // world
+                out = torch.empty(per, part.shape[1], dtype=part.dtype, device=part.device)
+                torch.distributed.reduce_scatter_tensor(out, part, group=self.process_group)
+                return out.add_(residual[rank * per:(rank + 1) * per])
+            torch.distributed.all_reduce(part, group=self.process_group)
+            return part.add_(residual)
 
     @torch.inference_mode()
     def forward(self, hidden_states):
@@ -217,32 +245,43 @@ class _PagedDecoderLayer(nn.Module):
             torch.ops.mylib.update_kv(key_states, value_states, self.qkv_indptr, self.kv_cache,
                                       self.paged_kv_indices, self.full_kv_indptr, self.last_kv_lens)
         o = self._attention(query_states)
+        if self.capture is not None:
+            self.capture.update(o=o.clone())
         o = o.reshape(bsz * q_len, self.head_dim * self.num_heads)
         if self.fused is not None:
             # o_proj partial straight into the symmetric buffer, then all-reduce + residual add + norm at once
             torch.mm(o, self.wo.weight.t(), out=self.fused.x)
-            residual, hidden_states = self.fused(residual.contiguous(), self.post_attention_layernorm_weight,
-                                                 self.post_attention_layernorm_variance_epsilon)
+            with self._timed("exchange_o_proj"):
+                residual, hidden_states = self.fused(residual.contiguous(), self.post_attention_layernorm_weight,
+                                                     self.post_attention_layernorm_variance_epsilon)
         else:
             hidden_states = self.wo(o)
             if self.process_group is not None:
-                torch.distributed.all_reduce(hidden_states, group=self.process_group)
+                with self._timed("exchange_o_proj"):
+                    torch.distributed.all_reduce(hidden_states, group=self.process_group)
             # residual add + post-attention RMSNorm (:229-231) in one pass
             residual, hidden_states = ops.add_rmsnorm(hidden_states, residual,
                                                       self.post_attention_layernorm_weight,
                                                       self.post_attention_layernorm_variance_epsilon)
-        return self._mlp(hidden_states, residual).view(bsz, q_len, self.dim)
+        # [B, 1, H]; under down_exchange="scatter" the [B / world, 1, H] rows this rank owns
+        return self._mlp(hidden_states, residual).view(-1, q_len, self.dim)
 
     def _timed(self, name):
         return _EventPair(self.timers, name)
 
     def check_status(self):
-        """Synchronising check of the device status word."""
+        """Synchronising check of the device status words: the layer's own and those of its exchanges
+        (an expired cross-rank wait shows up here)."""
         ops.raise_on_status(self.status)
+        for ex in (self.fused, self.fused_down):
+            if ex is not None:
+                ops.raise_on_status(ex.status)
 
-    def make_graphed(self, example: torch.Tensor, warmup: int = 3):
-        """Capture one forward in a CUDA graph.  Returns (static_input, static_output, graph)."""
-        static_in = example.clone()
+    def make_graphed(self, example: torch.Tensor, warmup: int = 3, static_in: Optional[torch.Tensor] = None):
+        """Capture one forward in a CUDA graph.  Returns (static_input, static_output, graph).  `static_in`:
+        the buffer the graph reads its input from (default: a copy of `example`)."""
+        if static_in is None:
+            static_in = example.clone()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):

@@ -2,9 +2,11 @@
 
 Rank r of `world` owns KV heads [r*Hkv/world, (r+1)*Hkv/world) with their query groups, the
 matching rows of the fused QKV projection and columns of the output projection, and its slice of
-the KV pages and page summaries.  Append, scoring, selection and attention never cross ranks; the
-only exchange is the sum of the o_proj partial results.  Follows the weight split of LiteSys
-litesys/models/qwen_layer.py:354-379 and the all-reduce of litesys/models/qwen3_dist.py:111-112.
+the KV pages and page summaries.  Append, scoring, selection and attention never cross ranks.  The
+layer has two exchanges: the sum of the o_proj partial results and, with the MLP split by
+`shard_mlp`, the sum of the down_proj partial results; the residual is added once, after each sum.
+Follows the weight split of LiteSys litesys/models/qwen_layer.py:354-379 and the two all-reduces of
+litesys/models/qwen3_dist.py:111-112 and :120-121.
 """
 from __future__ import annotations
 
