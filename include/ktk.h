@@ -211,12 +211,16 @@ KTK_API int ktk_sparse_decode(const void* q, const void* kv_cache, const int32_t
  * started, so that an allocation made on its behalf would fail or shrink the pool; or a
  * decode loop in which the device-wide synchronisation of cudaMalloc is not acceptable.
  *
- * Same arguments and results as ktk_sparse_decode, minus `workspace`.  The partial
- * results of a split decode go to a 16 MiB array that is part of the library image
- * (ktk_noalloc_scratch_bytes()); every GPU that loads the library keeps that array until
- * the process ends.  A call whose splits need more (batch * Hq * num_splits * 520 bytes)
- * returns KTK_ERR_TOO_LARGE and launches nothing.  The call itself performs no
- * cudaMalloc / cudaFree and uses no allocating library routine.
+ * Same arguments (num_splits = 0 and KTK_SPLITS_BALANCED included) and results as
+ * ktk_sparse_decode, minus `workspace`.  The partial results of a split decode go to a
+ * 16 MiB array that is part of the library image (ktk_noalloc_scratch_bytes()); every GPU
+ * that loads the library keeps that array until the process ends.  What a call needs is
+ * ktk_decode_workspace_bytes(): for KTK_SPLITS_BALANCED (what num_splits = 0 means for
+ * bf16) a fixed 2 to 4 MB whatever the batch -- two partial slots per resident CTA -- so
+ * that case always fits; for an explicit split count batch * Hq * num_splits * 520 bytes,
+ * and a call that needs more than the array holds returns KTK_ERR_TOO_LARGE and launches
+ * nothing.  The call itself performs no cudaMalloc / cudaFree and uses no allocating
+ * library routine.
  *
  * The first call on a device looks up the array's device address (one runtime query, no
  * allocation); make that first call outside any stream capture.  All calls on a device

@@ -469,8 +469,8 @@ extern "C" int ktk_sparse_decode_noalloc(const void* q, const void* kv_cache, co
     }
     int rc = check_shape(shape, "ktk_sparse_decode_noalloc");
     if (rc != KTK_OK) return rc;
-    if (num_splits < 0 || num_splits > 256) {
-        set_error("ktk_sparse_decode_noalloc: num_splits %d outside [0, 256]", num_splits);
+    if (num_splits != KTK_SPLITS_BALANCED && (num_splits < 0 || num_splits > 256)) {
+        set_error("ktk_sparse_decode_noalloc: num_splits %d is neither KTK_SPLITS_BALANCED nor in [0, 256]", num_splits);
         return KTK_ERR_ARG;
     }
     if (num_splits == 0) num_splits = policy_num_splits(shape, variant, topk + 1);

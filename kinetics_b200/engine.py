@@ -361,13 +361,18 @@ class Engine:
         gen_counts = [0] * self.max_batch_size
         meta = [None] * self.max_batch_size
 
+        preprocessed = -1                          # index of the last request the hook has seen
+
         def try_fill(slot: int) -> bool:
-            nonlocal pending
+            nonlocal pending, preprocessed
             if pending >= total:
                 return False
             req = requests[pending]
-            if self.preprocess is not None:
+            if self.preprocess is not None and preprocessed < pending:
+                # once per request, as in the reference: a request that has to wait for pages comes back
+                # here on every refill attempt, and a hook need not be idempotent
                 self.preprocess(req)
+                preprocessed = pending
             ids = torch.as_tensor(req["input_ids"]).reshape(1, -1)
             if not self.can_admit(ids.shape[1], max_new_tokens):
                 return False                       # the pool is full: wait for a sequence to retire

@@ -317,6 +317,7 @@ def dense_decode(q, kv_cache, kv_indices, kv_indptr, kv_last_page_len, max_pages
                                        _ptr(kv_last_page_len), vp, max_pages_per_seq, sm_scale, _ptr(out),
                                        _ptr(workspace), wsb, num_splits, variant, ctypes.byref(shp),
                                        _ptr(status), _stream()))
+    _launched(1 if num_splits == 1 else 2)
     return out
 
 

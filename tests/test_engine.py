@@ -236,6 +236,25 @@ def test_engine_loop_serves_every_request(num_pages, slots):
     assert all(n == 1 or len(s) == 1 for s, n in model.calls)
 
 
+def test_preprocess_hook_sees_every_request_once_even_when_it_waits_for_pages():
+    # a hook that is not idempotent (it prepends a token): a request that waits for pages must not be
+    # preprocessed again on every refill attempt
+    rng = random.Random(5)
+    requests = [{"id": i, "input_ids": [rng.randrange(1, 60) for _ in range(rng.randrange(10, 20))]} for i in range(7)]
+    seen = []
+
+    def prepend(req):
+        seen.append(req["id"])
+        req["input_ids"] = [0] + list(req["input_ids"])
+
+    kv, model = HostKV(4, 3), CountingModel()           # 3 pages: requests queue up behind one another
+    eng = Engine(model, kv, max_seq_len=64, device="cpu", temperature=0.0, eos=[EOS], repeat_check=False,
+                 preprocess=prepend)
+    done = eng.offline_exec(requests, 12)
+    assert sorted(seen) == list(range(7))
+    assert all(r["input_ids"][0] == 0 and r["input_ids"][1] != 0 for r in done)
+
+
 def test_engine_refuses_a_request_that_can_never_fit():
     kv, model = HostKV(2, 1), CountingModel()
     eng = Engine(model, kv, max_seq_len=64, device="cpu", eos=[EOS], repeat_check=False)

@@ -62,7 +62,11 @@ def _run_pair(device, seed, lens, Hkv, G, topk, splits, variant):
                         oracle.default_scale())
     qd, seld = q.to(device), sel.to(device)
     B, Hq = q.shape[:2]
-    ws = torch.empty(ops.decode_workspace_bytes(B, Hkv, G, splits), dtype=torch.uint8, device=device)
+    # 0 = the library's policy, which for bf16 is the balanced partition (KTK_SPLITS_BALANCED = -1)
+    resolved = ops.decode_num_splits(B, Hkv, G, topk + 1) if splits == 0 and variant != 1 else splits
+    if splits == 0 and variant != 1:
+        assert resolved == ops.SPLITS_BALANCED
+    ws = torch.empty(max(1, ops.decode_workspace_bytes(B, Hkv, G, resolved)), dtype=torch.uint8, device=device)
     want = ops.sparse_decode(qd, d["kv_cache"], seld, d["kv_indptr"], d["kv_last_page_len"], workspace=ws,
                              num_splits=splits, variant=variant)
     got = torch.full_like(want, float("nan"))
@@ -79,6 +83,14 @@ def _run_pair(device, seed, lens, Hkv, G, topk, splits, variant):
     # same kernels, same split partition: identical bits; and within the bf16 tolerance of the oracle
     assert torch.equal(got, want)
     torch.testing.assert_close(got.float().cpu(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.gpu
+def test_noalloc_decode_default_and_balanced_splits_two_calls_in_a_row(cuda_device):
+    # what every bf16 caller gets without asking: num_splits = 0 resolves to the balanced partition (stream
+    # kernel + combine on the built-in array); then the same partition asked for by name
+    _run_pair(cuda_device, seed=73, lens=[2049, 1500, 777, 33, 4000, 16], Hkv=2, G=4, topk=48, splits=0, variant=0)
+    _run_pair(cuda_device, seed=74, lens=[300, 2049, 5000], Hkv=1, G=8, topk=24, splits=-1, variant=0)
 
 
 @pytest.mark.gpu
