@@ -176,3 +176,88 @@ def test_ragged_gqa2_properties_at_the_cfg5_shape(cuda_device):
             qq = q[b, h * G:(h + 1) * G].float()
             p = torch.softmax(qq @ keys.t() / math.sqrt(128), dim=-1)
             torch.testing.assert_close(out[b, h * G:(h + 1) * G].float(), p @ vals, rtol=2e-2, atol=2e-2)
+
+
+def test_balanced_decode_at_the_headline_geometry(cuda_device):
+    # BASELINE.json configs[2], one KV-head shard: 4096 lists of 128 selected pages + the page being filled,
+    # G=4, bf16 -- the geometry the benchmark runs (444 CTAs, about 1190 list positions and 9 lists each).
+    # The lists point into a small physical pool (ids are reused): the kernels only read it.
+    from kinetics_b200 import ops
+    B, k, G, pool = 4096, 128, 4, 8192
+    torch.manual_seed(21)
+    cache = torch.randn(pool, 2, 16, 1, 128, device=cuda_device, dtype=torch.bfloat16)
+    q = torch.randn(B, G, 128, device=cuda_device, dtype=torch.bfloat16)
+    g = torch.Generator(device="cpu").manual_seed(22)
+    sel = torch.randint(0, pool, (B, 1, k + 1), generator=g).to(torch.int32).to(cuda_device)
+    indptr = torch.arange(B + 1, dtype=torch.int32, device=cuda_device) * 2049      # 2048 scored pages + 1
+    last = torch.randint(1, 17, (B,), generator=g).to(torch.int32).to(cuda_device)
+    status = ops.new_status(cuda_device)
+    balanced = ops.sparse_decode(q, cache, sel, indptr, last, num_splits=ops.SPLITS_BALANCED, status=status)
+    default = ops.sparse_decode(q, cache, sel, indptr, last, status=status)
+    per_list = ops.sparse_decode(q, cache, sel, indptr, last, num_splits=1, status=status)
+    ops.raise_on_status(status)
+    assert torch.equal(balanced, default)                    # num_splits = 0 means the balanced partition for bf16
+    # the balanced partition cuts some lists in two and merges the pieces: same math, other rounding
+    torch.testing.assert_close(balanced.float(), per_list.float(), rtol=2e-2, atol=2e-2)
+    # determinism: the cut points follow from the shapes alone
+    assert torch.equal(balanced, ops.sparse_decode(q, cache, sel, indptr, last, status=status))
+    # fp32 torch attention over the listed pages, sampled rows from the whole batch (first and last CTA included)
+    rows = [0, 1, 8, 9, 10, 2047, 2048, 4086, 4094, 4095] + torch.randint(0, B, (54,), generator=g).tolist()
+    for b in rows:
+        kv = cache[sel[b, 0].long()][:, :, :, 0].float()                          # [k+1, 2, 16, 128]
+        ntok = k * 16 + int(last[b])
+        keys = kv[:, 0].reshape(-1, 128)[:ntok]
+        vals = kv[:, 1].reshape(-1, 128)[:ntok]
+        p = torch.softmax(q[b].float() @ keys.t() / math.sqrt(128), dim=-1)
+        torch.testing.assert_close(balanced[b].float(), p @ vals, rtol=2e-2, atol=2e-2)
+
+
+def _ulps_apart(a, b):
+    """Distance of two fp32 tensors in units in the last place (through the order-preserving integer map)."""
+    def key(x):
+        i = x.contiguous().view(torch.int32).to(torch.int64)
+        return torch.where(i < 0, -(i & 0x7FFFFFFF), i)
+    return (key(a) - key(b)).abs()
+
+
+def test_selected_sets_against_the_reference_statement_in_fp32(cuda_device):
+    # The reference selects with einsum(...).mean(1) followed by topk (benchmark/blocktopk_decoder.py:216-217).
+    # Evaluated in fp32 its sums run in another order than the kernel's fixed order, so a row may pick a
+    # different SET only where the k-th and (k+1)-th scores all but coincide.  At B=4096, 2048 pages, k=128:
+    # count the rows whose set differs and require each difference to be a near tie.  Two fp32 summation
+    # orders of one 128-term score were measured up to 6 ulp apart (typically < 1), so two pages can swap sides
+    # when their reference scores lie within about twice that: the bound is 16 ulp around the k-th score.
+    from kinetics_b200 import ops
+    B, n, k, G = 4096, 2048, 128, 4
+    torch.manual_seed(31)
+    summ = torch.randn(B, 1, n + 8, 128, device=cuda_device, dtype=torch.bfloat16)
+    q = torch.randn(B, G, 128, device=cuda_device, dtype=torch.bfloat16)
+    table = torch.arange(B * (n + 1), dtype=torch.int32, device=cuda_device)
+    indptr = torch.arange(B + 1, dtype=torch.int32, device=cuda_device) * (n + 1)
+    last = torch.ones(B, dtype=torch.int32, device=cuda_device)
+    logical = torch.empty(B, 1, k + 1, dtype=torch.int32, device=cuda_device)
+    status = ops.new_status(cuda_device)
+    ops.select_pages(q, summ, table, indptr, last, k, B * (n + 1), out_logical=logical, status=status)
+    ops.raise_on_status(status)
+    mine = logical[:, 0, :k].long()
+    assert not torch.backends.cuda.matmul.allow_tf32                                         # plain fp32 products
+    csim = torch.einsum("bgd,bnd->bgn", q.float(), summ[:, 0, :n].float()).mean(dim=1)      # :216 in fp32
+    order = torch.sort(-csim, dim=1, stable=True).indices[:, :k]                             # :217, ties to the lowest page
+    in_mine = torch.zeros(B, n, dtype=torch.bool, device=cuda_device).scatter_(1, mine, True)
+    in_ref = torch.zeros(B, n, dtype=torch.bool, device=cuda_device).scatter_(1, order, True)
+    differ = (in_mine != in_ref).any(1)
+    rows = differ.nonzero().flatten().tolist()
+    worst = 0
+    for b in rows:
+        only_mine = (in_mine[b] & ~in_ref[b]).nonzero().flatten()
+        only_ref = (in_ref[b] & ~in_mine[b]).nonzero().flatten()
+        assert only_mine.numel() == only_ref.numel()
+        # every page one side took instead of the other lies within 16 ulp of the reference's k-th score
+        kth = csim[b, order[b, -1]]
+        for idx in torch.cat([only_mine, only_ref]).tolist():
+            gap = int(_ulps_apart(csim[b, idx], kth))
+            worst = max(worst, gap)
+            assert gap <= 16, (b, idx, gap)
+    print(f"selected sets: {B - len(rows)}/{B} rows equal the fp32 reference statement; "
+          f"{len(rows)} differ, all at near ties (largest gap {worst} ulp)")
+    assert len(rows) <= B // 100
