@@ -20,7 +20,9 @@ same constructor arguments, ``forward(hidden_states[B, 1, H]) -> [B, 1, H]`` and
 """
 from __future__ import annotations
 
+import contextlib
 import math
+import weakref
 from typing import Optional
 
 import torch
@@ -185,6 +187,8 @@ class _PagedDecoderLayer(nn.Module):
         elif tuple(kv_cache.shape) != shape or kv_cache.dtype != dtype:
             raise ValueError(f"kv_cache must be {shape} {dtype}")
         self.kv_cache = kv_cache          # may be shared with another layer (dense next to sparse)
+        # the bindings ops.py keeps per cache address go when the layer goes
+        weakref.finalize(self, ops.unbind_address, kv_cache.data_ptr())
         self.decode_run = torch.ops.mylib.decode
         self.capture = None               # set to a dict to keep q / k / v of the last forward (tests)
         self.timers = None                # set to a dict name -> list of (start, end) CUDA events
@@ -203,7 +207,7 @@ class _PagedDecoderLayer(nn.Module):
         up = self.up_proj(hidden_states)
         gate = self.gate_proj(hidden_states)
         if self.hidden_act == "silu":
-            hidden_states = ops.silu_mul(gate, up)
+            hidden_states = torch.ops.ktk.silu_mul(gate, up)
         else:
             from transformers.activations import ACT2FN
             hidden_states = ACT2FN[self.hidden_act](gate) * up
@@ -228,17 +232,20 @@ class _PagedDecoderLayer(nn.Module):
 
     @torch.inference_mode()
     def forward(self, hidden_states):
-        self._bind()      # the torch ops find this layer's page state through its kv_cache
+        # The torch ops find this layer's page state through its kv_cache.  Under torch.compile the binding
+        # made by prepare_wrapper() stands (the reference calls it right after compiling, blocktopk.py:41-44).
+        if not torch.compiler.is_compiling():
+            self._bind()
         bsz, q_len, _ = hidden_states.size()
         residual = hidden_states.reshape(bsz * q_len, self.dim)
         # input RMSNorm (mylib::layer_norm of the reference, :192), 16-byte accesses
-        _, hidden_states = ops.add_rmsnorm(residual, None, self.input_layernorm_weight,
-                                           self.input_layernorm_variance_epsilon)
+        hidden_states = torch.ops.ktk.rms_norm(residual, self.input_layernorm_weight,
+                                               self.input_layernorm_variance_epsilon)
         proj = self.wqkv(hidden_states)
         # split + q-norm + k-norm (:198-207) in one launch
-        query_states, key_states, value_states = ops.qkv_norm(proj, self.qnorm_weight, self.knorm_weight,
-                                                              self.qnorm_variance_epsilon, self.num_heads,
-                                                              self.num_kv_heads)
+        query_states, key_states, value_states = torch.ops.ktk.qkv_norm(
+            proj, self.qnorm_weight, self.knorm_weight, self.qnorm_variance_epsilon, self.num_heads,
+            self.num_kv_heads)
         if self.capture is not None:
             self.capture.update(q=query_states.clone(), k=key_states.clone(), v=value_states.clone())
         with self._timed("append"):
@@ -260,14 +267,14 @@ class _PagedDecoderLayer(nn.Module):
                 with self._timed("exchange_o_proj"):
                     torch.distributed.all_reduce(hidden_states, group=self.process_group)
             # residual add + post-attention RMSNorm (:229-231) in one pass
-            residual, hidden_states = ops.add_rmsnorm(hidden_states, residual,
-                                                      self.post_attention_layernorm_weight,
-                                                      self.post_attention_layernorm_variance_epsilon)
+            residual, hidden_states = torch.ops.ktk.add_rms_norm(hidden_states, residual,
+                                                                 self.post_attention_layernorm_weight,
+                                                                 self.post_attention_layernorm_variance_epsilon)
         # [B, 1, H]; under down_exchange="scatter" the [B / world, 1, H] rows this rank owns
         return self._mlp(hidden_states, residual).view(-1, q_len, self.dim)
 
     def _timed(self, name):
-        return _EventPair(self.timers, name)
+        return contextlib.nullcontext() if self.timers is None else _EventPair(self.timers, name)
 
     def check_status(self):
         """Synchronising check of the device status words: the layer's own and those of its exchanges
@@ -321,9 +328,9 @@ class BlockTopkDecoderLayer(_PagedDecoderLayer):
     def _attention(self, query_states):
         # benchmark/blocktopk_decoder.py:216-221, one kernel
         with self._timed("select"):
-            ops.select_pages(query_states, self.compressed_key_cache, self.paged_kv_indices, self.full_kv_indptr,
-                             self.last_kv_lens, self.topk_page, self.total_pages, out=self._sel_view(),
-                             status=self.status)
+            torch.ops.ktk.select_pages_into(query_states, self.compressed_key_cache, self.paged_kv_indices,
+                                            self.full_kv_indptr, self.last_kv_lens, self.topk_page, self.total_pages,
+                                            self._sel_view(), self.status)
         with self._timed("decode"):
             return self.decode_run(query_states, self.kv_cache)
 

@@ -452,8 +452,14 @@ def bind_summaries(kv_cache: torch.Tensor, summaries: Optional[torch.Tensor]) ->
 
 
 def unbind(kv_cache: torch.Tensor) -> None:
-    _PLANS.pop(kv_cache.data_ptr(), None)
-    _SUMMARIES.pop(kv_cache.data_ptr(), None)
+    unbind_address(kv_cache.data_ptr())
+
+
+def unbind_address(address: int) -> None:
+    """Forget the plan and summaries bound to the cache at `address` (a layer that is deleted calls this, so
+    that a later cache which happens to get the same address does not inherit them)."""
+    _PLANS.pop(address, None)
+    _SUMMARIES.pop(address, None)
 
 
 # --------------------------------------------------------------------------------------
@@ -587,4 +593,83 @@ def _append_kv_with_summary(k, v, kv_cache, summaries, kv_indices, kv_indptr, kv
 
 @torch.library.register_fake("ktk::append_kv_with_summary")
 def _append_kv_with_summary_fake(k, v, kv_cache, summaries, kv_indices, kv_indptr, kv_last_page_len):
+    return None
+
+
+# --------------------------------------------------------------------------------------
+# the fused glue kernels and the selection as torch ops, so that torch.compile(fullgraph=True)
+# traces a layer forward end to end the way it traces the reference's
+# (benchmark/blocktopk.py:41-43); the functional wrappers above stay the eager entry points
+# --------------------------------------------------------------------------------------
+
+torch.library.define("ktk::rms_norm", "(Tensor x, Tensor weight, float eps) -> Tensor")
+
+
+@torch.library.impl("ktk::rms_norm", "cuda")
+def _rms_norm_op(x, weight, eps):
+    return add_rmsnorm(x, None, weight, eps)[1]
+
+
+@torch.library.register_fake("ktk::rms_norm")
+def _rms_norm_fake(x, weight, eps):
+    return torch.empty_like(x)
+
+
+torch.library.define("ktk::add_rms_norm", "(Tensor x, Tensor residual, Tensor weight, float eps) -> (Tensor, Tensor)")
+
+
+@torch.library.impl("ktk::add_rms_norm", "cuda")
+def _add_rms_norm_op(x, residual, weight, eps):
+    return add_rmsnorm(x, residual, weight, eps)
+
+
+@torch.library.register_fake("ktk::add_rms_norm")
+def _add_rms_norm_fake(x, residual, weight, eps):
+    return torch.empty_like(x), torch.empty_like(x)
+
+
+torch.library.define(
+    "ktk::qkv_norm",
+    "(Tensor proj, Tensor wq, Tensor wk, float eps, int num_q_heads, int num_kv_heads) -> (Tensor, Tensor, Tensor)")
+
+
+@torch.library.impl("ktk::qkv_norm", "cuda")
+def _qkv_norm_op(proj, wq, wk, eps, num_q_heads, num_kv_heads):
+    return qkv_norm(proj, wq, wk, eps, num_q_heads, num_kv_heads)
+
+
+@torch.library.register_fake("ktk::qkv_norm")
+def _qkv_norm_fake(proj, wq, wk, eps, num_q_heads, num_kv_heads):
+    B = proj.numel() // ((num_q_heads + 2 * num_kv_heads) * HEAD_DIM)
+    return (proj.new_empty(B, num_q_heads, HEAD_DIM), proj.new_empty(B, num_kv_heads, HEAD_DIM),
+            proj.new_empty(B, num_kv_heads, HEAD_DIM))
+
+
+torch.library.define("ktk::silu_mul", "(Tensor gate, Tensor up) -> Tensor")
+
+
+@torch.library.impl("ktk::silu_mul", "cuda")
+def _silu_mul_op(gate, up):
+    return silu_mul(gate, up)
+
+
+@torch.library.register_fake("ktk::silu_mul")
+def _silu_mul_fake(gate, up):
+    return torch.empty_like(gate)
+
+
+torch.library.define(
+    "ktk::select_pages_into",
+    "(Tensor q, Tensor summaries, Tensor kv_indices, Tensor kv_indptr, Tensor kv_last_page_len, int topk, "
+    "int num_pages, Tensor(a!) out, Tensor(b!) status) -> ()",
+)
+
+
+@torch.library.impl("ktk::select_pages_into", "cuda")
+def _select_pages_into(q, summaries, kv_indices, kv_indptr, kv_last_page_len, topk, num_pages, out, status):
+    select_pages(q, summaries, kv_indices, kv_indptr, kv_last_page_len, topk, num_pages, out=out, status=status)
+
+
+@torch.library.register_fake("ktk::select_pages_into")
+def _select_pages_into_fake(q, summaries, kv_indices, kv_indptr, kv_last_page_len, topk, num_pages, out, status):
     return None
