@@ -230,7 +230,7 @@ class _PagedDecoderLayer(nn.Module):
             torch.distributed.all_reduce(part, group=self.process_group)
             return part.add_(residual)
 
-    @torch.inference_mode()
+    @torch.no_grad()      # the reference uses inference_mode (:186); torch 2.11 cannot compile a function decorated with it
     def forward(self, hidden_states):
         # The torch ops find this layer's page state through its kv_cache.  Under torch.compile the binding
         # made by prepare_wrapper() stands (the reference calls it right after compiling, blocktopk.py:41-44).

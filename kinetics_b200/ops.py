@@ -251,8 +251,8 @@ def _decode_args(q, kv_cache, max_entries, workspace, num_splits, variant=0):
         num_splits = decode_num_splits(B, shp.num_kv_heads, shp.group_size, max_entries,
                                        torch.float32 if variant == VARIANT_SIMT else q.dtype)
     need = int(_lib.load().ktk_decode_workspace_bytes(ctypes.byref(shp), num_splits))
-    if need and workspace is None and num_splits == SPLITS_BALANCED:
-        workspace = _shared_workspace(q.device, need)      # a few MB, independent of the batch
+    if need and workspace is None:
+        workspace = _shared_workspace(q.device, need)      # the balanced partition: a few MB whatever the batch
     if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
         raise RuntimeError(f"decode with {num_splits} splits needs a {need}-byte workspace "
                            "(decode_workspace_bytes); pass one, or num_splits=1")
@@ -425,12 +425,15 @@ class DecodePlan:
         if need and (self.workspace is None or self.workspace.numel() < need):
             self.workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
 
-    def run(self, q):
+    def run(self, q, kv_cache=None):
+        """Attention of q under this plan; `kv_cache` (default: the plan's own) is the tensor the pages are read
+        from -- like flashinfer's wrapper.run(q, kv_cache), which takes the cache as an argument."""
         self._ensure_workspace(q)
+        cache = self.kv_cache if kv_cache is None else kv_cache
         if self.sel_pages is not None:
-            return sparse_decode(q, self.kv_cache, self.sel_pages, self.kv_indptr, self.kv_last_page_len,
+            return sparse_decode(q, cache, self.sel_pages, self.kv_indptr, self.kv_last_page_len,
                                  self.sm_scale, self.workspace, self.num_splits, self.variant, status=self.status)
-        return dense_decode(q, self.kv_cache, self.kv_indices, self.kv_indptr, self.kv_last_page_len,
+        return dense_decode(q, cache, self.kv_indices, self.kv_indptr, self.kv_last_page_len,
                             self.max_pages_per_seq, self.sm_scale, self.workspace, self.num_splits, self.variant,
                             status=self.status)
 
@@ -439,8 +442,26 @@ _PLANS: dict[int, DecodePlan] = {}
 _SUMMARIES: dict[int, torch.Tensor] = {}
 
 
+_LAST_PLAN: list = [None]     # weak reference to the plan bound last
+
+
 def bind_decode_plan(plan: DecodePlan) -> None:
+    import weakref
     _PLANS[plan.kv_cache.data_ptr()] = plan
+    _LAST_PLAN[0] = weakref.ref(plan)
+
+
+def _plan_for(kv_cache: torch.Tensor) -> Optional[DecodePlan]:
+    """The plan bound to this cache; for a cache nobody bound (a copy of a bound one, as torch.library.opcheck
+    makes), the plan bound last if its cache has the same shape and dtype -- the reference's op likewise runs
+    whatever cache it is handed through the one wrapper it closes over (benchmark/blocktopk_decoder.py:171-178)."""
+    plan = _PLANS.get(kv_cache.data_ptr())
+    if plan is None and _LAST_PLAN[0] is not None:
+        last = _LAST_PLAN[0]()
+        if last is not None and last.kv_cache.shape == kv_cache.shape and last.kv_cache.dtype == kv_cache.dtype \
+                and last.kv_cache.device == kv_cache.device:
+            plan = last
+    return plan
 
 
 def bind_summaries(kv_cache: torch.Tensor, summaries: Optional[torch.Tensor]) -> None:
@@ -493,10 +514,10 @@ torch.library.define("mylib::decode", "(Tensor q, Tensor kv_cache) -> Tensor")
 
 @torch.library.impl("mylib::decode", "cuda")
 def _decode(q, kv_cache):
-    plan = _PLANS.get(kv_cache.data_ptr())
+    plan = _plan_for(kv_cache)
     if plan is None:
         raise RuntimeError("mylib::decode: no DecodePlan bound to this kv_cache (bind_decode_plan)")
-    return plan.run(q)
+    return plan.run(q, kv_cache)
 
 
 @torch.library.register_fake("mylib::decode")
