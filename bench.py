@@ -80,7 +80,7 @@ def parse():
     ap.add_argument("--down-exchange", default="scatter", choices=["scatter", "allreduce"],
                     help="N > 1: what the down_proj exchange leaves on a rank: its row slice of the layer output "
                          "(reduce-scatter + residual) or all rows (all-reduce + residual, the reference's form)")
-    ap.add_argument("--exchange-schedule", default="pipelined", choices=["pipelined", "lockstep"],
+    ap.add_argument("--exchange-schedule", default="lockstep", choices=["pipelined", "lockstep"],
                     help="schedule of the fused o_proj exchange kernel")
     ap.add_argument("--reps", type=int, default=5, help="repetitions of the --steps loop; the median is reported")
     ap.add_argument("--no-flashinfer", action="store_true",

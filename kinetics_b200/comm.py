@@ -35,8 +35,13 @@ class FusedExchange:
     """
 
     def __init__(self, group, rows: int, cols: int, dtype, device, mode: int = _lib.ALLREDUCE_AUTO,
-                 result: str = "allreduce_norm", schedule: str = "pipelined"):
+                 result: str = "allreduce_norm", schedule: str = None):
         import torch.distributed._symmetric_memory as symm_mem
+
+        if schedule is None:
+            # measured on two B200s, 32 MiB: the lock-step all-reduce + norm takes 79 us, the row-pipelined one
+            # 109 us (one system-scope release per row); only the pipelined kernel has the other two results
+            schedule = "lockstep" if result == "allreduce_norm" else "pipelined"
 
         if dtype != torch.bfloat16:
             raise TypeError("the fused exchange is built for bfloat16")
@@ -109,7 +114,7 @@ class FusedAllReduceNorm(FusedExchange):
     """All-reduce + residual add + RMSNorm (the o_proj exchange)."""
 
     def __init__(self, group, rows: int, cols: int, dtype, device, mode: int = _lib.ALLREDUCE_AUTO,
-                 schedule: str = "pipelined"):
+                 schedule: str = None):
         super().__init__(group, rows, cols, dtype, device, mode=mode, result="allreduce_norm", schedule=schedule)
 
 

@@ -11,9 +11,13 @@
 //     fence + flag: "row j of this CTA is on its way", to the same-index CTA of every rank
 //     rows that the same-index CTAs of the other ranks have flagged meanwhile are normalised locally
 // so that a rank's outbound link (the partials it serves to the others' reductions) and its inbound
-// link (the sums the others send) are busy at the same time, and the local normalisation of the
+// link (the sums the others send) can be busy at the same time, and the local normalisation of the
 // received rows hides behind the link time.  In the lock-step form of ktk_comm.cu all CTAs load,
 // then all CTAs store, then all normalise.
+// Measured on two B200s over 32 MiB (CUDA events, 50 launches): reduce-scatter + residual 46 us (NCCL
+// reduce_scatter alone 55 us); all-reduce + residual + norm 109 us here against 79 us for the lock-step
+// kernel, whose single fence per CTA costs less than one system-scope release per row -- the lock-step
+// kernel therefore stays the default for that result, this kernel serves the other two.
 //
 // Flags: one word per (CTA, source rank) in every rank's memory, written with st.release.sys by the
 // source and polled with ld.acquire.sys; the values only grow (a per-CTA launch counter kept in
@@ -63,19 +67,6 @@ __device__ __forceinline__ void issue_row(RowLoads<NV, PEERS>& L, const __nv_bfl
     }
 }
 
-// block-wide sum of squares -> 1 / rms
-__device__ __forceinline__ float block_inv_rms(float ss, float* part, int cols, float eps) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    __syncthreads();                                   // `part` of the previous row has been read
-    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    float tot = 0.0f;
-#pragma unroll
-    for (int i = 0; i < kXThreads / 32; ++i) tot += part[i];
-    return rsqrtf(tot / (float)cols + eps);
-}
-
 template <int NV>
 __device__ __forceinline__ void store_norm(const float (&v)[NV][8], float inv, const __nv_bfloat16* __restrict__ w,
                                            __nv_bfloat16* norm_row, int nvec) {
@@ -97,47 +88,57 @@ __device__ __forceinline__ void store_norm(const float (&v)[NV][8], float inv, c
     }
 }
 
-// RMSNorm of a row of this rank's own copy of `sum` (a row another rank sent), read at L2
-template <int NV>
-__device__ __forceinline__ void norm_received_row(const __nv_bfloat16* sum_row, const __nv_bfloat16* __restrict__ w,
-                                                  __nv_bfloat16* norm_row, float* part, int nvec, int cols, float eps) {
-    float v[NV][8];
-    float ss = 0.0f;
-    uint4 sr[NV];
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const int c = threadIdx.x + i * kXThreads;
-        if (c < nvec) sr[i] = __ldcg(reinterpret_cast<const uint4*>(sum_row + (size_t)c * 8));
-    }
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const int c = threadIdx.x + i * kXThreads;
-        if (c < nvec) {
-            unpack8(sr[i], v[i]);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
-        }
-    }
-    const float inv = block_inv_rms(ss, part, cols, eps);
-    store_norm<NV>(v, inv, w, norm_row, nvec);
+// ---- CTA-internal hand-off between the data warps and the signalling warp ----
+__device__ __forceinline__ void bar_sync_named(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+__device__ __forceinline__ void st_release_cta_shared(int* p, int v) {
+    asm volatile("st.release.cta.shared.s32 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_cta_shared(const int* p) {
+    int v;
+    asm volatile("ld.acquire.cta.shared.s32 %0, [%1];" : "=r"(v) : "r"((uint32_t)__cvta_generic_to_shared(p)) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_cta_shared_add(int* p, int v) {
+    asm volatile("red.release.cta.shared.add.s32 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(p)), "r"(v) : "memory");
+}
+
+constexpr int kXDataWarps = kXThreads / 32;
+constexpr int kXAllThreads = kXThreads + 32;     // + the signalling warp
+
+// rows of loads in flight per thread (the ring), by how much of a row a thread holds
+template <int NV, int PEERS>
+struct XDepth {
+    static constexpr int value = (PEERS == 4) ? (NV == 2 ? 2 : 3) : (PEERS == 2 ? (NV == 2 ? 2 : 5) : 3);
+    static constexpr int ctas_per_sm = (PEERS == 0 && NV == 1) ? 2 : 1;
+};
 
 // NV: vectors per thread.  PEERS = 0: the switch reduces and multicasts; PEERS = world (2 or 4): peer
 // loads and stores.  SCATTER: the sums of the owned rows stay on this rank (reduce-scatter), nothing
 // is sent and nothing is normalised.  NORM (all-reduce form only): RMSNorm of every row into `norm`.
+//
+// 16 data warps move rows; a 17th warp does all cross-rank signalling, so that no data warp ever sits in a
+// system-scope fence: a data warp that has stored its part of row j adds one to a shared counter (release,
+// CTA scope); the signalling warp sees the counter reach 16 * (j + 1) (acquire), then tells every rank "row
+// j of this CTA is on its way" (st.release.sys, cumulative over the data warps' stores) and publishes, in
+// shared memory, how many rows the same-index CTAs of the other ranks have flagged.
 template <int NV, int PEERS, bool SCATTER, bool NORM>
-__global__ void __launch_bounds__(kXThreads, (PEERS == 4 || NV == 2) ? 1 : 2)
+__global__ void __launch_bounds__(kXAllThreads, XDepth<NV, PEERS>::ctas_per_sm)
 exchange_rows_kernel(const __nv_bfloat16* x_mc, const __nv_bfloat16* const* x_peer,
                      const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ w,
                      __nv_bfloat16* sum_mc, __nv_bfloat16* const* sum_peer, __nv_bfloat16* sum_local,
                      __nv_bfloat16* norm_local, uint32_t* const* flags, uint32_t* launch_count, int rank, int world,
                      int rows, int cols, float eps, uint32_t stride, int32_t* status) {
-    __shared__ float part[kXThreads / 32];
+    constexpr int DEPTH = XDepth<NV, PEERS>::value;
+    __shared__ float part[kXDataWarps];
     __shared__ uint32_t s_epoch;
-    __shared__ int s_avail[kCommMaxWorld];      // rows the same-index CTA of rank p has flagged
+    __shared__ int s_avail[kCommMaxWorld];      // rows the same-index CTA of rank p has flagged (signalling warp writes)
+    __shared__ int s_take[kCommMaxWorld];       // snapshot of s_avail the data warps agree on
     __shared__ int s_done[kCommMaxWorld];       // rows of rank p this CTA has normalised
-    if (threadIdx.x == 0) s_epoch = launch_count[blockIdx.x];
-    if (threadIdx.x < kCommMaxWorld) { s_avail[threadIdx.x] = 0; s_done[threadIdx.x] = 0; }
+    __shared__ int s_warps_done;                // data-warp arrivals: 16 per finished row (per kernel for SCATTER)
+    if (threadIdx.x == 0) { s_epoch = launch_count[blockIdx.x]; s_warps_done = 0; }
+    if (threadIdx.x < kCommMaxWorld) { s_avail[threadIdx.x] = 0; s_take[threadIdx.x] = 0; s_done[threadIdx.x] = 0; }
     __syncthreads();
     const uint32_t base = s_epoch * stride;
     const int G = gridDim.x;
@@ -145,38 +146,112 @@ exchange_rows_kernel(const __nv_bfloat16* x_mc, const __nv_bfloat16* const* x_pe
     const int nvec = cols / 8;
     const int J = (per - (int)blockIdx.x + G - 1) / G;      // rows of every owner that fall to CTAs of this index
     uint32_t* my_flags = flags[rank] + (size_t)blockIdx.x * world;
+    const int lane = threadIdx.x & 31;
+    const bool signaller = threadIdx.x >= kXThreads;
 
     // every rank's partial output is complete (its GEMM precedes this kernel in stream order)
-    if ((int)threadIdx.x < world) st_release_sys(flags[threadIdx.x] + (size_t)blockIdx.x * world + rank, base + 1);
-    if ((int)threadIdx.x < world) flag_wait(my_flags + threadIdx.x, base + 1, status);
+    if (signaller && lane < world) {
+        st_release_sys(flags[lane] + (size_t)blockIdx.x * world + rank, base + 1);
+        flag_wait(my_flags + lane, base + 1, status);
+    }
     __syncthreads();
 
+    if (signaller) {
+        // ---------------- the signalling warp ----------------
+        int sent = 0;                   // own rows flagged so far (SCATTER: 0 or 1 for the closing flag)
+        const int to_send = SCATTER ? 1 : J;
+        const int per_flag = SCATTER ? kXDataWarps * 1 : kXDataWarps;
+        bool gave_up = false;
+        for (uint32_t spin = 0;; ++spin) {
+            const int arrived = ld_acquire_cta_shared(&s_warps_done);
+            const int ready = SCATTER ? (arrived >= per_flag ? 1 : 0) : arrived / per_flag;
+            while (sent < ready) {
+                // SCATTER: nobody may overwrite its partial output while a peer still reads it -- one closing flag
+                if (lane < world)
+                    st_release_sys(flags[lane] + (size_t)blockIdx.x * world + rank, base + 2 + (SCATTER ? 0 : sent));
+                ++sent;
+            }
+            bool in = true;
+            if (lane < world) {
+                const int32_t got = (int32_t)(ld_acquire_sys(my_flags + lane) - (base + 1));
+                const int want = SCATTER ? 1 : J;
+                const int have = got < 0 ? 0 : (got > want ? want : got);
+                if (!SCATTER) st_release_cta_shared(&s_avail[lane], gave_up ? J : have);
+                in = have >= want;
+            }
+            const bool all_in = __all_sync(0xffffffffu, in) || gave_up;
+            if (sent == to_send && all_in) break;
+            if (spin > (kCommSpinCap >> 2) && !gave_up) {
+                // a peer never arrived: record it, let the data warps run on (they wait for s_avail only)
+                if (lane == 0) report(status, KTK_STATUS_TIMEOUT);
+                gave_up = true;
+            }
+            if (spin > 16) __nanosleep(spin > 4096 ? 256 : 32);
+        }
+        if (lane == 0) launch_count[blockIdx.x] = s_epoch + 1;
+        return;
+    }
+
+    // ---------------- the data warps ----------------
+    auto data_sync = [&]() { bar_sync_named(1, kXThreads); };
+    auto inv_rms = [&](float ss) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        data_sync();                                   // `part` of the previous row has been read
+        if (lane == 0) part[threadIdx.x >> 5] = ss;
+        data_sync();
+        float tot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kXDataWarps; ++i) tot += part[i];
+        return rsqrtf(tot / (float)cols + eps);
+    };
+    auto norm_received = [&](size_t r) {
+        const __nv_bfloat16* sum_row = sum_local + r * cols;
+        float v[NV][8];
+        float ss = 0.0f;
+        uint4 sr[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = threadIdx.x + i * kXThreads;
+            if (c < nvec) sr[i] = __ldcg(reinterpret_cast<const uint4*>(sum_row + (size_t)c * 8));
+        }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = threadIdx.x + i * kXThreads;
+            if (c < nvec) {
+                unpack8(sr[i], v[i]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+            }
+        }
+        const float inv = inv_rms(ss);
+        store_norm<NV>(v, inv, w, norm_local + r * cols, nvec);
+    };
     // rows another rank has flagged so far: normalise those not yet done (never blocks)
     auto drain = [&]() {
-        if ((int)threadIdx.x < world) {
-            const int32_t got = (int32_t)(ld_acquire_sys(my_flags + threadIdx.x) - (base + 1));
-            s_avail[threadIdx.x] = got < 0 ? 0 : (got > J ? J : got);
-        }
-        __syncthreads();
+        if ((int)threadIdx.x < world) s_take[threadIdx.x] = ld_acquire_cta_shared(&s_avail[threadIdx.x]);
+        data_sync();
         for (int p = 1; p < world; ++p) {
             const int owner = (rank + p) % world;
-            const int have = s_avail[owner];
-            for (int j = s_done[owner]; j < have; ++j) {
-                const size_t r = (size_t)owner * per + blockIdx.x + (size_t)j * G;
-                norm_received_row<NV>(sum_local + r * cols, w, norm_local + r * cols, part, nvec, cols, eps);
-            }
-            __syncthreads();
+            const int have = s_take[owner];
+            for (int j = s_done[owner]; j < have; ++j)
+                norm_received((size_t)owner * per + blockIdx.x + (size_t)j * G);
+            data_sync();
             if (threadIdx.x == 0 && have > s_done[owner]) s_done[owner] = have;
         }
-        __syncthreads();
+        data_sync();
     };
 
-    RowLoads<NV, PEERS> cur, nxt;
+    RowLoads<NV, PEERS> ring[DEPTH];
     const int first = rank * per + blockIdx.x;
-    if (J > 0) issue_row<NV, PEERS>(cur, x_mc, x_peer, residual, first, cols, nvec);
+#pragma unroll
+    for (int a = 0; a < DEPTH - 1; ++a)
+        if (a < J) issue_row<NV, PEERS>(ring[a], x_mc, x_peer, residual, first + a * G, cols, nvec);
     for (int j = 0; j < J; ++j) {
         const int r = first + j * G;
-        if (j + 1 < J) issue_row<NV, PEERS>(nxt, x_mc, x_peer, residual, r + G, cols, nvec);
+        if (j + DEPTH - 1 < J)
+            issue_row<NV, PEERS>(ring[DEPTH - 1], x_mc, x_peer, residual, r + (DEPTH - 1) * G, cols, nvec);
+        const RowLoads<NV, PEERS>& cur = ring[0];
         float v[NV][8];
         float ss = 0.0f;
 #pragma unroll
@@ -225,43 +300,41 @@ exchange_rows_kernel(const __nv_bfloat16* x_mc, const __nv_bfloat16* const* x_pe
             }
         }
         if constexpr (!SCATTER) {
-            __threadfence_system();                        // this row is on its way to every rank
-            __syncthreads();
-            if ((int)threadIdx.x < world)
-                st_release_sys(flags[threadIdx.x] + (size_t)blockIdx.x * world + rank, base + 2 + j);
+            __syncwarp();                                  // this warp's part of the row is on its way
+            if (lane == 0) red_release_cta_shared_add(&s_warps_done, 1);
+            // the counter reads "rows finished" only while no warp runs a row ahead of another: with the norm
+            // the block reductions below keep the warps together, without it this barrier does
+            if constexpr (!NORM) data_sync();
         }
         if constexpr (NORM) {
-            const float inv = block_inv_rms(ss, part, cols, eps);
+            const float inv = inv_rms(ss);
             store_norm<NV>(v, inv, w, norm_local + (size_t)r * cols, nvec);
             if (j + 1 < J) drain();
         }
-        if (j + 1 < J) cur = nxt;
+#pragma unroll
+        for (int a = 0; a + 1 < DEPTH; ++a) ring[a] = ring[a + 1];
     }
 
     if constexpr (SCATTER) {
-        // nobody may overwrite its partial output while a peer still reads it: meet once more
-        __syncthreads();
-        if ((int)threadIdx.x < world) st_release_sys(flags[threadIdx.x] + (size_t)blockIdx.x * world + rank, base + 2);
-        if ((int)threadIdx.x < world) flag_wait(my_flags + threadIdx.x, base + 2, status);
-    } else {
-        // the rest of the other ranks' rows, owner by owner, row by row as the flags arrive.  Having
-        // seen a peer's last flag also means that it no longer reads this rank's partial output.
+        // every load of this warp has returned (its data was consumed): the closing flag may go out
+        __syncwarp();
+        if (lane == 0) red_release_cta_shared_add(&s_warps_done, 1);
+    } else if constexpr (NORM) {
+        // the rest of the other ranks' rows, owner by owner, row by row as the signalling warp publishes them
         for (int p = 1; p < world; ++p) {
             const int owner = (rank + p) % world;
-            if constexpr (NORM) {
-                for (int j = s_done[owner]; j < J; ++j) {
-                    if (threadIdx.x == 0) flag_wait(my_flags + owner, base + 2 + j, status);
-                    __syncthreads();
-                    const size_t r = (size_t)owner * per + blockIdx.x + (size_t)j * G;
-                    norm_received_row<NV>(sum_local + r * cols, w, norm_local + r * cols, part, nvec, cols, eps);
+            for (int j = s_done[owner]; j < J; ++j) {
+                if (threadIdx.x == 0) {
+                    for (uint32_t spin = 0; ld_acquire_cta_shared(&s_avail[owner]) <= j && spin < kCommSpinCap; ++spin)
+                        if (spin > 16) __nanosleep(64);
                 }
-            } else {
-                if (threadIdx.x == 0) flag_wait(my_flags + owner, base + 1 + J, status);
+                data_sync();
+                norm_received((size_t)owner * per + blockIdx.x + (size_t)j * G);
             }
         }
     }
-    __syncthreads();
-    if (threadIdx.x == 0) launch_count[blockIdx.x] = s_epoch + 1;
+    // (all-reduce without the norm: the signalling warp alone waits for the peers' last flags, which also
+    // means that none of them still reads this rank's partial output; the kernel ends when it returns)
 }
 
 // The ranks meet: thread p tells rank p that this rank arrived for the `epoch`-th time and waits for
@@ -296,9 +369,9 @@ extern "C" int ktk_rank_barrier(const void* flag_ptrs, void* launch_count, int32
     return KTK_OK;
 }
 
-// 512-thread CTAs resident per SM: the peer form at 4 ranks and rows wider than 4096 elements hold
-// more of a row per thread and run one per SM
-static int exchange_ctas_per_sm(int peers, int nv) { return (peers == 4 || nv == 2) ? 1 : 2; }
+// CTAs resident per SM: only the multicast form on rows of up to 4096 elements keeps few enough registers
+// for two; the others hold more of a row (and more rows in flight) per thread and run one per SM
+static int exchange_ctas_per_sm(int peers, int nv) { return (peers == 0 && nv == 1) ? 2 : 1; }
 
 // Every CTA must be resident: same-index CTAs of the ranks wait for one another.
 static int exchange_grid(int64_t rows, int world, int peers, int nv) {
@@ -359,7 +432,7 @@ extern "C" int ktk_exchange_rows(const void* x_multicast, const void* x_peer_ptr
     // flag values of one launch: start, one per owned row, (scatter) end
     const uint32_t stride = (uint32_t)((rows / world + grid - 1) / grid + 2);
 #define KTK_X_LAUNCH(NV, PEERS, SC, NO)                                                                        \
-    exchange_rows_kernel<NV, PEERS, SC, NO><<<grid, kXThreads, 0, (cudaStream_t)stream>>>(                     \
+    exchange_rows_kernel<NV, PEERS, SC, NO><<<grid, kXAllThreads, 0, (cudaStream_t)stream>>>(                     \
         (const __nv_bfloat16*)x_multicast, (const __nv_bfloat16* const*)x_peer_ptrs,                           \
         (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w, (__nv_bfloat16*)sum_multicast,                \
         (__nv_bfloat16* const*)sum_peer_ptrs, (__nv_bfloat16*)out_local, (__nv_bfloat16*)norm_local,           \
