@@ -403,6 +403,31 @@ KTK_API int ktk_append_tokens(const void* k, const void* v, const int32_t* appen
                               const int32_t* kv_indices, const int32_t* kv_indptr,
                               const int32_t* kv_last_page_len, const ktk_view* view, const ktk_shape* shape,
                               int32_t* status, void* stream);
+/*
+ * Chunked causal prefill attention over the paged cache: the new tokens of every sequence (already in their
+ * pages, see ktk_append_tokens) attend their sequence's history up to their own position.
+ * Replaces flashinfer.single_prefill_with_kv_cache(q, k_cache[:total], v_cache[:total], causal=True)
+ * (LiteSys/litesys/attention/batch_cache.py:129-145), which the reference calls for one sequence at a time on a
+ * contiguous cache; here the pages are read through the table where they lie and one launch serves the batch.
+ *   q, o             [total_new_tokens, Hq, D] packed by sequence; q_indptr int32[B+1] gives each sequence's
+ *                    range (the append_indptr of ktk_append_tokens); shape->batch = B
+ *   max_new_tokens   an upper bound of the new tokens of any one sequence (sizes the grid; host value)
+ *   page table       the state AFTER the append: sequence b holds n tokens in all, its new tokens are the
+ *                    last q_indptr[b+1] - q_indptr[b] of them.  `view` as for the other entry points (sink page,
+ *                    page_count); local_tokens plays no part, every visible token is attended.
+ *   variant          KTK_VARIANT_AUTO: tensor cores for bf16 with a group size of 1, 2, 4 or 8 (one CTA per
+ *                    sequence, kv head and tile of 32 / G tokens; each page staged once per tile by TMA);
+ *                    otherwise, and for KTK_VARIANT_SIMT, every new token runs as one row of the dense paged
+ *                    decode with its own horizon, which needs `workspace` of ktk_prefill_workspace_bytes()
+ *                    bytes (three ints per new token).
+ */
+KTK_API size_t ktk_prefill_workspace_bytes(int64_t total_new_tokens, int32_t dtype, int32_t variant);
+KTK_API int ktk_prefill_attention(const void* q, const int32_t* q_indptr, int64_t total_new_tokens,
+                                  int32_t max_new_tokens, const void* kv_cache, const int32_t* kv_indices,
+                                  const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                                  const ktk_view* view, float sm_scale, void* o, void* workspace,
+                                  size_t workspace_bytes, int32_t variant, const ktk_shape* shape,
+                                  int32_t* status, void* stream);
 KTK_API int ktk_build_summaries_v(const void* kv_cache, void* summaries, int64_t summary_stride,
                                   const int32_t* kv_indices, const int32_t* kv_indptr,
                                   const int32_t* kv_last_page_len, const ktk_view* view,

@@ -64,6 +64,10 @@ _SIGNATURES = {
                                POINTER(Shape), _i32p, c_void_p]),
     "ktk_append_tokens": (c_int32, [c_void_p, c_void_p, _i32p, c_int64, c_void_p, c_void_p, c_int64, _i32p, _i32p,
                                     _i32p, POINTER(View), POINTER(Shape), _i32p, c_void_p]),
+    "ktk_prefill_workspace_bytes": (c_size_t, [c_int64, c_int32, c_int32]),
+    "ktk_prefill_attention": (c_int32, [c_void_p, _i32p, c_int64, c_int32, c_void_p, _i32p, _i32p, _i32p,
+                                        POINTER(View), c_float, c_void_p, c_void_p, c_size_t, c_int32,
+                                        POINTER(Shape), _i32p, c_void_p]),
     "ktk_build_summaries_v": (c_int32, [c_void_p, c_void_p, c_int64, _i32p, _i32p, _i32p, POINTER(View),
                                         POINTER(Shape), _i32p, c_void_p]),
     "ktk_select_v": (c_int32, [c_void_p, c_void_p, c_int64, _i32p, _i32p, _i32p, c_int32, POINTER(View), c_int32,

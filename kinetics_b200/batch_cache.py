@@ -32,7 +32,6 @@ import math
 from typing import Optional
 
 import torch
-import torch.nn.functional as F
 
 from . import ops
 
@@ -171,34 +170,25 @@ class BatchKVManager:
 
     def prefill_or_append(self, query_states, key_states, value_states, layer_idx, batch_idx):
         """batch_cache.py:112-145: one sequence, seq_len tokens appended behind what the slot holds, causal
-        attention over the whole slot.  The attention itself is a library call here as it is in the
-        reference (flashinfer.single_prefill_with_kv_cache there, torch SDPA here)."""
+        attention over the whole slot -- two launches: the chunk goes into its pages (summaries of the touched
+        pages refreshed), then the prefill kernel reads the slot's pages through the table."""
         bsz, seq_len = query_states.shape[0], query_states.shape[2]
         assert bsz == 1, "prefill handles one sequence at a time, like the reference"
         slot = int(batch_idx.item())
         offset = int(self.kv_offset[layer_idx][slot].item())
-        pos = torch.arange(offset, offset + seq_len, device=self.device)
         pages = self.kv_pages[layer_idx]
         self.kv_offset[layer_idx][slot] += seq_len
         total = offset + seq_len
         bi = torch.tensor([slot], device=self.device, dtype=torch.int64)
         start, last, view = self._table(bi, torch.tensor([total], device=self.device, dtype=torch.int32))
         append_indptr = torch.tensor([0, seq_len], device=self.device, dtype=torch.int32)
-        # write the chunk into its pages and refresh the summaries of the pages it touched
         ops.append_tokens(key_states[0].transpose(0, 1).to(self.dtype).contiguous(),
                           value_states[0].transpose(0, 1).to(self.dtype).contiguous(), append_indptr, pages,
                           self.summaries[layer_idx], self.kv_indices, start, last, status=self.status, view=view)
-        # gather the slot's history as [Hkv, total, D]
-        allpos = torch.arange(total, device=self.device)
-        apage = torch.where(allpos < SINK, torch.zeros_like(allpos), 1 + (allpos - SINK) // PAGE) \
-            + slot * self.pages_per_slot
-        aslot = torch.where(allpos < SINK, allpos, (allpos - SINK) % PAGE)
-        k_all = pages[apage, 0, aslot].transpose(0, 1).unsqueeze(0)       # [1, Hkv, total, D]
-        v_all = pages[apage, 1, aslot].transpose(0, 1).unsqueeze(0)
-        qpos = pos[:, None]
-        mask = allpos[None, :] <= qpos                                     # causal over absolute positions
-        out = F.scaled_dot_product_attention(query_states, k_all, v_all, attn_mask=mask, enable_gqa=True)
-        return out.transpose(1, 2).reshape(bsz, seq_len, self.hidden_size)
+        q = query_states[0].transpose(0, 1).to(self.dtype).contiguous()          # [seq_len, Hq, D]
+        out = ops.prefill_attention(q, append_indptr, seq_len, pages, self.kv_indices, start, last, self.sm_scale,
+                                    status=self.status, view=view)
+        return out.reshape(bsz, seq_len, self.hidden_size)
 
     def clear_cache(self, batch_idx: int):
         """batch_cache.py:147-152.  Pages behind a slot's length are never read, so only the lengths

@@ -55,8 +55,12 @@ __device__ __forceinline__ void load_q_frags(uint32_t (&qb)[8][2], const void* q
 // (K tile, then V tile, each as two swizzled half tiles), `ntok` the tokens the page holds.
 //     S^T[16 tok x 8 heads]  = K[16 x 128] . Q^T          8 x mma.m16n8k16
 //     O^T[128 x 8 heads]    += V^T[128 x 16] . P^T        8 x mma.m16n8k16
-__device__ __forceinline__ void mma_consume_page(MmaState& st, uint8_t* stage, int ntok,
-                                                 const uint32_t (&qb)[8][2], float scale_log2, int lane) {
+// CAUSAL (prefill): the 8 columns are (query token, head) pairs with their own horizon -- column 2*tig sees
+// the first lim0 tokens of the page, column 2*tig+1 the first lim1 (both <= ntok, possibly 0).
+template <bool CAUSAL>
+__device__ __forceinline__ void mma_consume_page_t(MmaState& st, uint8_t* stage, int ntok,
+                                                   const uint32_t (&qb)[8][2], float scale_log2, int lane,
+                                                   int lim0, int lim1) {
     const int gid = lane >> 2;
     // per-lane ldmatrix row addresses (relative to the tile): lane supplies row (lane & 7) of matrix lane >> 3
     const int mj = lane >> 3, mr = lane & 7;
@@ -86,19 +90,29 @@ __device__ __forceinline__ void mma_consume_page(MmaState& st, uint8_t* stage, i
     // scores of tokens gid and gid+8 for heads 2*tig, 2*tig+1 (log2 domain)
     float s00 = (s_a[0] + s_b[0]) * scale_log2, s01 = (s_a[1] + s_b[1]) * scale_log2;
     float s10 = (s_a[2] + s_b[2]) * scale_log2, s11 = (s_a[3] + s_b[3]) * scale_log2;
-    if (gid >= ntok) { s00 = -INFINITY; s01 = -INFINITY; }
-    if (gid + 8 >= ntok) { s10 = -INFINITY; s11 = -INFINITY; }
+    if constexpr (CAUSAL) {
+        if (gid >= lim0) s00 = -INFINITY;
+        if (gid >= lim1) s01 = -INFINITY;
+        if (gid + 8 >= lim0) s10 = -INFINITY;
+        if (gid + 8 >= lim1) s11 = -INFINITY;
+    } else {
+        if (gid >= ntok) { s00 = -INFINITY; s01 = -INFINITY; }
+        if (gid + 8 >= ntok) { s10 = -INFINITY; s11 = -INFINITY; }
+    }
     float mx0 = fmaxf(s00, s10), mx1 = fmaxf(s01, s11);
 #pragma unroll
     for (int off = 4; off <= 16; off <<= 1) {
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
     }
-    const float mn0 = fmaxf(st.m0, mx0), mn1 = fmaxf(st.m1, mx1);   // finite: token 0 is valid
-    const float al0 = exp2f(st.m0 - mn0), al1 = exp2f(st.m1 - mn1);
+    const float mn0 = fmaxf(st.m0, mx0), mn1 = fmaxf(st.m1, mx1);   // decode: finite, token 0 is valid
+    // a column that has seen nothing yet and sees nothing here keeps m = -inf: subtract 0 instead of it
+    const float b0 = (CAUSAL && mn0 == -INFINITY) ? 0.0f : mn0;
+    const float b1 = (CAUSAL && mn1 == -INFINITY) ? 0.0f : mn1;
+    const float al0 = exp2f(st.m0 - b0), al1 = exp2f(st.m1 - b1);
     // probabilities, rounded to bf16 once so that the normaliser matches what multiplies V
-    const uint32_t p_lo = pack_bf16(exp2f(s00 - mn0), exp2f(s01 - mn1));   // tokens 0-7
-    const uint32_t p_hi = pack_bf16(exp2f(s10 - mn0), exp2f(s11 - mn1));   // tokens 8-15
+    const uint32_t p_lo = pack_bf16(exp2f(s00 - b0), exp2f(s01 - b1));   // tokens 0-7
+    const uint32_t p_hi = pack_bf16(exp2f(s10 - b0), exp2f(s11 - b1));   // tokens 8-15
     float sum0 = __uint_as_float(p_lo << 16) + __uint_as_float(p_hi << 16);
     float sum1 = __uint_as_float(p_lo & 0xffff0000u) + __uint_as_float(p_hi & 0xffff0000u);
 #pragma unroll
@@ -120,6 +134,11 @@ __device__ __forceinline__ void mma_consume_page(MmaState& st, uint8_t* stage, i
         mma_bf16(st.acc[mt], va, pb0, pb1);
     }
     if (ntok < kPageSize) fence_proxy_async();   // the cleared rows were written by ordinary stores
+}
+
+__device__ __forceinline__ void mma_consume_page(MmaState& st, uint8_t* stage, int ntok,
+                                                 const uint32_t (&qb)[8][2], float scale_log2, int lane) {
+    mma_consume_page_t<false>(st, stage, ntok, qb, scale_log2, lane, ntok, ntok);
 }
 
 // The four TMA tile loads of one page (K and V, each as two 16-row x 128-byte boxes) into a stage.

@@ -18,7 +18,6 @@ import ctypes
 from typing import Callable, List, Optional, Sequence
 
 import torch
-import torch.nn.functional as F
 
 from . import _lib, ops
 from ._lib import check
@@ -213,16 +212,10 @@ class PooledKVManager(BatchKVManager):
                           self.summaries[layer_idx], indices, indptr, last, status=self.status, view=view)
         self._host_len[layer_idx][slot] = total
         self.kv_offset[layer_idx][slot] += seq_len
-        allpos = torch.arange(total, device=self.device)
-        logical = torch.where(allpos < SINK, torch.zeros_like(allpos), 1 + (allpos - SINK) // PAGE)
-        apage = indices.long()[logical]
-        aslot = torch.where(allpos < SINK, allpos, (allpos - SINK) % PAGE)
-        k_all = pages[apage, 0, aslot].transpose(0, 1).unsqueeze(0)       # [1, Hkv, total, D]
-        v_all = pages[apage, 1, aslot].transpose(0, 1).unsqueeze(0)
-        pos = torch.arange(offset, total, device=self.device)
-        mask = allpos[None, :] <= pos[:, None]                            # causal over absolute positions
-        out = F.scaled_dot_product_attention(query_states, k_all, v_all, attn_mask=mask, enable_gqa=True)
-        return out.transpose(1, 2).reshape(bsz, seq_len, self.hidden_size)
+        q = query_states[0].transpose(0, 1).to(self.dtype).contiguous()          # [seq_len, Hq, D]
+        out = ops.prefill_attention(q, append_indptr, seq_len, pages, indices, indptr, last, self.sm_scale,
+                                    status=self.status, view=view)
+        return out.reshape(bsz, seq_len, self.hidden_size)
 
 
 # --------------------------------------------------------------------------------------

@@ -321,6 +321,37 @@ def dense_decode(q, kv_cache, kv_indices, kv_indptr, kv_last_page_len, max_pages
     return out
 
 
+def prefill_attention(q, q_indptr, max_new_tokens: int, kv_cache, kv_indices, kv_indptr, kv_last_page_len,
+                      sm_scale: Optional[float] = None, variant: int = 0, out=None, status=None, view=None):
+    """Causal attention of the new tokens of every sequence over the paged cache (the tokens are already in
+    their pages: call append_tokens first).
+
+    q [total_new, Hq, D] packed by sequence, q_indptr int32 [B+1]; the page table describes the state after
+    the append.  Replaces flashinfer.single_prefill_with_kv_cache (litesys/attention/batch_cache.py:129-145).
+    """
+    _cuda(q, q_indptr, kv_cache, kv_indices, kv_indptr, kv_last_page_len, out, status)
+    total, Hq, _ = q.shape
+    B = q_indptr.numel() - 1
+    shp = _shape(B, kv_cache, Hq)
+    if q.dtype != kv_cache.dtype or q_indptr.dtype != torch.int32:
+        raise TypeError("q and kv_cache must share a dtype; q_indptr must be int32")
+    if out is None:
+        out = torch.empty_like(q)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(q.shape[-1])
+    need = int(_lib.load().ktk_prefill_workspace_bytes(total, shp.dtype, variant))
+    if shp.dtype == _lib.KTK_BF16 and variant != VARIANT_SIMT and shp.group_size not in (1, 2, 4, 8):
+        need = int(_lib.load().ktk_prefill_workspace_bytes(total, shp.dtype, VARIANT_SIMT))
+    ws = _shared_workspace(q.device, need) if need else None
+    vp, _keep = _view_ref(view)
+    check(_lib.load().ktk_prefill_attention(_ptr(q), _ptr(q_indptr), total, int(max_new_tokens), _ptr(kv_cache),
+                                            _ptr(kv_indices), _ptr(kv_indptr), _ptr(kv_last_page_len), vp, sm_scale,
+                                            _ptr(out), _ptr(ws), need, variant, ctypes.byref(shp), _ptr(status),
+                                            _stream()))
+    _launched(2 if need else 1)
+    return out
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """RMSNorm over the last dimension (flashinfer.rmsnorm, benchmark/model_utils.py:12,23)."""
     _cuda(x, weight)
