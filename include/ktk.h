@@ -485,6 +485,31 @@ KTK_API int ktk_sv(const void* value_cache, const int64_t* batch_idx, const int3
                    int64_t max_len, int32_t head_dim, int32_t dtype, int32_t* status, void* stream);
 
 /*
+ * Token-level top-k sparsity and the paged forms of the steps around it (the LiteSys decode chain with
+ * attn_topk instead of attn_block_topk, LiteSys/litesys/attention/batch_cache.py:154-168).
+ *   ktk_token_topk_mask  topk_sparsity (sparsity_utils.py:6-21): rows longer than sink + topk + local keep the
+ *                        sink, the `local` newest tokens and the topk tokens of the region between them with the
+ *                        largest logit averaged over the query group (ties to the lower position); the rest of
+ *                        that region becomes -inf for every head of the group.  logits fp32 [rows, Hq, max_len],
+ *                        offset[row] = tokens of the row.  max_len - sink - local <= 49152.
+ *   ktk_paged_qk         qk (cache_utils.py:173-190) over a paged cache: logits[row, hq, s] = sm_scale * q . K[s]
+ *                        for s < tokens(row), the keys read through the page table (and `view`: sink page,
+ *                        page_count).  Positions behind the row's length are left as they are.
+ *   ktk_paged_sv         sv (cache_utils.py:193-212) over a paged cache: out[row, hq, :] = sum_s p[row, hq, s] * V[s];
+ *                        value rows whose probability is zero for the whole query group are not read.
+ * Between them ktk_softmax_rows applies unchanged.
+ */
+KTK_API int ktk_token_topk_mask(float* logits, const int32_t* offset, int32_t rows, int32_t num_q_heads,
+                                int32_t num_kv_heads, int64_t max_len, int32_t topk, int32_t local, int32_t sink,
+                                int32_t* status, void* stream);
+KTK_API int ktk_paged_qk(const void* q, const void* kv_cache, const int32_t* kv_indices, const int32_t* kv_indptr,
+                         const int32_t* kv_last_page_len, const ktk_view* view, float sm_scale, float* logits,
+                         int64_t max_len, const ktk_shape* shape, int32_t* status, void* stream);
+KTK_API int ktk_paged_sv(const void* kv_cache, const int32_t* kv_indices, const int32_t* kv_indptr,
+                         const int32_t* kv_last_page_len, const ktk_view* view, const float* probs, int64_t max_len,
+                         void* out, const ktk_shape* shape, int32_t* status, void* stream);
+
+/*
  * Host-side page pool for continuous batching.  No CUDA call, no device memory: the pool decides
  * which physical pages of the KV cache a sequence slot owns and writes the CSR arrays the kernels
  * read.  The reference has no counterpart: its benchmark uses one static interleaved table

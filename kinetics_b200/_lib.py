@@ -100,6 +100,12 @@ _SIGNATURES = {
     "ktk_softmax_rows": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int64, c_void_p]),
     "ktk_sv": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int64,
                          c_int64, c_int32, c_int32, _i32p, c_void_p]),
+    "ktk_token_topk_mask": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int64, c_int32, c_int32,
+                                      c_int32, _i32p, c_void_p]),
+    "ktk_paged_qk": (c_int32, [c_void_p, c_void_p, _i32p, _i32p, _i32p, POINTER(View), c_float, c_void_p, c_int64,
+                               POINTER(Shape), _i32p, c_void_p]),
+    "ktk_paged_sv": (c_int32, [c_void_p, _i32p, _i32p, _i32p, POINTER(View), c_void_p, c_int64, c_void_p,
+                               POINTER(Shape), _i32p, c_void_p]),
     "ktk_qkv_norm_rope": (c_int32, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int64,
                                     c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int32, c_void_p]),
     "ktk_pool_create": (c_void_p, [c_int64, c_int32, c_int32]),

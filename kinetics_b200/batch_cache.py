@@ -23,8 +23,10 @@ Lengths are kept per SLOT and looked up through ``batch_idx``; the reference's k
 offset of the active-batch ROW instead (``cache_utils.py:67,106,149``), which is only right while
 the active slots are ``0..n-1``.
 
-Only the block top-k mask and the dense path are built.  The token-level, strided, random and
-local-only masks of ``sparsity_utils.py`` raise ``NotImplementedError`` here.
+Built: the block top-k mask (``attn_block_topk``), the token top-k mask (``attn_topk``,
+``sparsity_utils.py:6-21``: every key is read for the logits, only the kept tokens' values after the
+mask) and the dense path.  The strided, random and local-only masks of ``sparsity_utils.py`` raise
+``NotImplementedError`` here.
 """
 from __future__ import annotations
 
@@ -79,10 +81,11 @@ class BatchKVManager:
 
         sk = self.sparse_kwargs
         self.block_topk: Optional[int] = sk.get("attn_block_topk", None)
+        self.token_topk: Optional[int] = sk.get("attn_topk", None)
         self.local = int(sk.get("attn_local") or 0)
-        if sk["use_sparsity"] and self.block_topk is None:
-            raise NotImplementedError("only attn_block_topk (+ attn_local) and dense attention are built; "
-                                      "token-level, random and local-only masks are not")
+        if sk["use_sparsity"] and self.block_topk is None and self.token_topk is None:
+            raise NotImplementedError("only attn_block_topk, attn_topk (+ attn_local) and dense attention are built; "
+                                      "random and local-only masks are not")
         if self.block_topk is not None:
             if sk.get("attn_block_size", PAGE) != PAGE or sk.get("attn_stride", None) is not None:
                 raise NotImplementedError(f"attn_block_size must be {PAGE} and attn_stride unset")
@@ -98,6 +101,7 @@ class BatchKVManager:
         self.row_width = ops.PageView(SINK, self.local).row_width(self.block_topk) if self.block_topk else 0
         self._sel = None
         self._workspace = None
+        self._logits = None          # fp32 [max_batch, Hq, max_len], token-level top-k only (the reference's attn_score)
         self.sm_scale = 1.0 / math.sqrt(self.head_dim)
 
     # ------------------------------------------------------------------ page bookkeeping
@@ -154,6 +158,8 @@ class BatchKVManager:
         q = query.reshape(B, self.num_attention_heads, self.head_dim).contiguous()
         pages = self.kv_pages[layer_idx]
         sparse = self.block_topk is not None and layer_idx not in self.layer_skip
+        if self.token_topk is not None and layer_idx not in self.layer_skip:
+            return self._decode_token_topk(q, pages, start, last, view, batch_idx, layer_idx)
         if sparse:
             if self._sel is None or self._sel.shape[0] < B:
                 self._sel = torch.empty(self.max_batch_size, self.num_key_value_heads, self.row_width,
@@ -167,6 +173,23 @@ class BatchKVManager:
         splits = self._ws(B, self.pages_per_slot)
         return ops.dense_decode(q, pages, self.kv_indices, start, last, self.pages_per_slot, self.sm_scale,
                                 self._workspace, splits, status=self.status, view=view)
+
+    def _decode_token_topk(self, q, pages, start, last, view, batch_idx, layer_idx):
+        """attn_topk (sparsity_utils.py:6-21): the reference's own chain qk -> mask -> softmax -> sv
+        (batch_cache.py:154-168) on the paged cache.  Every key is read (the mask needs every logit), of the
+        values only those of the kept tokens."""
+        B = q.shape[0]
+        if self._logits is None:
+            width = (self.max_length + 127) // 128 * 128
+            self._logits = torch.empty(self.max_batch_size, self.num_attention_heads, width, dtype=torch.float32,
+                                       device=self.device)
+        logits = self._logits[:B]
+        lengths = self.kv_offset[layer_idx][batch_idx].to(torch.int32).contiguous()
+        ops.paged_qk(q, pages, self.kv_indices, start, last, logits, self.sm_scale, status=self.status, view=view)
+        ops.token_topk_mask(logits, lengths, self.num_attention_heads, self.num_key_value_heads, self.token_topk,
+                            self.local, SINK, status=self.status)
+        ops.softmax_rows(logits, lengths)
+        return ops.paged_sv(logits, B, pages, self.kv_indices, start, last, status=self.status, view=view)
 
     def prefill_or_append(self, query_states, key_states, value_states, layer_idx, batch_idx):
         """batch_cache.py:112-145: one sequence, seq_len tokens appended behind what the slot holds, causal

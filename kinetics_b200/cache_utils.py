@@ -1,5 +1,5 @@
 """The functions of ``LiteSys/litesys/attention/cache_utils.py`` and the block top-k branch of
-``sparsity_utils.attn_logits_processor``, with the reference's names, arguments and in-place
+``sparsity_utils.attn_logits_processor`` (plus its token top-k branch), with the reference's names, arguments and in-place
 behaviour, on CUDA kernels of ``libktk.so`` (``csrc/ktk_dense_chain.cu``).
 
 They keep the reference's own data layout -- unpaged ``[max_batch, Hkv, max_len, D]`` caches and an
@@ -122,12 +122,28 @@ def blockwise_topk_sparsity(logits_triton, offset, num_query_heads, num_key_valu
     return logits_triton
 
 
+def topk_sparsity(logits_triton, offset, num_query_heads, num_key_value_heads, topk, local, sink=4):
+    """sparsity_utils.py:6-21, for every row of the buffer, without the per-row host loop: rows longer than
+    sink + topk + local keep the sink, the `local` newest tokens and the topk tokens in between with the
+    largest group-mean logit."""
+    _cuda(logits_triton, offset)
+    rows = min(logits_triton.shape[0], offset.numel())
+    check(_lib.load().ktk_token_topk_mask(_p(logits_triton), _p(_i32(offset)), rows, num_query_heads,
+                                          num_key_value_heads, logits_triton.shape[2], topk, local, sink,
+                                          _p(_status(logits_triton.device)), _stream()))
+    return logits_triton
+
+
 def attn_logits_processor(logits_triton, offset, num_query_heads, num_key_value_heads, layer_idx, **kwargs):
-    """sparsity_utils.py:217-249.  The block top-k mask and "no sparsity" are built; the other masks raise."""
+    """sparsity_utils.py:217-249.  The block top-k mask, the token top-k mask and "no sparsity" are built; the
+    other masks raise."""
     if (not kwargs["use_sparsity"]) or (layer_idx in kwargs["attn_layer_skip"]):
         return logits_triton
+    if kwargs.get("attn_topk") is not None:
+        return topk_sparsity(logits_triton, offset, num_query_heads, num_key_value_heads, kwargs["attn_topk"],
+                             kwargs["attn_local"])
     if kwargs.get("attn_block_topk") is None or kwargs.get("attn_stride") is not None:
-        raise NotImplementedError("only attn_block_topk (+ attn_local) is built; token-level, strided, random and "
+        raise NotImplementedError("only attn_block_topk and attn_topk (+ attn_local) are built; strided, random and "
                                   "local-only masks are not")
     return blockwise_topk_sparsity(logits_triton, offset, num_query_heads, num_key_value_heads,
                                    kwargs["attn_block_topk"], kwargs["attn_local"],

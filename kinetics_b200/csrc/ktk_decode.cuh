@@ -97,6 +97,44 @@ __device__ __forceinline__ int entry_tokens(const EntryList& el, int e) {
     return kPageSize;
 }
 
+// What the page table says about sequence b: its page list, and how many tokens it holds in all.
+struct SeqPages {
+    int start, n_pages, last_fill, first_fill, total;
+    bool bad;
+};
+__device__ __forceinline__ SeqPages seq_pages(const int32_t* kv_indptr, const int32_t* page_count,
+                                              const int32_t* kv_last_page_len, int sink, int b) {
+    SeqPages s;
+    s.start = kv_indptr[b];
+    s.n_pages = page_count ? page_count[b] : kv_indptr[b + 1] - kv_indptr[b];
+    s.last_fill = s.n_pages > 0 ? kv_last_page_len[b] : 0;
+    s.first_fill = sink > 0 ? sink : kPageSize;
+    s.bad = s.n_pages < 0 || (s.n_pages > 0 && (s.last_fill < 1 || s.last_fill > kPageSize)) ||
+            (sink > 0 && s.n_pages == 1 && s.last_fill > sink);
+    if (s.n_pages <= 0) s.total = 0;
+    else if (s.n_pages == 1) s.total = s.last_fill;
+    else s.total = s.first_fill + (s.n_pages - 2) * kPageSize + s.last_fill;
+    return s;
+}
+// position of the first token of logical page e
+__device__ __forceinline__ int page_first_pos(int e, int first_fill) {
+    return e == 0 ? 0 : first_fill + (e - 1) * kPageSize;
+}
+// pages that hold the first `visible` tokens (visible >= 1), and the tokens of the last of them
+__device__ __forceinline__ void pages_for(int visible, int first_fill, int& count, int& last) {
+    if (visible <= first_fill) { count = 1; last = visible; return; }
+    const int behind = visible - first_fill;
+    count = 1 + (behind + kPageSize - 1) / kPageSize;
+    last = behind - (count - 2) * kPageSize;
+}
+
+// logical page and slot of token position `pos`
+__device__ __forceinline__ void page_of_pos(int pos, int first_fill, int& e, int& slot) {
+    if (pos < first_fill) { e = 0; slot = pos; return; }
+    e = 1 + (pos - first_fill) / kPageSize;
+    slot = (pos - first_fill) % kPageSize;
+}
+
 int launch_decode_simt(const DecodeParams& p, int dtype, int G, cudaStream_t st);
 int launch_decode_mma(const DecodeParams& p, int G, cudaStream_t st);
 int launch_combine(const DecodeParams& p, int dtype, int G, cudaStream_t st);

@@ -41,37 +41,6 @@ struct PrefillParams {
     int32_t* status;
 };
 
-// What the page table says about sequence b: its page list, and how many tokens it holds in all.
-struct SeqPages {
-    int start, n_pages, last_fill, first_fill, total;
-    bool bad;
-};
-__device__ __forceinline__ SeqPages seq_pages(const int32_t* kv_indptr, const int32_t* page_count,
-                                              const int32_t* kv_last_page_len, int sink, int b) {
-    SeqPages s;
-    s.start = kv_indptr[b];
-    s.n_pages = page_count ? page_count[b] : kv_indptr[b + 1] - kv_indptr[b];
-    s.last_fill = s.n_pages > 0 ? kv_last_page_len[b] : 0;
-    s.first_fill = sink > 0 ? sink : kPageSize;
-    s.bad = s.n_pages < 0 || (s.n_pages > 0 && (s.last_fill < 1 || s.last_fill > kPageSize)) ||
-            (sink > 0 && s.n_pages == 1 && s.last_fill > sink);
-    if (s.n_pages <= 0) s.total = 0;
-    else if (s.n_pages == 1) s.total = s.last_fill;
-    else s.total = s.first_fill + (s.n_pages - 2) * kPageSize + s.last_fill;
-    return s;
-}
-// position of the first token of logical page e
-__device__ __forceinline__ int page_first_pos(int e, int first_fill) {
-    return e == 0 ? 0 : first_fill + (e - 1) * kPageSize;
-}
-// pages that hold the first `visible` tokens (visible >= 1), and the tokens of the last of them
-__device__ __forceinline__ void pages_for(int visible, int first_fill, int& count, int& last) {
-    if (visible <= first_fill) { count = 1; last = visible; return; }
-    const int behind = visible - first_fill;
-    count = 1 + (behind + kPageSize - 1) / kPageSize;
-    last = behind - (count - 2) * kPageSize;
-}
-
 __global__ void __launch_bounds__(kPfThreads, 3)
 prefill_mma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap kv_map) {
     extern __shared__ uint8_t smem_raw[];

@@ -352,6 +352,59 @@ def prefill_attention(q, q_indptr, max_new_tokens: int, kv_cache, kv_indices, kv
     return out
 
 
+def paged_qk(q, kv_cache, kv_indices, kv_indptr, kv_last_page_len, logits, sm_scale: Optional[float] = None,
+             status=None, view=None):
+    """Scaled logits of q [B, Hq, D] against every key of each sequence, read through the page table, into the
+    fp32 buffer logits [>= B, Hq, max_len] (qk of litesys/attention/cache_utils.py:173-190 on a paged cache)."""
+    _cuda(q, kv_cache, kv_indices, kv_indptr, kv_last_page_len, logits, status)
+    B, Hq, _ = q.shape
+    shp = _shape(B, kv_cache, Hq)
+    if logits.dtype != torch.float32 or logits.shape[0] < B or logits.shape[1] != Hq or q.dtype != kv_cache.dtype:
+        raise ValueError("paged_qk: logits must be fp32 [rows >= B, Hq, max_len]; q in the cache dtype")
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(q.shape[-1])
+    vp, _keep = _view_ref(view)
+    check(_lib.load().ktk_paged_qk(_ptr(q), _ptr(kv_cache), _ptr(kv_indices), _ptr(kv_indptr), _ptr(kv_last_page_len),
+                                   vp, sm_scale, _ptr(logits), logits.shape[2], ctypes.byref(shp), _ptr(status),
+                                   _stream()))
+    _launched()
+    return logits
+
+
+def paged_sv(probs, batch: int, kv_cache, kv_indices, kv_indptr, kv_last_page_len, out=None, status=None, view=None):
+    """sum_s probs[b, hq, s] * V[s] over a paged cache -> [B, Hq, D] in the cache dtype; rows of V whose
+    probability is zero for the whole query group are skipped (sv of cache_utils.py:193-212)."""
+    _cuda(probs, kv_cache, kv_indices, kv_indptr, kv_last_page_len, out, status)
+    Hq = probs.shape[1]
+    shp = _shape(batch, kv_cache, Hq)
+    if out is None:
+        out = torch.empty(batch, Hq, kv_cache.shape[4], dtype=kv_cache.dtype, device=kv_cache.device)
+    vp, _keep = _view_ref(view)
+    check(_lib.load().ktk_paged_sv(_ptr(kv_cache), _ptr(kv_indices), _ptr(kv_indptr), _ptr(kv_last_page_len), vp,
+                                   _ptr(probs), probs.shape[2], _ptr(out), ctypes.byref(shp), _ptr(status), _stream()))
+    _launched()
+    return out
+
+
+def token_topk_mask(logits, lengths, num_q_heads: int, num_kv_heads: int, topk: int, local: int, sink: int,
+                    status=None):
+    """topk_sparsity (litesys/attention/sparsity_utils.py:6-21) in place on logits [rows, Hq, max_len]."""
+    _cuda(logits, lengths, status)
+    check(_lib.load().ktk_token_topk_mask(_ptr(logits), _ptr(lengths), lengths.numel(), num_q_heads, num_kv_heads,
+                                          logits.shape[2], topk, local, sink, _ptr(status), _stream()))
+    _launched()
+    return logits
+
+
+def softmax_rows(logits, lengths):
+    """In-place softmax over the first lengths[row] positions (cache_utils.py:216-226)."""
+    _cuda(logits, lengths)
+    check(_lib.load().ktk_softmax_rows(_ptr(logits), _ptr(lengths), lengths.numel(), logits.shape[1], logits.shape[2],
+                                       _stream()))
+    _launched()
+    return logits
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """RMSNorm over the last dimension (flashinfer.rmsnorm, benchmark/model_utils.py:12,23)."""
     _cuda(x, weight)

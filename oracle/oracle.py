@@ -213,5 +213,38 @@ def reference_torch_decode(q, kv_cache, sel_pages, last_page_len: int, sm_scale:
     return torch.einsum("b g s, b s d -> b g d", p, v.float())
 
 
+def token_topk_decode(q, k, v, lens, topk: int, local: int, sink: int, sm_scale: float):
+    """Token-level top-k attention on contiguous histories -- the restatement of the reference chain
+    qk -> topk_sparsity -> softmax -> sv (LiteSys/litesys/attention/sparsity_utils.py:6-21,
+    cache_utils.py:54-226) in plain torch, fp32 logits as in the reference, float64 softmax and sum.
+
+    q [B, Hq, D]; k, v [B, Hkv, L, D]; lens[b] tokens of sequence b.  Rows longer than sink + topk + local keep
+    the sink, the `local` newest tokens and the topk tokens in between with the largest logit averaged over the
+    query group (a stable descending sort: ties to the lower position).
+    Returns (out [B, Hq, D] fp32, kept [B, Hkv, topk] int32 ascending positions or -1)."""
+    B, Hq, Dh = q.shape
+    Hkv = k.shape[1]
+    G = Hq // Hkv
+    out = torch.zeros(B, Hq, Dh, dtype=torch.float32)
+    kept = torch.full((B, Hkv, topk), -1, dtype=torch.int32)
+    for b in range(B):
+        n = int(lens[b])
+        if n == 0:
+            continue
+        for h in range(Hkv):
+            qg = q[b, h * G:(h + 1) * G].float()
+            logits = (qg @ k[b, h, :n].float().t()) * sm_scale                   # [G, n] fp32
+            mask = torch.ones(n, dtype=torch.bool)
+            if n > sink + topk + local:
+                mean = logits[:, sink:n - local].sum(0) / G
+                order = torch.sort(-(mean + 0.0), stable=True).indices[:topk]
+                mask[sink:n - local] = False
+                mask[sink + order] = True
+                kept[b, h] = (sink + torch.sort(order).values).to(torch.int32)
+            lg = logits.double().masked_fill(~mask[None], float("-inf"))
+            out[b, h * G:(h + 1) * G] = (torch.softmax(lg, dim=-1) @ v[b, h, :n].double()).float()
+    return out, kept
+
+
 def default_scale() -> float:
     return 1.0 / math.sqrt(D)

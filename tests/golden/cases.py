@@ -39,6 +39,14 @@ LITESYS_CASES = {
 }
 
 
+# Token-level top-k (`attn_topk`, sparsity_utils.py:6-21), same layout: name -> (seed, Hkv, G, lens, topk, local, dtype).
+# Lengths at and around sink + topk + local (the first length that selects is one more than that).
+LITESYS_TOKEN_CASES = {
+    "ls_tok_fp32": (3101, 2, 2, [300, 45, 44, 7, 130, 46], 32, 8, "float32"),
+    "ls_tok_bf16": (3201, 1, 4, [700, 1029, 90], 64, 16, "bfloat16"),
+}
+
+
 def _bf16_round(x: np.ndarray) -> np.ndarray:
     """Round fp32 to the nearest bf16-representable fp32 (ties to even)."""
     u = x.astype(np.float32).view(np.uint32).astype(np.uint64)
@@ -48,7 +56,9 @@ def _bf16_round(x: np.ndarray) -> np.ndarray:
 
 def make_case(name: str) -> dict:
     local = None
-    if name in LITESYS_CASES:
+    if name in LITESYS_TOKEN_CASES:
+        seed, hkv, g, lens, topk, local, dtype = LITESYS_TOKEN_CASES[name]
+    elif name in LITESYS_CASES:
         seed, hkv, g, lens, topk, local, dtype = LITESYS_CASES[name]
     else:
         seed, hkv, g, lens, topk, dtype = CASES[name]

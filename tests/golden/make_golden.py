@@ -29,7 +29,7 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE))
-from cases import CASES, LITESYS_CASES, SINK, D, P, make_case  # noqa: E402
+from cases import CASES, LITESYS_CASES, LITESYS_TOKEN_CASES, SINK, D, P, make_case  # noqa: E402
 
 
 def run_reference(ref_root: str, case: dict) -> dict:
@@ -148,6 +148,59 @@ def run_reference_litesys(ref_root: str, case: dict) -> dict:
     return dict(out=out.float().numpy().reshape(B, hq, D), kept=kept, margin=margin)
 
 
+def run_reference_litesys_token(ref_root: str, case: dict) -> dict:
+    """The same chain with the token-level mask: attn_logits_processor(**preprocess_sparse_args(attn_topk,
+    attn_local)) dispatches to topk_sparsity (sparsity_utils.py:6-21, :233-234)."""
+    sys.path.insert(0, os.path.join(ref_root, "LiteSys"))
+    from litesys.attention.cache_utils import qk, softmax, sv
+    from litesys.attention.sparsity_utils import attn_logits_processor, preprocess_sparse_args
+
+    hkv, g, topk, local = case["Hkv"], case["G"], case["topk"], case["local"]
+    hq = hkv * g
+    lens = torch.from_numpy(case["lens"])
+    B, L = len(lens), int(lens.max())
+    max_len = (L + 127) // 128 * 128
+    k_cache = torch.zeros(B, hkv, max_len, D)
+    v_cache = torch.zeros(B, hkv, max_len, D)
+    k_cache[:, :, :L] = torch.from_numpy(case["k"])
+    v_cache[:, :, :L] = torch.from_numpy(case["v"])
+    query = torch.from_numpy(case["q"]).view(B, hq, 1, D)
+    batch_idx = torch.arange(B, dtype=torch.long)
+    offset = lens.to(torch.int32)
+    logits = torch.full((B, hq, max_len), float("-inf"), dtype=torch.float32)
+    out_buf = torch.zeros(B, hq, (max_len + 127) // 128, D, dtype=torch.float32)
+    kwargs = preprocess_sparse_args(attn_topk=topk, attn_local=local)
+
+    qk(query=query, key=k_cache, batch_idx=batch_idx, offset=offset, logits_buffer=logits, BLOCK_SEQ=128)
+    dense_logits = logits.clone()
+    logits = attn_logits_processor(logits, offset, hq, hkv, 1, **kwargs)
+    masked = logits.clone()
+    softmax(logits, batch_idx, offset)
+    out = sv(value=v_cache, batch_idx=batch_idx, offset=offset, logits_buffer=logits, output_buffer=out_buf,
+             BLOCK_SEQ=128)
+
+    kept = np.full((B, hkv, topk), -1, np.int32)           # kept positions of the dynamic region, ascending
+    margin = np.full((B, hkv), np.inf, np.float64)
+    for b in range(B):
+        n = int(lens[b])
+        for h in range(hkv):
+            fin = torch.isfinite(masked[b, h * g, :n])
+            for gg in range(1, g):
+                assert torch.equal(fin, torch.isfinite(masked[b, h * g + gg, :n])), "heads of a group differ"
+            if n > SINK + topk + local:                     # sparsity_utils.py:9,12
+                assert bool(fin[:SINK].all()) and bool(fin[n - local:].all())
+                pos = torch.nonzero(fin[SINK:n - local]).flatten().numpy() + SINK
+                assert len(pos) == topk, (b, h, len(pos))
+                kept[b, h] = pos
+                sc = dense_logits[b, h * g:(h + 1) * g, SINK:n - local].double().mean(0)
+                srt = torch.sort(sc, descending=True).values
+                margin[b, h] = float((srt[topk - 1] - srt[topk]) / (srt[0] - srt[-1]))
+            else:
+                assert bool(fin.all())
+    assert margin.min() > 1e-6, f"near tie in case {case['name']}: margin {margin.min():.3g}; change the seed"
+    return dict(out=out.float().numpy().reshape(B, hq, D), kept=kept, margin=margin)
+
+
 def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: make_golden.py <path to the Kinetics checkout>")
@@ -162,6 +215,13 @@ def main():
     for name in LITESYS_CASES:
         case = make_case(name)
         res = run_reference_litesys(ref_root, case)
+        np.savez_compressed(HERE / f"{name}.npz", out=res["out"], kept=res["kept"], margin=res["margin"],
+                            lens=case["lens"], topk=case["topk"], Hkv=case["Hkv"], G=case["G"], local=case["local"],
+                            sink=SINK, checksum=case["checksum"], dtype=case["dtype"])
+        print(f"{name}: out {res['out'].shape} min margin {res['margin'].min():.3g}")
+    for name in LITESYS_TOKEN_CASES:
+        case = make_case(name)
+        res = run_reference_litesys_token(ref_root, case)
         np.savez_compressed(HERE / f"{name}.npz", out=res["out"], kept=res["kept"], margin=res["margin"],
                             lens=case["lens"], topk=case["topk"], Hkv=case["Hkv"], G=case["G"], local=case["local"],
                             sink=SINK, checksum=case["checksum"], dtype=case["dtype"])

@@ -6,7 +6,7 @@ from pathlib import Path
 import numpy as np
 import torch
 
-from golden.cases import CASES, LITESYS_CASES, SINK, D, P, make_case  # noqa: F401
+from golden.cases import CASES, LITESYS_CASES, LITESYS_TOKEN_CASES, SINK, D, P, make_case  # noqa: F401
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 

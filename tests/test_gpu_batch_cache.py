@@ -97,9 +97,57 @@ def test_prefill_then_decode_matches_the_litesys_semantics(cuda_device, dtype):
     assert int(mgr.kv_offset[0][0]) == 0 and int(mgr.kv_offset[1][0]) == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_token_topk_decode_matches_the_reference_chain(cuda_device, dtype):
+    # attn_topk (sparsity_utils.py:6-21) on the paged manager: prefill, then decode steps over scattered slots,
+    # against the oracle's restatement of qk -> topk_sparsity -> softmax -> sv (pinned by tests/golden/ls_tok_*)
+    from kinetics_b200 import BatchKVManager
+    topk, local = 24, 5
+    mgr = BatchKVManager(Cfg, max_batch_size=5, max_seq_len=384, device=cuda_device, dtype=dtype,
+                         attn_topk=topk, attn_local=local)
+    g = torch.Generator().manual_seed(4)
+    slots, plens = [3, 0, 4], [200, SINK + topk + local - 2, 2]       # the second crosses the threshold while decoding
+    L = 384
+    hist_k = torch.zeros(2, 5, 2, L, 128)
+    hist_v = torch.zeros(2, 5, 2, L, 128)
+    lens = {s: 0 for s in range(5)}
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+
+    def rnd(*shape):
+        return torch.randn(*shape, generator=g).to(dtype).float()
+
+    for slot, n in zip(slots, plens):
+        for layer in range(2):
+            q, k, v = rnd(1, 8, n, 128), rnd(1, 2, n, 128), rnd(1, 2, n, 128)
+            hist_k[layer, slot, :, :n] = k[0]
+            hist_v[layer, slot, :, :n] = v[0]
+            mgr.compute_attention(q.to(dtype).to(cuda_device), k.to(dtype).to(cuda_device),
+                                  v.to(dtype).to(cuda_device), layer, torch.tensor([slot], device=cuda_device))
+        lens[slot] = n
+    batch_idx = torch.tensor(slots, device=cuda_device)
+    for step in range(6):
+        for layer in range(2):
+            q, k, v = rnd(3, 8, 1, 128), rnd(3, 2, 1, 128), rnd(3, 2, 1, 128)
+            for i, s in enumerate(slots):
+                hist_k[layer, s, :, lens[s]] = k[i, :, 0]
+                hist_v[layer, s, :, lens[s]] = v[i, :, 0]
+            out = mgr.compute_attention(q.to(dtype).to(cuda_device), k.to(dtype).to(cuda_device),
+                                        v.to(dtype).to(cuda_device), layer, batch_idx)
+            now = [lens[s] + 1 for s in slots]
+            # layer 0 is in attn_layer_skip by default (dense): a budget that covers everything
+            ref, kept = oracle.token_topk_decode(q[:, :, 0], hist_k[layer, slots], hist_v[layer, slots], now,
+                                                 topk if layer else 10 ** 6, local, SINK, 1 / math.sqrt(128))
+            torch.testing.assert_close(out.float().cpu().view(3, 8, 128), ref, rtol=tol, atol=tol)
+            if layer == 1 and step == 5:
+                assert (kept[0] >= 0).all() and (kept[1] >= 0).all() and (kept[2] < 0).all()
+        for s in slots:
+            lens[s] += 1
+    mgr.check_status()
+
+
 def test_unbuilt_masks_are_refused():
     from kinetics_b200 import BatchKVManager
     with pytest.raises(NotImplementedError):
-        BatchKVManager(Cfg, 2, 128, "cuda", torch.bfloat16, attn_topk=64, attn_local=16)
+        BatchKVManager(Cfg, 2, 128, "cuda", torch.bfloat16, attn_random_select=64, attn_local=16)
     with pytest.raises(NotImplementedError):
         BatchKVManager(Cfg, 2, 128, "cuda", torch.bfloat16, attn_local=16)

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import LITESYS_CASES, load_golden, torch_dtype
+from helpers import LITESYS_CASES, LITESYS_TOKEN_CASES, load_golden, torch_dtype
 from golden.cases import make_case
 
 pytestmark = pytest.mark.gpu
@@ -79,6 +79,63 @@ def test_function_chain_reproduces_the_reference_outputs(cuda_device, name):
         assert torch.isfinite(kept_logits[b, :, :SINK]).all() and torch.isfinite(kept_logits[b, :, SINK + nblk * 16:n]).all()
 
 
+@pytest.mark.parametrize("name", sorted(LITESYS_TOKEN_CASES))
+def test_function_chain_with_token_topk_reproduces_the_reference(cuda_device, name):
+    # attn_topk: attn_logits_processor dispatches to topk_sparsity (sparsity_utils.py:6-21, :233-234)
+    from kinetics_b200 import cache_utils as cu
+    case, gold = make_case(name), load_golden(name)
+    dt = torch_dtype(case["dtype"])
+    lens = [int(n) for n in case["lens"]]
+    B, hkv, g = len(lens), case["Hkv"], case["G"]
+    hq, L = hkv * g, max(lens)
+    max_len = (L + BLOCK_SEQ) // BLOCK_SEQ * BLOCK_SEQ
+    k = torch.from_numpy(case["k"]).to(dt).to(cuda_device)
+    v = torch.from_numpy(case["v"]).to(dt).to(cuda_device)
+    q = torch.from_numpy(case["q"]).to(dt).to(cuda_device).view(B, hq, 1, 128)
+    k_cache = torch.zeros(B, hkv, max_len, 128, dtype=dt, device=cuda_device)
+    v_cache = torch.zeros_like(k_cache)
+    new_k = torch.empty(B, hkv, 1, 128, dtype=dt, device=cuda_device)
+    new_v = torch.empty_like(new_k)
+    for b, n in enumerate(lens):
+        k_cache[b, :, :n - 1] = k[b, :, :n - 1]
+        v_cache[b, :, :n - 1] = v[b, :, :n - 1]
+        new_k[b, :, 0] = k[b, :, n - 1]
+        new_v[b, :, 0] = v[b, :, n - 1]
+    logits = torch.full((B, hq, max_len), float("-inf"), device=cuda_device)
+    topk, local = case["topk"], case["local"]
+    kwargs = cu.preprocess_sparse_args(attn_topk=topk, attn_local=local)
+    batch_idx = torch.arange(B, device=cuda_device)
+    before = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=cuda_device)
+    out, kept_logits = _chain(cu, q, k_cache, v_cache, new_k, new_v, batch_idx, before, logits, kwargs, hq, hkv)
+    cu.check_status(cuda_device)
+    tol = 5e-5 if dt == torch.float32 else 2e-2
+    np.testing.assert_allclose(out.float().cpu().numpy(), gold["out"], rtol=tol, atol=tol)
+    # the positions the mask kept are the reference's, for every head of a group alike
+    for b, n in enumerate(lens):
+        fin = torch.isfinite(kept_logits[b, :, :n]).view(hkv, g, n)
+        assert (fin == fin[:, :1]).all()
+        if n <= SINK + topk + local:
+            assert fin.all()
+            continue
+        assert fin[:, :, :SINK].all() and fin[:, :, n - local:].all()
+        for h in range(hkv):
+            pos = (torch.nonzero(fin[h, 0, SINK:n - local]).view(-1) + SINK).tolist()
+            assert pos == [int(x) for x in gold["kept"][b, h]], (name, b, h)
+
+
+def test_token_topk_mask_ties_go_to_the_lower_position(cuda_device):
+    from kinetics_b200 import cache_utils as cu
+    hq, hkv, n, topk, local = 4, 2, 200, 5, 3
+    logits = torch.zeros(1, hq, 256, device=cuda_device)              # every dynamic token ties
+    logits[0, :, 50] = 1.0                                            # one clear winner
+    off = torch.tensor([n], dtype=torch.int32, device=cuda_device)
+    cu.topk_sparsity(logits, off, hq, hkv, topk, local, sink=SINK)
+    cu.check_status(cuda_device)
+    kept = torch.nonzero(torch.isfinite(logits[0, 0, SINK:n - local])).view(-1).tolist()
+    assert kept == [0, 1, 2, 3, 46]                                   # positions 4..7 and 50
+    assert torch.isfinite(logits[0, :, :SINK]).all() and torch.isfinite(logits[0, :, n - local:n]).all()
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_dense_chain_with_scattered_slots(cuda_device, dtype):
     # no sparsity; rows of the active batch live in arbitrary cache slots
@@ -117,6 +174,7 @@ def test_other_masks_are_refused(cuda_device):
     logits = torch.zeros(1, 4, 128, device=cuda_device)
     off = torch.tensor([100], dtype=torch.int32, device=cuda_device)
     with pytest.raises(NotImplementedError):
-        cu.attn_logits_processor(logits, off, 4, 1, 1, **cu.preprocess_sparse_args(attn_topk=8, attn_local=4))
+        cu.attn_logits_processor(logits, off, 4, 1, 1, **cu.preprocess_sparse_args(attn_random_select=8, attn_local=4,
+                                                                                   attn_topk=None))
     # layer 0 is skipped by default, whatever the mask
     assert cu.attn_logits_processor(logits, off, 4, 1, 0, **cu.preprocess_sparse_args(attn_topk=8, attn_local=4)) is logits

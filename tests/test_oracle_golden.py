@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import CASES, LITESYS_CASES, P, SINK, case_state, load_golden
+from helpers import CASES, LITESYS_CASES, LITESYS_TOKEN_CASES, P, SINK, case_state, load_golden, make_case
 from oracle import oracle
 
 
@@ -154,6 +154,24 @@ def test_oracle_view_reproduces_litesys_chain(name):
     dense = oracle.decode_v(q, st["kv_cache"], st["kv_indices"], -1, st["kv_indptr"], st["kv_last_page_len"],
                             oracle.default_scale(), SINK, local)
     assert torch.isfinite(dense).all()
+
+
+@pytest.mark.parametrize("name", sorted(LITESYS_TOKEN_CASES))
+def test_oracle_token_topk_reproduces_litesys_chain(name):
+    """qk -> attn_logits_processor(attn_topk) -> softmax -> sv of the reference (topk_sparsity,
+    sparsity_utils.py:6-21), run on CPU when the fixtures were made, against the oracle's token-level restatement."""
+    case = make_case(name)
+    gold = load_golden(name)
+    assert str(gold["checksum"]) == case["checksum"]
+    topk, local = int(gold["topk"]), int(gold["local"])
+    q, k, v = (torch.from_numpy(case[x]) for x in ("q", "k", "v"))
+    out, kept = oracle.token_topk_decode(q, k, v, case["lens"], topk, local, SINK, oracle.default_scale())
+    assert np.array_equal(kept.numpy(), gold["kept"])
+    assert np.abs(out.numpy() - gold["out"]).max() < 5e-5
+    if name == "ls_tok_fp32":           # lengths at the threshold stay dense, one more token selects
+        lens = [int(x) for x in case["lens"]]
+        at, over = lens.index(SINK + topk + local), lens.index(SINK + topk + local + 1)
+        assert (gold["kept"][at] < 0).all() and (gold["kept"][over] >= 0).all()
 
 
 def test_view_defaults_equal_plain_oracle():
