@@ -46,6 +46,14 @@ WORKLOADS = {
     # [512, 32768]; a tenth of them sit on a page boundary, so the step opens a new page for those
     "cfg5-tp1": dict(model="Qwen3-1.7B", tp=1, batch=512, ctx=32768, topk=32, ragged=(512, 32768), boundary=0.1),
     "tiny": dict(model="Qwen3-8B", tp=8, batch=64, ctx=2048, topk=16),
+    # configs[4] as stated: the whole Qwen3-1.7B model (28 layers, final norm, vocabulary projection, greedy
+    # sampling) stepping 512 sequences with contexts uniform in [512, 32768], a tenth of them on a page boundary
+    # at the first timed step, block top-k budget 32; tensor parallel over the GPUs of the run (--gpus 1/2/4/8),
+    # driven by Engine + PagePool (the page table is exported on the host every step)
+    "cfg5": dict(model="Qwen3-1.7B", tp=0, batch=512, ctx=32768, topk=32, ragged=(512, 32768), boundary=0.1,
+                 full_model=True),
+    # configs[0]: fp32, one KV head with four query heads, 4 sequences of 2048 tokens, top-k 16
+    "cfg1": dict(model="cfg1", tp=1, batch=4, ctx=2048, topk=16, dtype="float32"),
 }
 PAGE = 16
 HEAD_DIM = 128
@@ -93,6 +101,7 @@ def parse():
                     help="library comparison: also flashinfer's CUDA-core decode (one more kernel to build)")
     ap.add_argument("--library-timeout", type=float, default=420.0,
                     help="seconds the library comparison may take (flashinfer builds its kernels on first use)")
+    ap.add_argument("--layers", type=int, default=0, help="full-model workloads: run this many layers (0: all)")
     ap.add_argument("--micro", default="", choices=["", "select", "exchange"],
                     help="time one kernel alone on the workload's shapes (select: only the page summaries are "
                          "allocated, so the full batch fits in a few GB; exchange: the NVLink exchange kernels "
@@ -222,6 +231,7 @@ def run_reference(args):
     wl = dict(WORKLOADS[args.workload])
     if args.batch:
         wl["batch"] = args.batch
+    args.cpu_sample = min(args.cpu_sample, wl["batch"])
     value, ms, threads, done = cpu_reference_run(wl, args.cpu_sample, args.steps, args.warmup, args.seed,
                                                  budget_s=120.0)
     sample = (f"{args.cpu_sample} of {wl['batch']} sequences of the workload per step, fp32, "
@@ -402,7 +412,7 @@ def run_ours(args):
         wl["batch"] = args.batch
     cfg = kb.get_config(wl["model"])
     tp, B, ctx, topk = wl["tp"], wl["batch"], wl["ctx"], wl["topk"]
-    dtype = torch.bfloat16
+    dtype = getattr(torch, wl.get("dtype", "bfloat16"))
     torch.manual_seed(args.seed * 1000 + rank)
     fused = use_fused_allreduce(args, world)
     scatter = world > 1 and args.down_exchange == "scatter"
@@ -487,7 +497,7 @@ def run_ours(args):
     t_decode = mean_ms(timers["decode"][2:])
     t_append = mean_ms(timers["append"][2:])
     hkv = cfg.num_key_value_heads // tp
-    esz = 2
+    esz = 2 if dtype == torch.bfloat16 else 4
     scored = (ctx_lens // PAGE) if ctx_lens is not None else torch.full((B,), ctx // PAGE)
     bytes_select = int(scored.sum()) * hkv * HEAD_DIM * esz
     bytes_decode = int((torch.clamp(scored, max=topk) + 1).sum()) * hkv * PAGE * HEAD_DIM * 2 * esz
@@ -504,8 +514,9 @@ def run_ours(args):
     ach_attn = (bytes_decode + bytes_select) / ((t_decode + t_select) * 1e-3) / 1e9
     # DRAM traffic of one launch of the decode kernel: not measurable inside this run (it needs the
     # profiler), so the ratio of a profiler capture of the same kernel is applied to this run's bytes.
-    traffic = int(bytes_decode * DECODE_TRAFFIC_RATIO)
-    roofline = {"bound": "hbm", "kernel": "sparse decode (decode_stream_kernel + stream_combine_kernel)",
+    traffic = int(bytes_decode * DECODE_TRAFFIC_RATIO) if dtype == torch.bfloat16 else None
+    roofline = {"bound": "hbm", "kernel": "sparse decode (decode_stream_kernel + stream_combine_kernel)"
+                if dtype == torch.bfloat16 else "sparse decode (decode_simt_kernel, fp32)",
                 "achieved": ach_decode, "peak": peak_gbs, "unit": "GB/s", "frac": ach_decode / peak_gbs,
                 "traffic": traffic, "traffic_source": DECODE_TRAFFIC_SOURCE,
                 "peak_kind": peak_kind, "ms": t_decode, "algorithmic_bytes": bytes_decode}
@@ -567,7 +578,7 @@ def run_ours(args):
 
     # ---- the library kernels the reference itself runs on a GPU, on the same cache (comparison only) ----
     library_bar = None
-    if not args.no_flashinfer and world == 1 and ctx_lens is None:
+    if not args.no_flashinfer and world == 1 and ctx_lens is None and dtype == torch.bfloat16:
         library_bar = bounded_library_bar(args, sparse, static_in, B, hkv, cfg.num_attention_heads // tp, topk, device,
                                           with_dense=not args.no_dense)
         if library_bar and "flashinfer_sparse_decode_ms_tensor_cores" in library_bar:
@@ -583,9 +594,10 @@ def run_ours(args):
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu and ctx_lens is None:
         sys.path.insert(0, ROOT)
-        v, ms, threads, done = cpu_reference_run(wl, args.cpu_sample, 1000, 1, args.seed, budget_s=15.0)
+        sample_b = min(args.cpu_sample, B)
+        v, ms, threads, done = cpu_reference_run(wl, sample_b, 1000, 1, args.seed, budget_s=15.0)
         cpu = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "ms_per_step": ms,
-               "sample": f"{args.cpu_sample} of {B} sequences of the workload per step, {done} steps, fp32, "
+               "sample": f"{sample_b} of {B} sequences of the workload per step, {done} steps, fp32, "
                          f"torch on {threads} host threads (oracle/reference_layer.py)"}
 
     if rank == 0:
@@ -593,7 +605,8 @@ def run_ours(args):
             "metric": "block-top-k decode tokens/s (Qwen3-8B layer, B=4096, 32K ctx)", "value": value,
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "ms_per_step_passes": {"reps": len(passes), "min": min(passes), "median": ms_step, "max": max(passes)},
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16" if dtype == torch.bfloat16 else "f32", "data": "synthetic",
             "config": workload_config(args, wl, world), "roofline": roofline, "kernels": kernels,
             "parity_check": parity, "cpu_baseline": cpu, "e2e": e2e, "dense": dense_info,
             "library_bar": library_bar,
@@ -797,6 +810,171 @@ def run_micro_select(args):
           "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / (ms * 1e-3) / 1e9})
 
 
+def run_full_model(args):
+    """BASELINE.json configs[4]: a full-model decode step.  One process per GPU; the model is tensor parallel
+    over the ranks of the run.  A step = Engine.decode_graphed: host page-table work (PagePool growth, CSR export,
+    asynchronous copies into static device buffers) + one CUDA-graph replay of embedding, 28 layers (block top-k
+    attention through PooledKVManager, LiteSys semantics: sink 4, layer 0 dense), final norm, vocabulary
+    projection, argmax and token bookkeeping."""
+    import torch.distributed as dist
+    import numpy as np
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    pg = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        pg = dist.group.WORLD
+    import kinetics_b200 as kb
+    from kinetics_b200 import ops
+
+    wl = dict(WORKLOADS[args.workload])
+    if args.batch:
+        wl["batch"] = args.batch
+    cfg = kb.get_config(wl["model"])
+    B, topk = wl["batch"], wl["topk"]
+    lo, hi = wl["ragged"]
+    dtype = torch.bfloat16
+    layers = args.layers or cfg.num_hidden_layers
+    gl = torch.Generator().manual_seed(args.seed)
+    lens = torch.randint(lo, hi + 1, (B,), generator=gl)
+    on_boundary = int(round(wl.get("boundary", 0.0) * B))
+    pick = torch.randperm(B, generator=gl)[:on_boundary]
+    # a sequence opens a page when the token it appends is the first behind a page edge (4 sink tokens, then 16s)
+    ahead = 2 + max(args.warmup, 3)                          # decode steps that run before the first timed one
+    lens[pick] = torch.clamp((lens[pick] - 4) // PAGE * PAGE + 4 - ahead, min=lo)
+    steps_total = args.warmup + args.steps * max(1, args.reps) * 2 + 16
+    max_seq = int(lens.max()) + steps_total + PAGE
+    pool_pages = int(((lens + steps_total - 4 + PAGE - 1) // PAGE + 2).sum()) + 64
+    hkv = cfg.num_key_value_heads // world
+    kv_bytes_layer = pool_pages * 2 * PAGE * hkv * HEAD_DIM * 2
+    # every layer needs its own pages; they fit only when the model is spread over enough GPUs
+    alias = kv_bytes_layer * layers > 140e9
+    torch.manual_seed(args.seed)
+
+    class Cfg:                                               # what the KV manager reads from a model config
+        hidden_size, num_attention_heads, num_key_value_heads = cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads
+        head_dim, num_hidden_layers = cfg.head_dim, layers
+
+    kv = kb.PooledKVManager(Cfg, B, max_seq, device, dtype, num_pages=pool_pages, alias_layers=alias,
+                            attn_block_topk=topk, attn_local=0, attn_block_size=PAGE)
+    for pages in ({id(p): p for p in kv.kv_pages}.values()):
+        pages.normal_()                                      # KV pre-filled from N(0, 1)
+    kv.assume_filled({s: int(lens[s]) for s in range(B)}, headroom=steps_total)
+    model = kb.DecoderStack(cfg, device, dtype, process_group=pg, max_positions=max_seq + 8, decode_batch=B,
+                            seed=args.seed, num_layers=layers)
+    eng = kb.Engine(model, kv, max_seq, device, temperature=0.0, repeat_check=False)
+    slots = list(range(B))
+    for s in slots:
+        eng.slots_occupy_status[s] = True
+    eng.slots_offsets.copy_(lens.to(device))
+    eng.slots_prompt_len.copy_(lens.to(device))
+    eng._offsets_host = [int(x) for x in lens]
+    eng._prompt_host = [int(x) for x in lens]
+    eng.slots_tokens.random_(0, cfg.vocab_size)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    launches0 = ops.launch_count()
+    eng.decode_graphed(slots)                                # eager step (warms the kernels up)
+    launches_per_step = ops.launch_count() - launches0
+    eng.decode_graphed(slots)                                # captures, then replays
+    for _ in range(max(args.warmup, 3)):
+        eng.decode_graphed(slots)
+    kv.check_status()
+    model.check_status()
+    sampler = ClockSampler(local)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    passes, host_ms, opened = [], [], []
+    barrier()
+    with sampler:
+        for _ in range(max(1, args.reps)):
+            e0.record()
+            for _ in range(args.steps):
+                t0 = time.perf_counter()
+                eng.kv.prepare_step(slots)                   # (timed apart: the host share of a step)
+                host_ms.append((time.perf_counter() - t0) * 1e3)
+                opened.append(kv.pages_opened)
+                eng._graph.replay()
+                eng.kv.end_step()
+            e1.record()
+            barrier()
+            passes.append(max_over_ranks(e0.elapsed_time(e1) / args.steps))
+    ms_step = median(passes)
+    # end to end: the serving loop needs the sampled tokens on the host every step (end-of-sequence test)
+    host_tokens = torch.empty(B, dtype=torch.long).pin_memory()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        out = eng.decode_graphed(slots)
+        host_tokens.copy_(out, non_blocking=False)
+    e1.record()
+    barrier()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    kv.check_status()
+    model.check_status()
+    # algorithmic attention bytes of a step on this rank (layer 0 dense, the others sparse)
+    now = lens + args.warmup
+    scored = (now - 4) // PAGE
+    esz = 2
+    b_sel = int(scored.sum()) * hkv * HEAD_DIM * esz
+    b_dec = int((torch.clamp(scored, max=topk) + 2).sum()) * hkv * PAGE * HEAD_DIM * 2 * esz
+    b_dense = int((scored + 2).sum()) * hkv * PAGE * HEAD_DIM * 2 * esz
+    attn_bytes = (layers - 1) * (b_sel + b_dec) + b_dense
+    weight_bytes = sum(t.numel() * 2 for L in model.layers for k, t in L.items() if t.dim() == 2) \
+        + model.lm_head.numel() * 2
+    if rank == 0:
+        peaks = {}
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peaks = json.load(f)
+        except Exception:
+            pass
+        peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
+        ach = (attn_bytes + weight_bytes) / (ms_step * 1e-3) / 1e9
+        emit({
+            "metric": "block-top-k decode tokens/s (Qwen3-1.7B full-model step, 512 sequences, contexts in [512, 32768])",
+            "value": B / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step,
+            "ms_per_step_passes": {"reps": len(passes), "min": min(passes), "median": ms_step, "max": max(passes)},
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {wl['model']} full model, {layers} layers + final norm + "
+                                   f"vocabulary projection + greedy sampling, {B} sequences, contexts uniform in "
+                                   f"{[lo, hi]}, top-k {topk} pages, page {PAGE}, tensor parallel over {world} GPU(s)",
+                       "batch": B, "layers": layers, "topk_pages": topk, "parallelism": f"tp{world} by KV head",
+                       "kv_pool_pages": pool_pages, "kv_bytes_per_layer_per_gpu": kv_bytes_layer,
+                       "layers_share_one_physical_pool": alias,
+                       "l2": "per-layer traffic exceeds the 126 MB L2"},
+            "roofline": {"bound": "hbm", "kernel": "whole step (attention pages + summaries + weights)",
+                         "achieved": ach, "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs, "traffic": None,
+                         "algorithmic_bytes": attn_bytes + weight_bytes, "attention_bytes": attn_bytes,
+                         "weight_bytes": weight_bytes},
+            "host": {"prepare_step_ms_median": median(host_ms), "prepare_step_ms_max": max(host_ms),
+                     "table_bytes_per_step": kv.table_bytes, "pages_opened_first_step": opened[0],
+                     "pages_opened_per_step_mean": sum(opened) / len(opened)},
+            "e2e": {"value": B / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": kv.table_bytes, "d2h_bytes_per_step": B * 8,
+                    "how": "Engine.decode_graphed + the sampled tokens copied to the host every step"},
+            "cpu_baseline": None, "gpu_launches": launches_per_step * args.steps * max(1, args.reps),
+            "gpu_launches_per_step": launches_per_step, "clocks": sampler.summary(),
+        })
+    if world > 1:
+        leave_group(dist, [eng, model, kv])
+
+
 def run_micro_exchange(args):
     """The NVLink exchange kernels alone on [batch, hidden] bf16 (under torchrun): every form, schedule and
     result, beside NCCL all-reduce (+ the add / norm kernel) and NCCL reduce-scatter."""
@@ -883,6 +1061,8 @@ def main():
         return run_micro_exchange(args)
     if args.impl == "reference":
         run_reference(args)
+    elif WORKLOADS[args.workload].get("full_model"):
+        run_full_model(args)
     else:
         run_ours(args)
 

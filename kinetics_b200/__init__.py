@@ -14,6 +14,7 @@ from .config import LayerConfig, get_config  # noqa: E402
 from .layers import BlockTopkDecoderLayer, DecoderLayer, init_weights  # noqa: E402
 from .batch_cache import BatchKVManager  # noqa: E402
 from .engine import Engine, PagePool, PooledKVManager, PoolExhausted  # noqa: E402
+from .decoder_stack import DecoderStack  # noqa: E402
 
 __all__ = ["ops", "LayerConfig", "get_config", "BlockTopkDecoderLayer", "DecoderLayer", "init_weights",
-           "BatchKVManager", "Engine", "PagePool", "PooledKVManager", "PoolExhausted"]
+           "BatchKVManager", "DecoderStack", "Engine", "PagePool", "PooledKVManager", "PoolExhausted"]

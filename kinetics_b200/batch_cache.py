@@ -93,8 +93,7 @@ class BatchKVManager:
 
         self.pages_per_slot = 1 + (max(max_seq_len - SINK, 0) + PAGE - 1) // PAGE
         self._alloc_pages()
-        self.summaries = [torch.zeros(max_batch_size, self.num_key_value_heads, self.pages_per_slot, self.head_dim,
-                                      device=self.device, dtype=dtype) for _ in range(self.num_layers)]
+        self.summaries = self._alloc_summaries()
         self.kv_offset = [torch.zeros(max_batch_size, device=self.device, dtype=torch.int32)
                           for _ in range(self.num_layers)]
         self.status = ops.new_status(self.device)
@@ -111,6 +110,11 @@ class BatchKVManager:
         self.kv_pages = [torch.zeros(total, 2, PAGE, self.num_key_value_heads, self.head_dim, device=self.device,
                                      dtype=self.dtype) for _ in range(self.num_layers)]
         self.kv_indices = torch.arange(total, device=self.device, dtype=torch.int32)
+
+    def _alloc_summaries(self):
+        """One mean-key row per (slot, kv head, logical page) and layer."""
+        return [torch.zeros(self.max_batch_size, self.num_key_value_heads, self.pages_per_slot, self.head_dim,
+                            device=self.device, dtype=self.dtype) for _ in range(self.num_layers)]
 
     def _table(self, batch_idx: torch.Tensor, lengths: torch.Tensor):
         """Per active row: start of its page list, page count, tokens in its last page, view."""

@@ -29,6 +29,8 @@ PRESETS = {
     "Qwen3-8B": LayerConfig(4096, 32, 8, 12288, 36),
     "Qwen3-32B": LayerConfig(5120, 64, 8, 25600, 64),
     "Qwen3-1.7B": LayerConfig(2048, 16, 8, 6144, 28),
+    # the attention shape of the CPU-runnable case (one KV head, four query heads) inside a small layer
+    "cfg1": LayerConfig(512, 4, 1, 1024, 1),
 }
 
 

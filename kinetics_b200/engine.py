@@ -17,6 +17,7 @@ import copy
 import ctypes
 from typing import Callable, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from . import _lib, ops
@@ -93,6 +94,18 @@ class PagePool:
         return indices[:total], indptr, last[:n]
 
 
+    def export_into(self, slots: Sequence[int], indices: torch.Tensor, indptr: torch.Tensor, last: torch.Tensor) -> int:
+        """The same into caller-owned int32 CPU tensors (pinned ones, for a copy that overlaps); returns the
+        number of page ids written."""
+        n = len(slots)
+        arr = (ctypes.c_int32 * n)(*slots)
+        total = self._lib.ktk_pool_export(self._h, arr, n, ctypes.c_void_p(indices.data_ptr()), indices.numel(),
+                                          ctypes.c_void_p(indptr.data_ptr()), ctypes.c_void_p(last.data_ptr()))
+        if total < 0:
+            check(int(total))
+        return int(total)
+
+
 # --------------------------------------------------------------------------------------
 # KV manager backed by the pool
 # --------------------------------------------------------------------------------------
@@ -114,21 +127,36 @@ class PooledKVManager(BatchKVManager):
     slots as a host list to spare the manager a device-to-host read of ``batch_idx``.
     """
 
-    def __init__(self, config, max_batch_size: int, max_seq_len: int, device, dtype, num_pages: int, **kwargs):
+    def __init__(self, config, max_batch_size: int, max_seq_len: int, device, dtype, num_pages: int,
+                 alias_layers: bool = False, **kwargs):
+        """`alias_layers`: every layer reads and writes ONE physical pool and one summary table (a benchmark
+        device for models whose caches would not fit: the traffic per layer is real, the contents are not)."""
         self._num_pool_pages = int(num_pages)
+        self._alias = bool(alias_layers)
         super().__init__(config, max_batch_size, max_seq_len, device, dtype, **kwargs)
+
+    def _alloc_summaries(self):
+        if not self._alias:
+            return super()._alloc_summaries()
+        one = torch.zeros(self.max_batch_size, self.num_key_value_heads, self.pages_per_slot, self.head_dim,
+                          device=self.device, dtype=self.dtype)
+        return [one] * self.num_layers
 
     # BatchKVManager allocates pages_per_slot * max_batch pages per layer; here the pool decides
     def _alloc_pages(self):
         total = self._num_pool_pages
         self.pool = PagePool(total, self.max_batch_size, PAGE)
-        self.kv_pages = [torch.zeros(total, 2, PAGE, self.num_key_value_heads, self.head_dim, device=self.device,
-                                     dtype=self.dtype) for _ in range(self.num_layers)]
+        def pages():
+            return torch.zeros(total, 2, PAGE, self.num_key_value_heads, self.head_dim, device=self.device,
+                               dtype=self.dtype)
+        self.kv_pages = [pages()] * self.num_layers if self._alias else [pages() for _ in range(self.num_layers)]
         self.kv_indices = None
-        self._host_len = [[0] * self.max_batch_size for _ in range(self.num_layers)]
+        self._host_len = np.zeros((self.num_layers, self.max_batch_size), dtype=np.int64)
         self._active: Optional[List[int]] = None
         self._table_key = None
         self._table_val = None
+        self._step_table = None          # set by prepare_step: the table every layer of the step uses
+        self._static = None              # static device buffers + pinned mirrors of that table
 
     # ---- admission / retirement
     def can_admit(self, max_total_len: int) -> bool:
@@ -149,6 +177,74 @@ class PooledKVManager(BatchKVManager):
 
     def begin_step(self, slots: Sequence[int]) -> None:
         self._active = list(slots)
+
+    # ---- a decode step whose device work can sit in a CUDA graph
+    def _static_buffers(self):
+        if self._static is None:
+            n, cap, dev = self.max_batch_size, self._num_pool_pages, self.device
+            mk = lambda k: torch.empty(k, dtype=torch.int32)
+            self._static = dict(
+                h_indices=mk(cap).pin_memory(), h_indptr=mk(n + 1).pin_memory(), h_last=mk(n).pin_memory(),
+                h_slot=mk(n).pin_memory(), d_indices=mk(cap).to(dev), d_indptr=mk(n + 1).to(dev),
+                d_last=mk(n).to(dev), d_slot=mk(n).to(dev))
+        return self._static
+
+    def prepare_step(self, slots: Sequence[int]) -> None:
+        """All the host work of one decode step over `slots` (every layer appends one token): the pool grows
+        where a sequence crosses a page boundary, the CSR table goes into pinned memory and from there, with
+        asynchronous copies on the current stream, into device buffers whose addresses never change -- so the
+        device work that follows can be a replayed CUDA graph.  `end_step()` closes the step."""
+        slots = list(slots)
+        n = len(slots)
+        st = self._static_buffers()
+        idx = np.asarray(slots, dtype=np.int64)
+        lengths = self._host_len[0, idx] + 1
+        pool_tokens = lambda ln: np.where(ln > 0, PAGE + np.maximum(ln - SINK, 0), 0)
+        grow = idx[pool_tokens(lengths) > pool_tokens(lengths - 1)]
+        if grow.size:
+            self.pool.extend(grow.tolist(), 1)
+        total = self.pool.export_into(slots, st["h_indices"], st["h_indptr"], st["h_last"])
+        st["h_last"].numpy()[:n] = np.where(lengths <= SINK, lengths, (lengths - SINK - 1) % PAGE + 1)
+        st["h_slot"].numpy()[:n] = idx
+        st["d_indices"][:total].copy_(st["h_indices"][:total], non_blocking=True)
+        st["d_indptr"][:n + 1].copy_(st["h_indptr"][:n + 1], non_blocking=True)
+        st["d_last"][:n].copy_(st["h_last"][:n], non_blocking=True)
+        st["d_slot"][:n].copy_(st["h_slot"][:n], non_blocking=True)
+        view = ops.PageView(SINK, self.local, None, st["d_slot"][:n])
+        self._step_table = (st["d_indices"], st["d_indptr"][:n + 1], st["d_last"][:n], view)
+        self.kv_indices = st["d_indices"]
+        self._host_len[:, idx] += 1
+        self._active = slots
+        self.table_bytes = 4 * (total + 3 * n + 1)
+        # pages the step opened (a promise made at admission may already have reserved them)
+        self.pages_opened = int(np.count_nonzero((lengths - SINK - 1) % PAGE == 0)) if n else 0
+
+    def end_step(self) -> None:
+        self._step_table = None
+        self._table_key = None
+
+    def assume_filled(self, lengths: dict, headroom: int = 0) -> None:
+        """Benchmark set-up: slot -> number of tokens its pages are taken to hold already (the page contents
+        are whatever the pool memory holds).  Admits the slots with a promise of `headroom` more tokens, grows
+        them to that length, sets the lengths of every layer and rebuilds the page summaries from the pages."""
+        slots = sorted(lengths)
+        for s in slots:
+            self.pool.admit(s, _pool_tokens(lengths[s]), _pool_tokens(min(lengths[s] + headroom, self.max_length)))
+        lens_t = torch.zeros(self.max_batch_size, dtype=torch.int32)
+        for s in slots:
+            lens_t[s] = lengths[s]
+        for layer in range(self.num_layers):
+            self.kv_offset[layer].copy_(lens_t)
+            for s in slots:
+                self._host_len[layer][s] = lengths[s]
+        indices, indptr, _ = self.pool.export(slots)
+        last = torch.tensor([n if n <= SINK else (n - SINK - 1) % PAGE + 1 for n in (lengths[s] for s in slots)],
+                            dtype=torch.int32)
+        dev = self.device
+        view = ops.PageView(SINK, self.local, None, torch.tensor(slots, dtype=torch.int32, device=dev))
+        for layer in range(1 if self._alias else self.num_layers):
+            ops.build_summaries(self.kv_pages[layer], self.summaries[layer], indices.to(dev), indptr.to(dev),
+                                last.to(dev), status=self.status, view=view)
 
     # ---- page table of the active rows
     def _slots_of(self, batch_idx: torch.Tensor) -> List[int]:
@@ -184,8 +280,18 @@ class PooledKVManager(BatchKVManager):
 
     # ---- reference surface, on the pooled table
     def append_key_value_cache(self, new_key_cache, new_value_cache, batch_idx, layer_idx: int):
+        if self._step_table is not None:
+            # inside a prepared step: the table is in place and the host lengths are already advanced
+            indices, indptr, last, view = self._step_table
+            B = batch_idx.numel()
+            k = new_key_cache.reshape(B, self.num_key_value_heads, self.head_dim).contiguous()
+            v = new_value_cache.reshape(B, self.num_key_value_heads, self.head_dim).contiguous()
+            ops.append_kv(k, v, self.kv_pages[layer_idx], self.summaries[layer_idx], indices, indptr, last,
+                          status=self.status, view=view)
+            self.kv_offset[layer_idx][batch_idx] += 1
+            return indptr, last, view
         slots = self._slots_of(batch_idx)
-        lengths = [self._host_len[layer_idx][s] + 1 for s in slots]
+        lengths = [int(self._host_len[layer_idx][s]) + 1 for s in slots]
         indices, indptr, last, view = self._table_for(slots, lengths)
         B = len(slots)
         k = new_key_cache.reshape(B, self.num_key_value_heads, self.head_dim).contiguous()
@@ -202,7 +308,7 @@ class PooledKVManager(BatchKVManager):
         bsz, seq_len = query_states.shape[0], query_states.shape[2]
         assert bsz == 1, "prefill handles one sequence at a time, like the reference"
         slot = self._slots_of(batch_idx)[0]
-        offset = self._host_len[layer_idx][slot]
+        offset = int(self._host_len[layer_idx][slot])
         total = offset + seq_len
         indices, indptr, last, view = self._table_for([slot], [total])
         pages = self.kv_pages[layer_idx]
@@ -343,6 +449,51 @@ class Engine:
         self.slots_tokens[batch_idx, self.slots_offsets[batch_idx]] = next_tokens.reshape(-1)
         self.steps += 1
         return (next_tokens.reshape(-1, 1) == self.eos_tensor.view(1, -1)).any(dim=1)
+
+    # ---- the same step with its device work replayed from a CUDA graph
+    def _decode_device(self, batch_idx: torch.Tensor):
+        pos = self.slots_offsets[batch_idx]
+        input_ids = self.slots_tokens[batch_idx, pos].unsqueeze(1)
+        logits = self.model.inference(input_ids, pos.unsqueeze(1), batch_idx, self.kv)
+        next_tokens = self._sample(logits).reshape(-1)
+        self.slots_offsets[batch_idx] += 1
+        self.slots_tokens[batch_idx, pos + 1] = next_tokens
+        return next_tokens
+
+    def decode_graphed(self, slots: List[int]) -> torch.Tensor:
+        """`decode` for a `PooledKVManager` and greedy sampling, with everything the device does in one step --
+        embedding, all layers, vocabulary projection, argmax, token bookkeeping -- captured once and replayed.
+        The host part of a step is `kv.prepare_step` (page growth + table export into static buffers).  The set
+        of slots must not change between calls (capture a new engine step otherwise).  Returns the sampled
+        tokens [len(slots)] (a device tensor the next replay overwrites)."""
+        if self.temperature >= 0.02:
+            raise ValueError("decode_graphed samples greedily (temperature < 0.02)")
+        slots = list(slots)
+        if getattr(self, "_graph_slots", None) != slots:
+            self._graph_slots, self._graph = slots, None
+            self._graph_batch_idx = torch.tensor(slots, device=self.device)
+        self.kv.prepare_step(slots)
+        if self._graph is None:
+            # one eager pass warms every kernel up (and is this call's step); the graph serves the later calls
+            self._graph_out = self._decode_device(self._graph_batch_idx)
+            torch.cuda.synchronize(self.device)
+            self.kv.end_step()
+            self._graph = False
+        elif self._graph is False:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._graph_out = self._decode_device(self._graph_batch_idx)
+            # capture does not execute: run the captured step now
+            graph.replay()
+            self._graph = graph
+            self.kv.end_step()
+        else:
+            self._graph.replay()
+            self.kv.end_step()
+        for s in slots:
+            self._offsets_host[s] += 1
+        self.steps += 1
+        return self._graph_out
 
     def _sample(self, logits: torch.Tensor) -> torch.Tensor:
         return sample_next_tokens(logits, self.temperature, self.top_k, self.top_p, self.generator)

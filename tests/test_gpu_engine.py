@@ -122,3 +122,41 @@ def test_engine_generates_the_same_tokens_on_a_small_pool(cuda_device):
     assert sorted(got) == list(range(7)) and all(len(v) >= 1 for v in got.values())
     assert got == want
     assert small.pool.free_pages == 22 and not any(eng.slots_occupy_status)
+
+
+def test_graphed_decode_of_a_decoder_stack_equals_the_eager_engine_step(cuda_device):
+    # DecoderStack (the layer loop of litesys/models/qwen3.py on this library's ops) under Engine: prompts go
+    # through the prefill kernel, then the same greedy decode steps run eagerly (Engine.decode) and with the
+    # device work replayed from one CUDA graph (Engine.decode_graphed, host work in PooledKVManager.prepare_step)
+    from kinetics_b200 import DecoderStack, Engine, PooledKVManager
+    from kinetics_b200.config import LayerConfig
+    cfg = LayerConfig(hidden_size=256, num_attention_heads=4, num_key_value_heads=2, intermediate_size=512,
+                      num_hidden_layers=3, vocab_size=503)
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(21)
+    prompts = [torch.randint(0, 500, (1, n), generator=g) for n in (150, 37, 3, 96)]
+    kw = dict(attn_block_topk=3, attn_local=5, attn_block_size=16)
+
+    def make():
+        kv = PooledKVManager(cfg, 4, 256, cuda_device, dtype, num_pages=64, **kw)
+        model = DecoderStack(cfg, cuda_device, dtype, max_positions=300, seed=3)
+        eng = Engine(model, kv, 256, cuda_device, temperature=0.0, repeat_check=False)
+        for slot, p in enumerate(prompts):
+            eng.prefill(slot, p, 40)
+        return eng, kv
+
+    slots = [0, 1, 2, 3]
+    eager, kv_e = make()
+    graphed, kv_g = make()
+    assert torch.equal(eager.slots_tokens, graphed.slots_tokens)           # same prefill, same first token
+    for step in range(20):                                                 # several sequences cross page edges
+        eager.decode(slots)
+        out = graphed.decode_graphed(slots)
+        torch.cuda.synchronize()
+        n = [graphed._offsets_host[s] for s in slots]
+        assert n == [eager._offsets_host[s] for s in slots]
+        assert torch.equal(eager.slots_tokens, graphed.slots_tokens), step
+        assert out.tolist() == [int(graphed.slots_tokens[s, n[i]]) for i, s in enumerate(slots)]
+    kv_e.check_status()
+    kv_g.check_status()
+    assert kv_g.pool.free_pages == kv_e.pool.free_pages
