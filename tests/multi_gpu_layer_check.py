@@ -21,15 +21,60 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 TOL = 2e-2
 
 
+def stack_logits(dev, group, steps=4):
+    """A small DecoderStack (3 layers, attention through BatchKVManager): prompts through the prefill kernel,
+    then `steps` batched decode steps with fixed input tokens.  Returns the logits of every call.  The page
+    budget covers every page, so that a query bit that differs between the sharded and the unsharded GEMM
+    cannot flip a page selection (the layer check below compares selections): what is compared here is the
+    sharding of the weights, both exchanges of every layer and the head-sharded KV manager."""
+    import kinetics_b200 as kb
+    from kinetics_b200.config import LayerConfig
+    cfg = LayerConfig(hidden_size=512, num_attention_heads=16, num_key_value_heads=8, intermediate_size=1024,
+                      num_hidden_layers=3, vocab_size=1000)
+    dtype = torch.bfloat16
+    B = 8
+    model = kb.DecoderStack(cfg, dev, dtype, process_group=group, max_positions=512, decode_batch=B, seed=5)
+    kv = kb.BatchKVManager(cfg, B, 400, dev, dtype, attn_block_topk=32, attn_local=5, attn_block_size=16)
+    g = torch.Generator().manual_seed(8)
+    outs = []
+    lens = [150, 37, 96, 3, 200, 64, 17, 81]
+    for slot, n in enumerate(lens):
+        ids = torch.randint(0, 1000, (1, n), generator=g).to(dev)
+        pos = torch.arange(n, device=dev).unsqueeze(0)
+        outs.append(model.inference(ids, pos, torch.tensor([slot], device=dev), kv)[:, -1].clone())
+    bi = torch.arange(B, device=dev)
+    for step in range(steps):
+        ids = torch.randint(0, 1000, (B, 1), generator=g).to(dev)
+        pos = torch.tensor([[n + step] for n in lens], device=dev)
+        outs.append(model.inference(ids, pos, bi, kv)[:, 0].clone())
+    torch.cuda.synchronize()
+    kv.check_status()
+    model.check_status()
+    return outs
+
+
 def main():
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    # the unsharded stack first: the KV manager reads the world size from torch.distributed, as the reference's does
+    ref_logits = stack_logits(dev, None)
     dist.init_process_group("nccl", device_id=dev)
     rank, world = dist.get_rank(), dist.get_world_size()
     import kinetics_b200 as kb
     from kinetics_b200 import tp
     from kinetics_b200.config import LayerConfig
+
+    got_logits = stack_logits(dev, dist.group.WORLD)
+    worst_stack = 0.0
+    for a, b in zip(got_logits, ref_logits):
+        scale = b.abs().max().item()
+        err = (a - b).abs().max().item()
+        assert err <= 3e-2 * max(scale, 1.0), ("decoder stack", len(got_logits), err, scale)
+        worst_stack = max(worst_stack, err / max(scale, 1.0))
+        same = a.clone()
+        dist.broadcast(same, src=0)
+        assert torch.equal(same, a), "ranks disagree on the logits"
 
     cfg = LayerConfig(hidden_size=1024, num_attention_heads=32, num_key_value_heads=8, intermediate_size=2048,
                       num_hidden_layers=1)
@@ -112,6 +157,8 @@ def main():
     torch.cuda.synchronize()
     if rank == 0:
         print("\n".join(lines), flush=True)
+        print(f"tp decoder stack ok on {world} ranks: prefill + decode logits within {worst_stack:.4f} of the "
+              f"unsharded stack's (relative to the largest logit), identical on every rank", flush=True)
     sys.stdout.flush()
     del full
     import gc

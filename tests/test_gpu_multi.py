@@ -1,7 +1,8 @@
 """Multi-GPU checks, run as one process per GPU under torchrun when the machine has at least two GPUs:
 
 * ``multi_gpu_allreduce_check.py``: the fused NVLink exchange kernels against an fp32 all-reduce + torch;
-* ``multi_gpu_layer_check.py``: the KV-head-sharded decoder layer (both exchanges) against the TP=1 layer.
+* ``multi_gpu_layer_check.py``: the KV-head-sharded decoder layer (both exchanges) against the TP=1 layer, and a
+  sharded decoder stack (prefill + decode) against the unsharded one.
 """
 import os
 import subprocess
@@ -36,3 +37,4 @@ def test_sharded_layer_equals_tp1_layer():
     r = _torchrun("multi_gpu_layer_check.py", 2, 29543)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert r.stdout.count("tp layer ok on 2 ranks") == 5
+    assert "tp decoder stack ok on 2 ranks" in r.stdout
