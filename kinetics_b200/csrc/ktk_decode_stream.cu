@@ -19,17 +19,18 @@
 // CTA and continues into the next, "head" for a unit that started in an earlier CTA.
 // stream_combine_kernel then merges the pieces of every cut unit (at most one per CTA).
 // Which CTA holds which piece follows from the shapes alone, so results are deterministic.
+#include <cstdlib>
 #include <mutex>
 
 #include "ktk_decode_mma.cuh"
 
 namespace ktk {
 
-constexpr int kStreamCtasPerSm = 3;
+constexpr int kStreamMaxCtasPerSm = 4;                    // the most any variant keeps resident (sizes the workspace)
 constexpr int kStreamMinChunk = 16;                       // pages: below this a CTA is not worth its start-up
 constexpr int kExchangeHeads = 4;                         // heads merged per pass through shared memory
 constexpr int kExchangeBytes = kMmaConsumers * kExchangeHeads * kHeadDim * 4;   // 8 KiB
-constexpr int kStreamSmem = kMmaStages * kStageBytes + 1024 + kExchangeBytes;
+constexpr int stream_smem(int stages) { return stages * kStageBytes + 1024 + kExchangeBytes; }
 
 struct StreamParams {
     DecodeParams d;
@@ -150,8 +151,13 @@ __device__ __forceinline__ void consumer_bar() {          // the four consumer w
     asm volatile("bar.sync 1, %0;" ::"n"(kMmaConsumers * 32) : "memory");
 }
 
-__global__ void __launch_bounds__(kMmaThreads, kStreamCtasPerSm)
+// STAGES: ring depth (a multiple of the consumer count, so that a stage always belongs to one warp);
+// CTAS: CTAs resident per SM.
+template <int STAGES, int CTAS>
+__global__ void __launch_bounds__(kMmaThreads, CTAS)
 decode_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap kv_map) {
+    static_assert(STAGES % kMmaConsumers == 0, "a stage must belong to one consumer warp");
+    constexpr int kMmaStages = STAGES;                     // shadows the per-list kernel's ring depth
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kMmaStages];
     __shared__ __align__(8) uint64_t empty_bar[kMmaStages];
@@ -364,37 +370,71 @@ stream_combine_kernel(const StreamParams p) {
     }
 }
 
-// resident CTAs of decode_stream_kernel on the current device
-static int stream_slots() {
-    static std::mutex mu;
-    static int slots[64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return kStreamCtasPerSm * sm_count();
-    std::lock_guard<std::mutex> lock(mu);
-    if (slots[dev] == 0) {
-        int per_sm = 0;
-        cudaFuncSetAttribute(decode_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem);
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stream_kernel, kMmaThreads, kStreamSmem) !=
-                cudaSuccess || per_sm < 1)
-            per_sm = 1;
-        if (per_sm > kStreamCtasPerSm) per_sm = kStreamCtasPerSm;
-        slots[dev] = per_sm * sm_count();
-    }
-    return slots[dev];
+// Ring depth x residency variants.  Which one runs: the environment variable KTK_STREAM_VARIANT (a tuning knob,
+// read once), else the measured best for the kind of list.
+struct StreamVariant {
+    int stages, ctas;
+    void (*kernel)(const StreamParams, const CUtensorMap);
+};
+// Measured on a B200 at B = 4096, 32768-token context (sparse: 129 pages per list / dense: 2049), ms:
+//   4 stages x 4 CTAs per SM   0.639 / 9.53      <- default: 16 consumer warps per SM
+//   8 stages x 3 CTAs per SM   0.643 / 10.29
+//   4 stages x 3 CTAs per SM   0.668 / 10.16
+//   4 stages x 5 CTAs per SM   0.714 / 10.96     (72 registers: spills)
+//   8 or 12 stages x 2 CTAs    0.88  / 13.5
+// The consumer warps, not the bytes in flight, set the pace: more resident warps win until registers run out.
+static const StreamVariant kStreamVariants[] = {
+    {4, 4, decode_stream_kernel<4, 4>},      // 0
+    {8, 3, decode_stream_kernel<8, 3>},      // 1
+};
+constexpr int kNumStreamVariants = (int)(sizeof(kStreamVariants) / sizeof(kStreamVariants[0]));
+
+static int stream_variant_index(bool dense) {
+    static const int forced = [] {
+        const char* e = getenv("KTK_STREAM_VARIANT");
+        const int v = e ? atoi(e) : -1;
+        return (v >= 0 && v < kNumStreamVariants) ? v : -1;
+    }();
+    if (forced >= 0) return forced;
+    (void)dense;
+    return 0;
 }
 
-int stream_grid(int64_t units, int max_entries) {
+// resident CTAs of a variant on the current device
+static int stream_slots(int vi) {
+    static std::mutex mu;
+    static int slots[64][kNumStreamVariants] = {};
+    const StreamVariant& v = kStreamVariants[vi];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return v.ctas * sm_count();
+    std::lock_guard<std::mutex> lock(mu);
+    if (slots[dev][vi] == 0) {
+        int per_sm = 0;
+        const int smem = stream_smem(v.stages);
+        cudaFuncSetAttribute(v.kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, v.kernel, kMmaThreads, smem) != cudaSuccess ||
+            per_sm < 1)
+            per_sm = 1;
+        if (per_sm > v.ctas) per_sm = v.ctas;
+        slots[dev][vi] = per_sm * sm_count();
+    }
+    return slots[dev][vi];
+}
+
+static int stream_grid_of(int vi, int64_t units, int max_entries) {
     const int64_t total = units * (int64_t)max_entries;
     int64_t grid = (total + kStreamMinChunk - 1) / kStreamMinChunk;
-    const int64_t slots = stream_slots();
+    const int64_t slots = stream_slots(vi);
     if (grid > slots) grid = slots;
     if (grid < 1) grid = 1;
     return (int)grid;
 }
 
+int stream_grid(int64_t units, int max_entries) { return stream_grid_of(stream_variant_index(false), units, max_entries); }
+
 size_t stream_workspace_bytes(int G) {
     // two slots per CTA of the largest grid, each G rows of (m, l) + 128 floats
-    return (size_t)kStreamCtasPerSm * sm_count() * 2 * G * (2 + kHeadDim) * sizeof(float);
+    return (size_t)kStreamMaxCtasPerSm * sm_count() * 2 * G * (2 + kHeadDim) * sizeof(float);
 }
 
 int launch_decode_stream(const DecodeParams& p, int G, int max_entries, cudaStream_t st) {
@@ -410,7 +450,9 @@ int launch_decode_stream(const DecodeParams& p, int G, int max_entries, cudaStre
     sp.exact = (p.topk < 0 && p.page_count == nullptr) ? 1 : 0;
     const int64_t units = (int64_t)p.batch * p.Hkv;
     sp.total = units * max_entries;
-    int grid = stream_grid(units, max_entries);
+    const int vi = stream_variant_index(p.topk < 0);
+    const StreamVariant& var = kStreamVariants[vi];
+    int grid = stream_grid_of(vi, units, max_entries);
     const int64_t chunk = (sp.total + grid - 1) / grid;
     if (chunk > 2147483647LL) {
         set_error("ktk decode: %lld page positions per CTA exceed the balanced partition's limit", (long long)chunk);
@@ -418,9 +460,10 @@ int launch_decode_stream(const DecodeParams& p, int G, int max_entries, cudaStre
     }
     sp.chunk = (int)chunk;
     if (!sp.exact) grid = (int)((sp.total + chunk - 1) / chunk);            // no empty CTA
-    KTK_CUDA_TRY(cudaFuncSetAttribute(decode_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem),
+    const int smem = stream_smem(var.stages);
+    KTK_CUDA_TRY(cudaFuncSetAttribute(var.kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                  "ktk decode (balanced)");
-    decode_stream_kernel<<<grid, kMmaThreads, kStreamSmem, st>>>(sp, map);
+    var.kernel<<<grid, kMmaThreads, smem, st>>>(sp, map);
     KTK_CUDA_TRY(cudaGetLastError(), "ktk decode (balanced)");
     if (grid > 1 || sp.exact) {
         stream_combine_kernel<<<grid, kHeadDim, 0, st>>>(sp);
