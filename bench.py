@@ -33,26 +33,26 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # BASELINE.json configs[2] as one 8-way KV-head shard per GPU (68.2 GB of KV per GPU)
+    # the paper's throughput shape (Qwen3-8B, batch 4096, 32768-token context) as one 8-way KV-head shard per GPU (68.2 GB of KV per GPU)
     "cfg3-shard": dict(model="Qwen3-8B", tp=8, batch=4096, ctx=32768, topk=128),
-    # configs[1] at TP=8 and TP=1
+    # Qwen3-8B, batch 256, 8192-token context, top-k 64: at TP=8 (one shard) and TP=1
     "cfg2-shard": dict(model="Qwen3-8B", tp=8, batch=256, ctx=8192, topk=64),
     "cfg2-tp1": dict(model="Qwen3-8B", tp=1, batch=256, ctx=8192, topk=64),
-    # configs[3] shape with uniform context (ragged contexts are covered by the parity tests)
+    # the Qwen3-32B shape with uniform context (ragged contexts are covered by the parity tests)
     "cfg4-shard": dict(model="Qwen3-32B", tp=8, batch=1024, ctx=8192, topk=64),
-    # configs[3]: ragged contexts uniform in [1024, 16384], fragmented (randomly permuted) page pool, GQA 8
+    # Qwen3-32B: ragged contexts uniform in [1024, 16384], fragmented (randomly permuted) page pool, GQA 8
     "cfg4-ragged": dict(model="Qwen3-32B", tp=8, batch=1024, ctx=16384, topk=64, ragged=(1024, 16384)),
-    # configs[4]: Qwen3-1.7B (GQA 2, all 8 KV heads on one GPU), 512 sequences with contexts uniform in
+    # one Qwen3-1.7B layer (GQA 2, all 8 KV heads on one GPU), 512 sequences with contexts uniform in
     # [512, 32768]; a tenth of them sit on a page boundary, so the step opens a new page for those
     "cfg5-tp1": dict(model="Qwen3-1.7B", tp=1, batch=512, ctx=32768, topk=32, ragged=(512, 32768), boundary=0.1),
     "tiny": dict(model="Qwen3-8B", tp=8, batch=64, ctx=2048, topk=16),
-    # configs[4] as stated: the whole Qwen3-1.7B model (28 layers, final norm, vocabulary projection, greedy
+    # the whole Qwen3-1.7B model (28 layers, final norm, vocabulary projection, greedy
     # sampling) stepping 512 sequences with contexts uniform in [512, 32768], a tenth of them on a page boundary
     # at the first timed step, block top-k budget 32; tensor parallel over the GPUs of the run (--gpus 1/2/4/8),
     # driven by Engine + PagePool (the page table is exported on the host every step)
     "cfg5": dict(model="Qwen3-1.7B", tp=0, batch=512, ctx=32768, topk=32, ragged=(512, 32768), boundary=0.1,
                  full_model=True),
-    # configs[0]: fp32, one KV head with four query heads, 4 sequences of 2048 tokens, top-k 16
+    # the CPU-runnable reference case: fp32, one KV head with four query heads, 4 sequences of 2048 tokens, top-k 16
     "cfg1": dict(model="cfg1", tp=1, batch=4, ctx=2048, topk=16, dtype="float32"),
 }
 PAGE = 16
@@ -811,7 +811,7 @@ def run_micro_select(args):
 
 
 def run_full_model(args):
-    """BASELINE.json configs[4]: a full-model decode step.  One process per GPU; the model is tensor parallel
+    """A full-model decode step (Qwen3-1.7B, 512 sequences in continuous batching).  One process per GPU; the model is tensor parallel
     over the ranks of the run.  A step = Engine.decode_graphed: host page-table work (PagePool growth, CSR export,
     asynchronous copies into static device buffers) + one CUDA-graph replay of embedding, 28 layers (block top-k
     attention through PooledKVManager, LiteSys semantics: sink 4, layer 0 dense), final norm, vocabulary

@@ -1,4 +1,4 @@
-"""A stack of decoder layers with random weights: the caller that BASELINE's full-model decode step needs.
+"""A stack of decoder layers with random weights: the caller a full-model decode step needs.
 
 The layer loop of ``LiteSys/litesys/models/qwen3.py:89-143`` (``layer_compute`` + ``inference``) and, with a
 process group, of ``qwen3_dist.py:87-122`` (two all-reduces per layer), written over this library's ops:
@@ -12,7 +12,6 @@ model loader.
 """
 from __future__ import annotations
 
-import math
 from typing import Optional
 
 import torch

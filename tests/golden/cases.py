@@ -18,7 +18,7 @@ P = 16
 # of the score spread: a bf16 page summary carries ~0.4 % rounding noise that the reference's
 # fp32 block mean does not, and a closer call could legitimately go either way.
 CASES = {
-    # BASELINE.json configs[0]: B=4, 1 kv head, GQA 4, 2048-token context (+ the new token), top-k 16, fp32
+    # the CPU-runnable reference case: B=4, 1 kv head, GQA 4, 2048-token context (+ the new token), top-k 16, fp32
     "cfg1_fp32": (1234, 1, 4, [2049, 2049, 2049, 2049], 16, "float32"),
     "ragged_bf16": (2591, 2, 4, [33, 300, 273, 1029, 640], 8, "bfloat16"),
     "ragged_fp32": (1302, 2, 2, [129, 400, 97], 4, "float32"),

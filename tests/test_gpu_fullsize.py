@@ -19,7 +19,7 @@ def _uniform_table(B, n_pages, device, shuffle_seed=None):
 
 
 def test_selection_properties_at_the_headline_shape(cuda_device):
-    # BASELINE.json configs[2], one KV-head shard: B=4096, 2048 scored pages, top-k 128, G=4, bf16
+    # The paper's throughput shape (Qwen3-8B, batch 4096, 32768-token context), one KV-head shard: B=4096, 2048 scored pages, top-k 128, G=4, bf16
     from kinetics_b200 import ops
     B, n, k, G = 4096, 2048, 128, 4
     torch.manual_seed(11)
@@ -56,7 +56,7 @@ def test_selection_properties_at_the_headline_shape(cuda_device):
 
 
 def test_decode_properties_at_the_cfg2_shard_shape(cuda_device):
-    # BASELINE.json configs[1] at TP=8: B=256, 8192-token context (512 pages + the one being filled), k=64
+    # Qwen3-8B, batch 256, at TP=8: B=256, 8192-token context (512 pages + the one being filled), k=64
     from kinetics_b200 import ops
     B, n, k, G = 256, 512, 64, 4
     torch.manual_seed(12)
@@ -119,7 +119,7 @@ def test_append_then_select_sees_the_new_page_summary(cuda_device):
 
 
 def test_ragged_gqa2_properties_at_the_cfg5_shape(cuda_device):
-    # BASELINE.json configs[4] at TP=1: Qwen3-1.7B heads (8 KV heads, 2 query heads each), 512 sequences,
+    # The full-model configuration at TP=1: Qwen3-1.7B heads (8 KV heads, 2 query heads each), 512 sequences,
     # contexts uniform in [512, 32768], 51 of them on a page boundary (the step opens a new page), top-k 32.
     # The physical pool is smaller than the logical page count (ids are reused): the kernels only read it.
     from kinetics_b200 import ops
@@ -179,7 +179,7 @@ def test_ragged_gqa2_properties_at_the_cfg5_shape(cuda_device):
 
 
 def test_balanced_decode_at_the_headline_geometry(cuda_device):
-    # BASELINE.json configs[2], one KV-head shard: 4096 lists of 128 selected pages + the page being filled,
+    # The paper's throughput shape (Qwen3-8B, batch 4096, 32768-token context), one KV-head shard: 4096 lists of 128 selected pages + the page being filled,
     # G=4, bf16 -- the geometry the benchmark runs (444 CTAs, about 1190 list positions and 9 lists each).
     # The lists point into a small physical pool (ids are reused): the kernels only read it.
     from kinetics_b200 import ops

@@ -100,7 +100,7 @@ def test_graph_replay_equals_eager(cuda_device):
 
 
 def test_ragged_contexts_select_like_the_oracle(cuda_device):
-    # BASELINE.json configs[3] in small: ragged per-sequence contexts, fragmented page pool
+    # The Qwen3-32B ragged configuration in small: ragged per-sequence contexts, fragmented page pool
     import kinetics_b200 as kb
     dtype = torch.bfloat16
     torch.manual_seed(0)
