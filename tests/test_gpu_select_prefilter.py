@@ -54,7 +54,7 @@ def test_prefilter_equals_canonical_on_random_scores(cuda_device, G, Hkv, k, n):
                                   "zeros"])
 def test_prefilter_equals_canonical_on_hostile_data(cuda_device, case):
     B, Hkv, G, k, n = 64, 2, 4, 48, 777
-    torch.manual_seed(hash(case) % 1000)
+    torch.manual_seed(sum(map(ord, case)))
     summ = torch.randn(B, Hkv, n + 3, 128, device=cuda_device)
     q = torch.randn(B, Hkv * G, 128, device=cuda_device)
     if case == "huge":
