@@ -15,24 +15,8 @@
 // Selection orders pages by the 48-bit composite (key(score) << 16) | (0xFFFF - page),
 // which is unique per page: the k largest composites are "largest score first, ties
 // to the lowest page number".
-//
-// bf16 without a score output runs a tensor-core PREFILTER in front of that contract (MMA = true):
-//   1. every 16-row tile of summaries is staged by TMA (128-byte swizzle) and scored approximately as
-//      A[16 x 128] . [hi | lo] with qbar = hi + lo + r split into two bf16 vectors (|r| <= 2^-18 |qbar|), plus a
-//      second product |A| . roundup(|qbar|) = U >= sum_d |qbar_d s_d|, the scale of every rounding error involved;
-//   2. the k-th largest approximate score v_k is found; with delta = 2^-14 * max U (three times the summed error
-//      bounds of the bf16 split, the tensor-core accumulation and the canonical fp32 order) every page of the
-//      true top-k has an approximate score >= v_k - 2 delta;
-//   3. only those candidates (k plus a handful) are scored again, from global memory, in the canonical order
-//      above, and the selection runs on their exact scores.  More than 1024 candidates (near-equal scores,
-//      infinities) -> every page is scored exactly.
-// The result is the contract's, bit for bit; the scoring loop drops from ~200 to ~45 instructions per 16 rows.
-#include <cstdlib>
-#include <cstring>
-
 #include "ktk_common.cuh"
 #include "ktk_decode.cuh"
-#include "ktk_decode_mma.cuh"
 #include "ktk_pipeline.cuh"
 
 namespace ktk {
@@ -49,18 +33,11 @@ constexpr int kMaxTopk = 1024;
 constexpr int kSelBins = 2048;                      // first radix digit: the top 11 bits of a key
 constexpr int kSelBinShift = 21;
 constexpr int kCandMax = 512;                       // pages of the threshold bin ranked directly
-constexpr int kCandList = 1024;                     // prefilter: candidates scored exactly (the list reuses candc)
-constexpr int kMmaRows = 16;                        // prefilter: rows per stage = one m16 tile, 4 KiB
 static_assert(kSelBins == 8 * kSelThreads, "eight bins per thread in the digit search");
 static_assert(kSelStages % kSelWarps == 0, "a stage must belong to one consumer warp");
 
 __device__ __forceinline__ unsigned long long composite(uint32_t key, int page) {
     return ((unsigned long long)key << 16) | (unsigned long long)(0xFFFFu - (unsigned)page);
-}
-
-// inverse of score_to_key
-__device__ __forceinline__ float key_to_score(uint32_t key) {
-    return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
 }
 
 __device__ __forceinline__ void consumer_sync() {
@@ -120,9 +97,9 @@ __device__ __forceinline__ SelItem sel_item(int b, const int32_t* kv_indptr, con
 // are contiguous); stage i of the stream is scored by consumer warp i mod 8, sixteen lanes per
 // row.  While the consumers run the selection of one item, the producer is already filling the
 // ring with the rows of the next.  The first radix pass is histogrammed while scoring.
-template <typename T, int G, bool MMA>
+template <typename T, int G>
 __global__ void __launch_bounds__(kSelCtaThreads, kSelCtasPerSm)
-select_kernel(const __grid_constant__ CUtensorMap summ_map, const T* __restrict__ q, const T* __restrict__ summaries, int64_t summary_stride,
+select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t summary_stride,
               const int32_t* __restrict__ kv_indices, const int32_t* __restrict__ kv_indptr,
               const int32_t* __restrict__ kv_last_page_len, int topk, int key_cap, int kp, const SelView view,
               int32_t* __restrict__ out_pages, int32_t* __restrict__ out_logical,
@@ -139,19 +116,11 @@ select_kernel(const __grid_constant__ CUtensorMap summ_map, const T* __restrict_
     __shared__ int s_digit, s_greater, s_bincount, s_count, s_ccount;
     __shared__ int abort_flag, issued_total;
 
-    __shared__ __align__(16) __nv_bfloat16 qsplit[3][kHeadDim];   // prefilter: hi, lo, roundup(|qbar|)
-    __shared__ unsigned int s_umax, s_vk;
-    __shared__ int s_ncand;
-
     constexpr int kRowBytes = kHeadDim * (int)sizeof(T);
-    constexpr int kRowsPerStage = MMA ? kMmaRows : SelStage<T>::kRows;
+    constexpr int kRowsPerStage = SelStage<T>::kRows;
     constexpr int kSelStageBytes = kRowsPerStage * kRowBytes;
     static_assert(kRowsPerStage % 8 == 0, "eight rows per warp step");
-    static_assert(!MMA || sizeof(T) == 2, "the tensor-core prefilter is bf16 only");
-    // the swizzle pattern of a TMA tile is a function of the shared-memory address: stages start on 1 KiB
-    uint8_t* stage_base = MMA ? reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(sel_smem) + 1023) & ~uintptr_t(1023))
-                              : sel_smem;
-    unsigned long long* sel = reinterpret_cast<unsigned long long*>(stage_base + kSelStages * kSelStageBytes);
+    unsigned long long* sel = reinterpret_cast<unsigned long long*>(sel_smem + kSelStages * kSelStageBytes);
     uint32_t* keys = reinterpret_cast<uint32_t*>(sel + kp);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -172,7 +141,6 @@ select_kernel(const __grid_constant__ CUtensorMap summ_map, const T* __restrict_
     if (warp == kSelWarps) {
         // ---------------- producer warp: one lane issues the bulk copies ----------------
         if (lane == 0) {
-            if constexpr (MMA) prefetch_tensormap(&summ_map);
             int i = 0;           // stages issued so far, over all items of this CTA
             bool alive = true;
             for (int64_t bh = blockIdx.x; bh < n_items && alive; bh += gridDim.x) {
@@ -188,24 +156,10 @@ select_kernel(const __grid_constant__ CUtensorMap summ_map, const T* __restrict_
                         break;
                     }
                     const int r0 = st * kRowsPerStage;
-                    if constexpr (MMA) {
-                        // one 16-row tile as two boxes of 16 rows x 128 bytes; rows past the item's (or the
-                        // tensor's) end arrive too and are ignored
-                        // the last tile starts early enough to end inside this (slot, head) block of summaries, so
-                        // that no copy ever reaches past the tensor; its first rows were scored by the tile before
-                        const int room = (int)summary_stride - it.front - kMmaRows;
-                        const int rs = r0 < room ? r0 : room;
-                        const int64_t grow = ((int64_t)it.slot * Hkv + h) * summary_stride + it.front + rs;
-                        uint8_t* dst = stage_base + s * kSelStageBytes;
-                        mbar_arrive_expect_tx(&full_bar[s], kSelStageBytes);
-                        tma_load_3d(dst, &summ_map, &full_bar[s], 0, (int)grow, 0);
-                        tma_load_3d(dst + kHalfTile, &summ_map, &full_bar[s], 64, (int)grow, 0);
-                    } else {
-                        const int rows = (it.n_scored - r0 < kRowsPerStage) ? it.n_scored - r0 : kRowsPerStage;
-                        const uint32_t bytes = (uint32_t)rows * kRowBytes;
-                        mbar_arrive_expect_tx(&full_bar[s], bytes);
-                        bulk_load(stage_base + s * kSelStageBytes, sbase + (int64_t)r0 * kHeadDim, bytes, &full_bar[s]);
-                    }
+                    const int rows = (it.n_scored - r0 < kRowsPerStage) ? it.n_scored - r0 : kRowsPerStage;
+                    const uint32_t bytes = (uint32_t)rows * kRowBytes;
+                    mbar_arrive_expect_tx(&full_bar[s], bytes);
+                    bulk_load(sel_smem + s * kSelStageBytes, sbase + (int64_t)r0 * kHeadDim, bytes, &full_bar[s]);
                 }
             }
             issued_total = i;
@@ -231,86 +185,15 @@ select_kernel(const __grid_constant__ CUtensorMap summ_map, const T* __restrict_
             if (it.scan) {
 #pragma unroll
                 for (int i = 0; i < kSelBins / kSelThreads; ++i) hist[tid + i * kSelThreads] = 0;
-                if (tid == 0) { s_count = 0; s_ccount = 0; s_ncand = 0; s_umax = 0u; s_vk = 0u; }
+                if (tid == 0) { s_count = 0; s_ccount = 0; }
                 if (tid < kHeadDim) {
                     const T* qp = q + ((int64_t)b * Hkv * G + (int64_t)h * G) * kHeadDim + tid;
                     float acc = 0.0f;
 #pragma unroll
                     for (int g = 0; g < G; ++g) acc = __fadd_rn(acc, to_f32(qp[g * kHeadDim]));
-                    const float qb_ = __fmul_rn(acc, 1.0f / (float)G);
-                    qbar[tid] = qb_;
-                    if constexpr (MMA) {
-                        const __nv_bfloat16 hi = __float2bfloat16_rn(qb_);
-                        qsplit[0][tid] = hi;
-                        qsplit[1][tid] = __float2bfloat16_rn(qb_ - __bfloat162float(hi));   // the difference is exact
-                        qsplit[2][tid] = __float2bfloat16_ru(fabsf(qb_));
-                    }
+                    qbar[tid] = __fmul_rn(acc, 1.0f / (float)G);
                 }
                 consumer_sync();
-              if constexpr (MMA) {
-                // ---- prefilter, step 1: approximate scores of every row on the tensor cores ----
-                const int gid = lane >> 2, tig = lane & 3;
-                const int mj = lane >> 3, mr = lane & 7;
-                const int k_tok = mr + 8 * (mj & 1), k_c = mj >> 1;       // A fragments as the decode kernels load K
-                uint32_t qs[8][2], qu[8][2];                              // B fragments: column gid of [hi | lo | 0..], [|q| | 0..]
-                {
-                    const uint32_t* ps = reinterpret_cast<const uint32_t*>(qsplit[gid < 2 ? gid : 0]);
-                    const uint32_t* pu = reinterpret_cast<const uint32_t*>(qsplit[2]);
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
-                        qs[ks][0] = gid < 2 ? ps[ks * 8 + tig] : 0u;
-                        qs[ks][1] = gid < 2 ? ps[ks * 8 + 4 + tig] : 0u;
-                        qu[ks][0] = gid == 0 ? pu[ks * 8 + tig] : 0u;
-                        qu[ks][1] = gid == 0 ? pu[ks * 8 + 4 + tig] : 0u;
-                    }
-                }
-                float umax = 0.0f;
-                int i = ibase + ((warp - ibase) & (kSelWarps - 1));
-                bool ok = true;
-                for (; i < ibase + it.n_stages; i += kSelWarps) {
-                    const int s = i % kSelStages;
-                    if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], (i / kSelStages) & 1, &abort_flag))) {
-                        ok = false;
-                        break;
-                    }
-                    const uint32_t kt = smem_u32(stage_base + s * kSelStageBytes);
-                    float sa[4] = {0.f, 0.f, 0.f, 0.f}, ua[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
-                        uint32_t ka[4];
-                        ldmatrix_x4(ka, kt + tile_off(k_tok, 2 * ks + k_c));
-                        mma_bf16(sa, ka, qs[ks][0], qs[ks][1]);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) ka[e] &= 0x7fff7fffu;          // |A|
-                        mma_bf16(ua, ka, qu[ks][0], qu[ks][1]);
-                    }
-                    if (tig == 0) {
-                        // columns 0 (hi) and 1 (lo) of rows gid and gid + 8; column 0 of the bound product
-                        const int r0 = (i - ibase) * kRowsPerStage;
-                        const int room = (int)summary_stride - it.front - kMmaRows;
-                        const int rs = r0 < room ? r0 : room;                  // where the producer started this tile
-#pragma unroll
-                        for (int half = 0; half < 2; ++half) {
-                            const int r = rs + gid + 8 * half;
-                            if (r >= r0 && r < it.n_scored) {
-                                const uint32_t key = score_to_key(sa[2 * half] + sa[2 * half + 1]);
-                                keys[r] = key;
-                                atomicAdd(&hist[key >> kSelBinShift], 1u);
-                                umax = fmaxf(umax, ua[2 * half]);
-                                if (!(ua[2 * half] == ua[2 * half])) umax = INFINITY;   // NaN: no bound
-                            }
-                        }
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&empty_bar[s]);
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) umax = fmaxf(umax, __shfl_xor_sync(0xffffffffu, umax, o));
-                if (lane == 0) atomicMax(&s_umax, __float_as_uint(umax));      // non-negative floats order as integers
-                ibase += it.n_stages;
-                consumer_sync();
-                if (!ok || abort_flag) break;
-              } else {
                 // Four lanes per row: lane j of a row owns the 8-element chunks j, j+4, j+8, j+12, i.e. the
                 // chunks whose partial sums meet in the first two levels of the contract's butterfly, so
                 // those two levels are plain in-lane adds and only two shuffles per row remain.  Odd rows
@@ -334,7 +217,7 @@ select_kernel(const __grid_constant__ CUtensorMap summ_map, const T* __restrict_
                         ok = false;
                         break;
                     }
-                    const T* stage = reinterpret_cast<const T*>(stage_base + s * kSelStageBytes);
+                    const T* stage = reinterpret_cast<const T*>(sel_smem + s * kSelStageBytes);
                     const int r0 = (i - ibase) * kRowsPerStage;
                     constexpr int kSteps = kRowsPerStage / 8;
                     static_assert(kSteps <= 4, "one lane of a row group finishes one step's scores");
@@ -380,7 +263,6 @@ select_kernel(const __grid_constant__ CUtensorMap summ_map, const T* __restrict_
                 ibase += it.n_stages;
                 consumer_sync();            // every key of the item is in shared memory (or the CTA gave up)
                 if (!ok || abort_flag) break;
-              }
             }
 
             if (!it.need_select) {
@@ -401,7 +283,7 @@ select_kernel(const __grid_constant__ CUtensorMap summ_map, const T* __restrict_
             // ---- the k-th largest 48-bit composite.  First digit: the top 11 bits of the key (sign,
             //      exponent, two mantissa bits), histogrammed while scoring.  Thread t owns bins
             //      2047-8t .. 2040-8t; a block-wide scan finds the bin in which the k-th largest falls.
-            auto find_digit = [&]() {
+            {
                 unsigned cnt[8];
                 unsigned mine = 0;
 #pragma unroll
@@ -429,92 +311,7 @@ select_kernel(const __grid_constant__ CUtensorMap summ_map, const T* __restrict_
                     running += cnt[j];
                 }
                 consumer_sync();
-            };
-            if constexpr (MMA) {
-                // ---- prefilter, step 2: v_k, the k-th largest APPROXIMATE key ----
-                find_digit();
-                const int dg0 = s_digit, greater0 = s_greater, bin0 = s_bincount;
-                if (bin0 <= kCandMax) {
-                    for (int i = tid; i < it.n_scored; i += kSelThreads) {
-                        const uint32_t key = keys[i];
-                        if ((int)(key >> kSelBinShift) == dg0) candc[atomicAdd(&s_ccount, 1)] = composite(key, i);
-                    }
-                    consumer_sync();
-                    const int need0 = topk - greater0;
-                    for (int c = tid; c < bin0; c += kSelThreads) {
-                        const unsigned long long mine = candc[c];
-                        int rank = 0;
-                        for (int j = 0; j < bin0; ++j) rank += (candc[j] > mine) ? 1 : 0;
-                        if (rank == need0 - 1) s_vk = (uint32_t)(mine >> 16);
-                    }
-                } else if (tid == 0) {
-                    s_vk = (uint32_t)dg0 << kSelBinShift;          // the lower edge of the bin: a weaker, still valid bound
-                }
-                consumer_sync();
-                // ---- step 3: the candidates.  |approximate - canonical| <= delta for every row, so at least k rows
-                //      have a canonical score >= v_k - delta, and a row of the true top-k has an approximate score
-                //      >= v_k - 2 delta.  delta = 2^-14 * max U, rounded up (error budget in the header comment).
-                const float umax_all = __uint_as_float(s_umax);
-                const float delta = __fadd_ru(__fmul_ru(umax_all, 6.2e-5f), 1e-30f);
-                const float thr = __fsub_rd(key_to_score(s_vk), __fmul_ru(2.0f, delta));
-                const bool all_rows = !(delta < INFINITY) || !(thr == thr);
-                const uint32_t tkey = score_to_key(thr);
-                if (tid == 0) s_ccount = 0;
-                int* cand = reinterpret_cast<int*>(candc);         // kCandList ints fit the composites' array
-                for (int i = tid; i < it.n_scored; i += kSelThreads) {
-                    if (all_rows || keys[i] >= tkey) {
-                        const int pos = atomicAdd(&s_ncand, 1);
-                        if (pos < kCandList) cand[pos] = i;
-                    } else {
-                        keys[i] = 0u;                              // below every real key: never selected
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < kSelBins / kSelThreads; ++i) hist[tid + i * kSelThreads] = 0;
-                consumer_sync();
-                // ---- step 4: canonical scores of the candidates (all rows if the list overflowed), read from
-                //      global memory, four lanes per row exactly as in the contract ----
-                const bool overflow = s_ncand > kCandList;
-                const int n_do = overflow ? it.n_scored : s_ncand;
-                const T* sbase = summaries + (((int64_t)it.slot * Hkv + h) * summary_stride + it.front) * kHeadDim;
-                const int rw = lane >> 2, j4 = lane & 3;
-                float q0[8], q1[8], q2[8], q3[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    q0[e] = qbar[j4 * 8 + e]; q1[e] = qbar[(j4 + 4) * 8 + e];
-                    q2[e] = qbar[(j4 + 8) * 8 + e]; q3[e] = qbar[(j4 + 12) * 8 + e];
-                }
-                for (int base = warp * 8; base < n_do; base += kSelWarps * 8) {
-                    const int c = base + rw;
-                    const bool valid = c < n_do;
-                    const int r = valid ? (overflow ? c : cand[c]) : 0;
-                    const T* rowp = sbase + (int64_t)r * kHeadDim;
-                    float x0[8], x1[8], x2[8], x3[8];
-                    load8(rowp + j4 * 8, x0);
-                    load8(rowp + (j4 + 4) * 8, x1);
-                    load8(rowp + (j4 + 8) * 8, x2);
-                    load8(rowp + (j4 + 12) * 8, x3);
-                    float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        p0 = __fmaf_rn(q0[e], x0[e], p0);
-                        p1 = __fmaf_rn(q1[e], x1[e], p1);
-                        p2 = __fmaf_rn(q2[e], x2[e], p2);
-                        p3 = __fmaf_rn(q3[e], x3[e], p3);
-                    }
-                    float acc = __fadd_rn(__fadd_rn(p0, p2), __fadd_rn(p1, p3));
-                    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
-                    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
-                    acc = __fadd_rn(acc, 0.0f);
-                    if (valid && j4 == 0) {
-                        const uint32_t key = score_to_key(acc);
-                        keys[r] = key;
-                        atomicAdd(&hist[key >> kSelBinShift], 1u);
-                    }
-                }
-                consumer_sync();            // exact keys of every possible winner, histogram rebuilt
             }
-            find_digit();
             const int digit = s_digit, greater = s_greater, bincount = s_bincount;
             if (bincount <= kCandMax) {
                 // ---- usual case: pages with a larger digit are winners; the few pages of the threshold
@@ -661,7 +458,7 @@ select_kernel(const __grid_constant__ CUtensorMap summ_map, const T* __restrict_
     }
 }
 
-template <typename T, int G, bool MMA>
+template <typename T, int G>
 static int select_launch(const void* q, const void* summaries, int64_t summary_stride,
                          const int32_t* kv_indices, const int32_t* kv_indptr,
                          const int32_t* kv_last_page_len, int topk, SelView view, int32_t* out_pages,
@@ -670,42 +467,29 @@ static int select_launch(const void* q, const void* summaries, int64_t summary_s
     int key_cap = (int)(summary_stride < kMaxScoredPages ? summary_stride : kMaxScoredPages);
     int kp = 1;
     while (kp < topk) kp <<= 1;
-    const size_t smem = (size_t)kSelStages * (MMA ? kMmaRows : SelStage<T>::kRows) * kHeadDim * sizeof(T) +
-                        (size_t)kp * 8 + (size_t)key_cap * sizeof(uint32_t) + (MMA ? 1024 : 0);
-    CUtensorMap map;
-    memset(&map, 0, sizeof(map));
-    if (MMA) {
-        // summaries as rows of 128 bf16; tiles of 16 rows x 64 elements with the 128-byte swizzle.  Tiles never leave
-        // the (slot, head) block they start in, so the row count only has to be an upper bound.
-        const int64_t rows = view.slot_index ? 2147483647LL : (int64_t)s->batch * s->num_kv_heads * summary_stride;
-        const uint64_t dims[3] = {(uint64_t)kHeadDim, (uint64_t)rows, 1};
-        const uint64_t strides[2] = {(uint64_t)kHeadDim * 2, (uint64_t)kHeadDim * 2 * (uint64_t)rows};
-        const uint32_t box[3] = {64, (uint32_t)kMmaRows, 1};
-        int rc = make_tensor_map_3d(&map, summaries, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, dims, strides, box,
-                                    CU_TENSOR_MAP_SWIZZLE_128B, "ktk_select");
-        if (rc != KTK_OK) return rc;
-    }
-    auto kern = select_kernel<T, G, MMA>;
+    const size_t smem = (size_t)kSelStages * SelStage<T>::kRows * kHeadDim * sizeof(T) + (size_t)kp * 8 +
+                        (size_t)key_cap * sizeof(uint32_t);
+    auto kern = select_kernel<T, G>;
     KTK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                  "ktk_select");
     const int64_t items = (int64_t)s->batch * s->num_kv_heads;
     int64_t grid = (int64_t)sm_count() * kSelCtasPerSm;
     if (grid > items) grid = items;
     kern<<<(unsigned)grid, kSelCtaThreads, smem, st>>>(
-        map, (const T*)q, (const T*)summaries, summary_stride, kv_indices, kv_indptr, kv_last_page_len,
+        (const T*)q, (const T*)summaries, summary_stride, kv_indices, kv_indptr, kv_last_page_len,
         topk, key_cap, kp, view, out_pages, out_logical, out_scores, items, s->num_kv_heads, s->num_pages,
         status);
     KTK_CUDA_TRY(cudaGetLastError(), "ktk_select");
     return KTK_OK;
 }
 
-template <typename T, bool MMA, typename... A>
+template <typename T, typename... A>
 static int select_group(int G, A... a) {
     switch (G) {
-        case 1: return select_launch<T, 1, MMA>(a...);
-        case 2: return select_launch<T, 2, MMA>(a...);
-        case 4: return select_launch<T, 4, MMA>(a...);
-        default: return select_launch<T, 8, MMA>(a...);
+        case 1: return select_launch<T, 1>(a...);
+        case 2: return select_launch<T, 2>(a...);
+        case 4: return select_launch<T, 4>(a...);
+        default: return select_launch<T, 8>(a...);
     }
 }
 
@@ -755,21 +539,12 @@ extern "C" int ktk_select_v(const void* q, const void* summaries, int64_t summar
     sv.page_count = v.page_count; sv.slot_index = v.slot_index;
     cudaStream_t st = (cudaStream_t)stream;
     if (shape->dtype == KTK_F32)
-        return select_group<float, false>(shape->group_size, q, summaries, summary_stride, kv_indices,
-                                          kv_indptr, kv_last_page_len, (int)topk, sv, out_pages, out_logical,
-                                          out_scores, shape, status, st);
-    // bf16: the tensor-core prefilter, unless the caller wants every score (they are then computed in the
-    // canonical order for every row anyway) or a block of summaries is shorter than one tile
-    static const bool no_prefilter = getenv("KTK_SELECT_NO_PREFILTER") != nullptr;     // A/B knob for tests
-    const bool mma = out_scores == nullptr && summary_stride >= kMmaRows + 1 && !no_prefilter &&
-                     (int64_t)shape->batch * shape->num_kv_heads * summary_stride < 2147483647LL;
-    if (mma)
-        return select_group<__nv_bfloat16, true>(shape->group_size, q, summaries, summary_stride, kv_indices,
-                                                 kv_indptr, kv_last_page_len, (int)topk, sv, out_pages,
-                                                 out_logical, out_scores, shape, status, st);
-    return select_group<__nv_bfloat16, false>(shape->group_size, q, summaries, summary_stride, kv_indices,
-                                              kv_indptr, kv_last_page_len, (int)topk, sv, out_pages,
-                                              out_logical, out_scores, shape, status, st);
+        return select_group<float>(shape->group_size, q, summaries, summary_stride, kv_indices,
+                                   kv_indptr, kv_last_page_len, (int)topk, sv, out_pages, out_logical,
+                                   out_scores, shape, status, st);
+    return select_group<__nv_bfloat16>(shape->group_size, q, summaries, summary_stride, kv_indices,
+                                       kv_indptr, kv_last_page_len, (int)topk, sv, out_pages,
+                                       out_logical, out_scores, shape, status, st);
 }
 
 extern "C" int ktk_select(const void* q, const void* summaries, int64_t summary_stride,
