@@ -60,9 +60,9 @@ HEAD_DIM = 128
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_stream_kernel launch over its algorithmic bytes,
 # from a profiler capture of the same kernel and shape at batch 296 (one CTA per resident slot, every page
 # read once: the traffic grows with the batch in proportion)
-DECODE_TRAFFIC_RATIO = 1.019
+DECODE_TRAFFIC_RATIO = 1.016
 DECODE_TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of decode_stream_kernel at batch 296 of "
-                         "this shape = 1.019 x algorithmic bytes, applied to this run's bytes")
+                         "this shape = 1.016 x algorithmic bytes, applied to this run's bytes")
 
 
 def parse():
