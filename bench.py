@@ -88,8 +88,8 @@ def parse():
     ap.add_argument("--down-exchange", default="scatter", choices=["scatter", "allreduce"],
                     help="N > 1: what the down_proj exchange leaves on a rank: its row slice of the layer output "
                          "(reduce-scatter + residual) or all rows (all-reduce + residual, the reference's form)")
-    ap.add_argument("--exchange-schedule", default="lockstep", choices=["pipelined", "lockstep"],
-                    help="schedule of the fused o_proj exchange kernel")
+    ap.add_argument("--exchange-schedule", default=None, choices=["pipelined", "lockstep"],
+                    help="schedule of the fused o_proj exchange kernel (default: by size, lock-step above 8 MiB)")
     ap.add_argument("--reps", type=int, default=5, help="repetitions of the --steps loop; the median is reported")
     ap.add_argument("--no-flashinfer", action="store_true",
                     help="skip the library comparison.  By default a one-GPU run also times, on the same cache and "
@@ -1031,19 +1031,29 @@ def run_micro_exchange(args):
     part = torch.randn(rows, cols, device=dev).to(torch.bfloat16)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
+    per_graph = 20                                           # calls captured into one CUDA graph: short
+                                                             # exchanges are otherwise paced by the host's launches
     def timed(fn):
         for _ in range(max(3, args.warmup)):
             fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(per_graph):
+                fn()
+        graph.replay()
+        replays = max(1, args.steps // per_graph)
         dist.barrier(); torch.cuda.synchronize()
         e0.record()
-        for _ in range(args.steps):
-            fn()
+        for _ in range(replays):
+            graph.replay()
         e1.record(); torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+        t = torch.tensor([e0.elapsed_time(e1) / (replays * per_graph)], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()) * 1e3                         # microseconds
 
-    out = {"micro": "exchange", "ranks": world, "rows": rows, "cols": cols, "bytes": rows * cols * 2, "us": {}}
+    out = {"micro": "exchange", "ranks": world, "rows": rows, "cols": cols, "bytes": rows * cols * 2,
+           "timing": "CUDA events around replays of a graph of 20 calls", "us": {}}
     forms = [("multicast", _lib.ALLREDUCE_MULTICAST)] + ([("peer", _lib.ALLREDUCE_PEER)] if world in (2, 4) else [])
     for fname, mode in forms:
         for schedule, result in (("lockstep", "allreduce_norm"), ("pipelined", "allreduce_norm"),

@@ -31,17 +31,22 @@ class FusedExchange:
     ``norm``  ``allreduce_norm`` only: RMSNorm of ``sum``
 
     ``schedule``: "pipelined" (ktk_exchange_rows) or "lockstep" (ktk_allreduce_add_rmsnorm, the
-    all-reduce + norm result only).
+    all-reduce + norm result only); None picks by size for the all-reduce + norm.
     """
+
+    PIPELINED_UP_TO = 8 << 20          # bytes of [rows, cols] bf16 up to which the all-reduce + norm is pipelined
 
     def __init__(self, group, rows: int, cols: int, dtype, device, mode: int = _lib.ALLREDUCE_AUTO,
                  result: str = "allreduce_norm", schedule: str = None):
         import torch.distributed._symmetric_memory as symm_mem
 
         if schedule is None:
-            # measured on two B200s, 32 MiB: the lock-step all-reduce + norm takes 79 us, the row-pipelined one
-            # 109 us (one system-scope release per row); only the pipelined kernel has the other two results
-            schedule = "lockstep" if result == "allreduce_norm" else "pipelined"
+            # all-reduce + norm, measured inside CUDA graphs on four B200s: up to 8 MiB the row-pipelined kernel
+            # is ahead (2 MiB: 20 us against 28 us, 8 MiB: 40 against 47 -- no closing barrier before the norm of
+            # the peers' rows); from 16 MiB the lock-step one is (32 MiB: 105 against 120 -- one system-scope
+            # release per CTA instead of one per row).  Only the pipelined kernel has the other two results.
+            small = rows * cols * 2 <= self.PIPELINED_UP_TO
+            schedule = "pipelined" if result != "allreduce_norm" or small else "lockstep"
 
         if dtype != torch.bfloat16:
             raise TypeError("the fused exchange is built for bfloat16")

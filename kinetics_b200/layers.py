@@ -80,7 +80,7 @@ class _PagedDecoderLayer(nn.Module):
     def __init__(self, config, world_size, batch_size, prefix_len, max_len, page_size, device, dtype,
                  page_table: str = "interleaved", process_group=None, seed: int = 0, variant: int = 0,
                  kv_cache: Optional[torch.Tensor] = None, context_lens=None, fused_allreduce: bool = False,
-                 down_exchange: str = "allreduce", exchange_schedule: str = "lockstep"):
+                 down_exchange: str = "allreduce", exchange_schedule: Optional[str] = None):
         super().__init__()
         self.num_heads = config.num_attention_heads // world_size
         self.num_kv_heads = config.num_key_value_heads // world_size
