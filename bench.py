@@ -102,6 +102,9 @@ def parse():
     ap.add_argument("--library-timeout", type=float, default=420.0,
                     help="seconds the library comparison may take (flashinfer builds its kernels on first use)")
     ap.add_argument("--layers", type=int, default=0, help="full-model workloads: run this many layers (0: all)")
+    ap.add_argument("--one-rank-of", type=int, default=0,
+                    help="full-model workloads on one GPU: run the compute of ONE rank of this many (heads and MLP "
+                         "width divided, no exchange) -- what a step costs without the NVLink exchanges")
     ap.add_argument("--micro", default="", choices=["", "select", "exchange"],
                     help="time one kernel alone on the workload's shapes (select: only the page summaries are "
                          "allocated, so the full batch fits in a few GB; exchange: the NVLink exchange kernels "
@@ -870,6 +873,12 @@ def run_full_model(args):
     if args.batch:
         wl["batch"] = args.batch
     cfg = kb.get_config(wl["model"])
+    shard_of = args.one_rank_of if world == 1 else 0
+    if shard_of > 1:
+        import dataclasses
+        cfg = dataclasses.replace(cfg, num_attention_heads=cfg.num_attention_heads // shard_of,
+                                  num_key_value_heads=cfg.num_key_value_heads // shard_of,
+                                  intermediate_size=cfg.intermediate_size // shard_of)
     B, topk = wl["batch"], wl["topk"]
     lo, hi = wl["ragged"]
     dtype = torch.bfloat16
@@ -899,8 +908,9 @@ def run_full_model(args):
     for pages in ({id(p): p for p in kv.kv_pages}.values()):
         pages.normal_()                                      # KV pre-filled from N(0, 1)
     kv.assume_filled({s: int(lens[s]) for s in range(B)}, headroom=steps_total)
+    # greedy sampling: the argmax is taken over the bf16 logits (identical to the argmax of an fp32 copy)
     model = kb.DecoderStack(cfg, device, dtype, process_group=pg, max_positions=max_seq + 8, decode_batch=B,
-                            seed=args.seed, num_layers=layers)
+                            seed=args.seed, num_layers=layers, logits_dtype=None)
     eng = kb.Engine(model, kv, max_seq, device, temperature=0.0, repeat_check=False)
     slots = list(range(B))
     for s in slots:
@@ -988,7 +998,8 @@ def run_full_model(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"{args.workload}: {wl['model']} full model, {layers} layers + final norm + "
                                    f"vocabulary projection + greedy sampling, {B} sequences, contexts uniform in "
-                                   f"{[lo, hi]}, top-k {topk} pages, page {PAGE}, tensor parallel over {world} GPU(s)",
+                                   f"{[lo, hi]}, top-k {topk} pages, page {PAGE}, tensor parallel over {world} GPU(s)"
+                                   + (f"; ONE RANK OF {shard_of} emulated, no exchange" if shard_of > 1 else ""),
                        "batch": B, "layers": layers, "topk_pages": topk, "parallelism": f"tp{world} by KV head",
                        "kv_pool_pages": pool_pages, "kv_bytes_per_layer_per_gpu": kv_bytes_layer,
                        "layers_share_one_physical_pool": alias,

@@ -94,8 +94,9 @@ class BatchKVManager:
         self.pages_per_slot = 1 + (max(max_seq_len - SINK, 0) + PAGE - 1) // PAGE
         self._alloc_pages()
         self.summaries = self._alloc_summaries()
-        self.kv_offset = [torch.zeros(max_batch_size, device=self.device, dtype=torch.int32)
-                          for _ in range(self.num_layers)]
+        # one [layers, max_batch] tensor; kv_offset[layer] (the reference's list) are its rows
+        self._kv_offset_all = torch.zeros(self.num_layers, max_batch_size, device=self.device, dtype=torch.int32)
+        self.kv_offset = list(self._kv_offset_all.unbind(0))
         self.status = ops.new_status(self.device)
         self.row_width = ops.PageView(SINK, self.local).row_width(self.block_topk) if self.block_topk else 0
         self._sel = None

@@ -22,7 +22,11 @@ from . import ops, tp
 
 class DecoderStack:
     def __init__(self, config, device, dtype=torch.bfloat16, process_group=None, max_positions: int = 40960,
-                 decode_batch: int = 0, seed: int = 0, num_layers: Optional[int] = None):
+                 decode_batch: int = 0, seed: int = 0, num_layers: Optional[int] = None,
+                 logits_dtype=torch.float32):
+        # logits_dtype: fp32 as the reference returns them (qwen3.py:141); None leaves them in the compute dtype,
+        # which greedy sampling can take as they are (the argmax of bf16 logits is the argmax of their fp32 copies)
+        self.logits_dtype = logits_dtype
         self.config, self.device, self.dtype = config, torch.device(device), dtype
         self.group = process_group
         self.world = torch.distributed.get_world_size(process_group) if process_group is not None else 1
@@ -103,7 +107,10 @@ class DecoderStack:
             nxt = self.layers[i + 1]["input_norm"] if i + 1 < self.num_layers else self.norm_weight
             x, n = self._reduce_add_norm(self.ex_d, act, L["down"].t(), x, nxt)
         # n is the final RMSNorm of the residual stream (qwen3.py:139)
-        return torch.mm(n, self.lm_head.t()).float().view(bsz, seq_len, -1)
+        logits = torch.mm(n, self.lm_head.t())
+        if self.logits_dtype is not None:
+            logits = logits.to(self.logits_dtype)
+        return logits.view(bsz, seq_len, -1)
 
     def check_status(self):
         for ex in (self.ex_o, self.ex_d):

@@ -156,6 +156,7 @@ class PooledKVManager(BatchKVManager):
         self._table_key = None
         self._table_val = None
         self._step_table = None          # set by prepare_step: the table every layer of the step uses
+        self._step_offsets_advanced = False
         self._static = None              # static device buffers + pinned mirrors of that table
 
     # ---- admission / retirement
@@ -212,6 +213,7 @@ class PooledKVManager(BatchKVManager):
         st["d_slot"][:n].copy_(st["h_slot"][:n], non_blocking=True)
         view = ops.PageView(SINK, self.local, None, st["d_slot"][:n])
         self._step_table = (st["d_indices"], st["d_indptr"][:n + 1], st["d_last"][:n], view)
+        self._step_offsets_advanced = False
         self.kv_indices = st["d_indices"]
         self._host_len[:, idx] += 1
         self._active = slots
@@ -288,7 +290,11 @@ class PooledKVManager(BatchKVManager):
             v = new_value_cache.reshape(B, self.num_key_value_heads, self.head_dim).contiguous()
             ops.append_kv(k, v, self.kv_pages[layer_idx], self.summaries[layer_idx], indices, indptr, last,
                           status=self.status, view=view)
-            self.kv_offset[layer_idx][batch_idx] += 1
+            if not self._step_offsets_advanced:
+                # every layer appends one token in a prepared step: advance all layers' device lengths with
+                # the first append (three small launches per step instead of three per layer)
+                self._kv_offset_all[:, batch_idx] += 1
+                self._step_offsets_advanced = True
             return indptr, last, view
         slots = self._slots_of(batch_idx)
         lengths = [int(self._host_len[layer_idx][s]) + 1 for s in slots]
