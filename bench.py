@@ -817,34 +817,53 @@ def run_micro_select(args):
     if args.batch:
         wl["batch"] = args.batch
     cfg = kb.get_config(wl["model"])
-    tp, B, ctx, topk = wl["tp"], wl["batch"], wl["ctx"], wl["topk"]
+    B, topk = wl["batch"], wl["topk"]
+    tp = args.one_rank_of or wl.get("tp", 1)
     hkv, hq = cfg.num_key_value_heads // tp, cfg.num_attention_heads // tp
-    n = ctx // PAGE
     dev = torch.device("cuda", 0)
     torch.manual_seed(args.seed)
+    if "ragged" in wl:                                       # contexts uniform in [lo, hi], like the workload's
+        lo, hi = wl["ragged"]
+        scored = (torch.randint(lo, hi + 1, (B,), generator=torch.Generator().manual_seed(args.seed)) // PAGE).to(dev)
+    else:
+        scored = torch.full((B,), wl["ctx"] // PAGE, device=dev)
+    n = int(scored.max())
     dtype = torch.bfloat16
     summ = torch.randn(B, hkv, n + 32, HEAD_DIM, device=dev, dtype=dtype)
     q = torch.randn(B, hq, HEAD_DIM, device=dev, dtype=dtype)
-    table = (torch.arange(n + 1, dtype=torch.int32, device=dev)[None, :] * B
-             + torch.arange(B, dtype=torch.int32, device=dev)[:, None]).contiguous().view(-1)
-    indptr = torch.arange(B + 1, dtype=torch.int32, device=dev) * (n + 1)
+    indptr = torch.zeros(B + 1, dtype=torch.int32, device=dev)
+    indptr[1:] = torch.cumsum(scored + 1, 0)                 # the scored pages + the page being filled
+    total_pages = int(indptr[-1])
+    table = torch.arange(total_pages, dtype=torch.int32, device=dev)
     last = torch.ones(B, dtype=torch.int32, device=dev)
     out = torch.empty(B, hkv, topk + 1, dtype=torch.int32, device=dev)
     status = ops.new_status(dev)
-    run = lambda: ops.select_pages(q, summ, table, indptr, last, topk, B * (n + 1), out=out, status=status)
-    for _ in range(args.warmup):
-        run()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        run()
-    e1.record()
-    torch.cuda.synchronize()
-    ops.raise_on_status(status)
-    ms = e0.elapsed_time(e1) / args.steps
-    nbytes = B * hkv * n * HEAD_DIM * 2
-    emit({"micro": "select", "batch": B, "pages_scored": n, "topk": topk, "ms": ms,
+    # each launch timed by its own pair of events, with a write larger than L2 before it
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(view):
+        run = lambda: ops.select_pages(q, summ, table, indptr, last, topk, total_pages, out=out, status=status,
+                                       view=view)
+        for _ in range(args.warmup):
+            run()
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                 for _ in range(args.steps)]
+        for e0, e1 in pairs:
+            flush.zero_()
+            e0.record()
+            run()
+            e1.record()
+        torch.cuda.synchronize()
+        ops.raise_on_status(status)
+        return median([e0.elapsed_time(e1) for e0, e1 in pairs])
+
+    ms = timed(None)
+    # the same with the sequences handed to the CTAs from the longest to the shortest
+    order = torch.argsort(scored, descending=True, stable=True).to(torch.int32)
+    ms_ordered = timed(ops.PageView(0, 1, None, None, order))
+    nbytes = int(scored.sum()) * hkv * HEAD_DIM * 2
+    emit({"micro": "select", "batch": B, "kv_heads": hkv, "pages_scored_max": n, "topk": topk, "ms": ms,
+          "ms_with_seq_order": ms_ordered,
           "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / (ms * 1e-3) / 1e9})
 
 

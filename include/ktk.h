@@ -97,6 +97,10 @@ typedef struct ktk_shape {
  *                the start of its list in kv_indices (lists need not be packed), and kv_indptr
  *                needs B entries.
  *   slot_index   nullable int32[B]: row of `summaries` that belongs to sequence b (default b).
+ *   seq_order    nullable int32[B], read by ktk_select_v only: a permutation of 0..B-1, the sequences from the
+ *                longest to the shortest.  The persistent CTAs then take the sequences in that order, every other
+ *                round of CTAs in reverse, so that a ragged batch loads them evenly; results do not depend on it.
+ *                An entry outside [0, B) reports KTK_STATUS_BAD_TABLE and leaves that row at -1.
  * Selected-page rows then hold [sink page][<= topk picks][always-attended tail pages], at most
  * ktk_view_row_width(topk, view) entries.
  */
@@ -105,6 +109,7 @@ typedef struct ktk_view {
     int32_t local_tokens;
     const int32_t* page_count;
     const int32_t* slot_index;
+    const int32_t* seq_order;
 } ktk_view;
 
 /* Entries per (sequence, kv head) row of a selected-page table under `view` (topk + 1 for a null view). */

@@ -37,7 +37,7 @@ class Shape(ctypes.Structure):
 
 class View(ctypes.Structure):
     _fields_ = [("sink_tokens", c_int32), ("local_tokens", c_int32), ("page_count", c_void_p),
-                ("slot_index", c_void_p)]
+                ("slot_index", c_void_p), ("seq_order", c_void_p)]
 
 
 _i32p = c_void_p   # device pointers travel as integers

@@ -26,6 +26,7 @@ struct View {
     int local_tokens = 1;
     const int32_t* page_count = nullptr;
     const int32_t* slot_index = nullptr;
+    const int32_t* seq_order = nullptr;
 };
 inline View make_view(const ktk_view* v) {
     View r;
@@ -34,6 +35,7 @@ inline View make_view(const ktk_view* v) {
         r.local_tokens = v->local_tokens;
         r.page_count = v->page_count;
         r.slot_index = v->slot_index;
+        r.seq_order = v->seq_order;
     }
     return r;
 }

@@ -61,6 +61,7 @@ struct SelView {
     int sink_tokens, local_tokens, row_width;
     const int32_t* page_count;
     const int32_t* slot_index;
+    const int32_t* seq_order;
 };
 
 // What both the producer and the consumers derive for a work item (sequence b, kv head h).
@@ -91,7 +92,24 @@ __device__ __forceinline__ SelItem sel_item(int b, const int32_t* kv_indptr, con
     return it;
 }
 
-// Persistent kernel: CTA c handles the (sequence, kv head) items c, c + gridDim.x, ...
+// The item CTA `cta` handles in its round `round`, or -1 when that round has none for it.  Without an order: item
+// round * grid + cta.  With one (sequences sorted from the longest to the shortest) the rounds alternate in
+// direction, so that the CTA that got the longest sequences of one round gets the shortest of the next, and the
+// item is (seq_order[rank / Hkv], rank % Hkv); -2 for an entry that is no sequence of the batch.
+__device__ __forceinline__ int64_t sel_item_of(int64_t round, int64_t n_items, int Hkv, const int32_t* seq_order) {
+    const int64_t grid = gridDim.x, cta = blockIdx.x;
+    if (seq_order == nullptr) {
+        const int64_t bh = round * grid + cta;
+        return bh < n_items ? bh : -1;
+    }
+    const int64_t rank = round * grid + ((round & 1) ? grid - 1 - cta : cta);
+    if (rank >= n_items) return -1;
+    const int64_t b = seq_order[rank / Hkv];
+    if (b < 0 || b >= n_items / Hkv) return -2;
+    return b * Hkv + rank % Hkv;
+}
+
+// Persistent kernel: CTA c handles the (sequence, kv head) items c, c + gridDim.x, ... (see sel_item_of)
 // A producer warp streams the summaries of its items, one after the other without a gap,
 // through a ring of shared-memory stages with bulk asynchronous copies (the rows of one item
 // are contiguous); stage i of the stream is scored by consumer warp i mod 8, sixteen lanes per
@@ -143,7 +161,10 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
         if (lane == 0) {
             int i = 0;           // stages issued so far, over all items of this CTA
             bool alive = true;
-            for (int64_t bh = blockIdx.x; bh < n_items && alive; bh += gridDim.x) {
+            const int64_t rounds = (n_items + gridDim.x - 1) / gridDim.x;
+            for (int64_t round = 0; round < rounds && alive; ++round) {
+                const int64_t bh = sel_item_of(round, n_items, Hkv, view.seq_order);
+                if (bh < 0) continue;
                 const int b = (int)(bh / Hkv);
                 const int h = (int)(bh % Hkv);
                 const SelItem it = sel_item<kRowsPerStage>(b, kv_indptr, kv_last_page_len, view, summary_stride,
@@ -167,7 +188,13 @@ select_kernel(const T* __restrict__ q, const T* __restrict__ summaries, int64_t 
     } else {
         // ---------------- consumer warps ----------------
         int ibase = 0;           // stream position of the current item's first stage
-        for (int64_t bh = blockIdx.x; bh < n_items; bh += gridDim.x) {
+        const int64_t rounds = (n_items + gridDim.x - 1) / gridDim.x;
+        for (int64_t round = 0; round < rounds; ++round) {
+            const int64_t bh = sel_item_of(round, n_items, Hkv, view.seq_order);
+            if (bh < 0) {
+                if (bh == -2 && tid == 0) report(status, KTK_STATUS_BAD_TABLE);
+                continue;
+            }
             const int b = (int)(bh / Hkv), h = (int)(bh % Hkv);
             int32_t* row_pages = out_pages + bh * stride_out;
             int32_t* row_logical = out_logical ? out_logical + bh * stride_out : nullptr;
@@ -536,7 +563,7 @@ extern "C" int ktk_select_v(const void* q, const void* summaries, int64_t summar
     }
     SelView sv;
     sv.sink_tokens = v.sink_tokens; sv.local_tokens = v.local_tokens; sv.row_width = row_width;
-    sv.page_count = v.page_count; sv.slot_index = v.slot_index;
+    sv.page_count = v.page_count; sv.slot_index = v.slot_index; sv.seq_order = v.seq_order;
     cudaStream_t st = (cudaStream_t)stream;
     if (shape->dtype == KTK_F32)
         return select_group<float>(shape->group_size, q, summaries, summary_stride, kv_indices,

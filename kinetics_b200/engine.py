@@ -186,8 +186,8 @@ class PooledKVManager(BatchKVManager):
             mk = lambda k: torch.empty(k, dtype=torch.int32)
             self._static = dict(
                 h_indices=mk(cap).pin_memory(), h_indptr=mk(n + 1).pin_memory(), h_last=mk(n).pin_memory(),
-                h_slot=mk(n).pin_memory(), d_indices=mk(cap).to(dev), d_indptr=mk(n + 1).to(dev),
-                d_last=mk(n).to(dev), d_slot=mk(n).to(dev))
+                h_slot=mk(n).pin_memory(), h_order=mk(n).pin_memory(), d_indices=mk(cap).to(dev),
+                d_indptr=mk(n + 1).to(dev), d_last=mk(n).to(dev), d_slot=mk(n).to(dev), d_order=mk(n).to(dev))
         return self._static
 
     def prepare_step(self, slots: Sequence[int]) -> None:
@@ -207,17 +207,20 @@ class PooledKVManager(BatchKVManager):
         total = self.pool.export_into(slots, st["h_indices"], st["h_indptr"], st["h_last"])
         st["h_last"].numpy()[:n] = np.where(lengths <= SINK, lengths, (lengths - SINK - 1) % PAGE + 1)
         st["h_slot"].numpy()[:n] = idx
+        # rows of the batch from the longest to the shortest: the selection kernel's CTAs share them evenly
+        st["h_order"].numpy()[:n] = np.argsort(-lengths, kind="stable")
         st["d_indices"][:total].copy_(st["h_indices"][:total], non_blocking=True)
         st["d_indptr"][:n + 1].copy_(st["h_indptr"][:n + 1], non_blocking=True)
         st["d_last"][:n].copy_(st["h_last"][:n], non_blocking=True)
         st["d_slot"][:n].copy_(st["h_slot"][:n], non_blocking=True)
-        view = ops.PageView(SINK, self.local, None, st["d_slot"][:n])
+        st["d_order"][:n].copy_(st["h_order"][:n], non_blocking=True)
+        view = ops.PageView(SINK, self.local, None, st["d_slot"][:n], st["d_order"][:n])
         self._step_table = (st["d_indices"], st["d_indptr"][:n + 1], st["d_last"][:n], view)
         self._step_offsets_advanced = False
         self.kv_indices = st["d_indices"]
         self._host_len[:, idx] += 1
         self._active = slots
-        self.table_bytes = 4 * (total + 3 * n + 1)
+        self.table_bytes = 4 * (total + 4 * n + 1)
         # pages the step opened (a promise made at admission may already have reserved them)
         self.pages_opened = int(np.count_nonzero((lengths - SINK - 1) % PAGE == 0)) if n else 0
 

@@ -87,17 +87,22 @@ class PageView:
     over a page table whose logical page 0 holds the 4 sink tokens.
     """
 
-    def __init__(self, sink_tokens: int = 0, local_tokens: int = 1, page_count=None, slot_index=None):
+    def __init__(self, sink_tokens: int = 0, local_tokens: int = 1, page_count=None, slot_index=None,
+                 seq_order=None):
         self.sink_tokens, self.local_tokens = int(sink_tokens), int(local_tokens)
         self.page_count, self.slot_index = page_count, slot_index
-        for t in (page_count, slot_index):
+        # selection only: the sequences from the longest to the shortest (a permutation of 0..B-1); the
+        # persistent CTAs of the selection kernel then share a ragged batch evenly
+        self.seq_order = seq_order
+        for t in (page_count, slot_index, seq_order):
             if t is not None and (t.dtype != torch.int32 or not t.is_cuda or not t.is_contiguous()):
-                raise ValueError("PageView: page_count / slot_index must be contiguous int32 CUDA tensors")
+                raise ValueError("PageView: page_count / slot_index / seq_order must be contiguous int32 CUDA tensors")
 
     def c(self):
         return _lib.View(self.sink_tokens, self.local_tokens,
                          0 if self.page_count is None else self.page_count.data_ptr(),
-                         0 if self.slot_index is None else self.slot_index.data_ptr())
+                         0 if self.slot_index is None else self.slot_index.data_ptr(),
+                         0 if self.seq_order is None else self.seq_order.data_ptr())
 
     def row_width(self, topk: int) -> int:
         v = self.c()

@@ -92,7 +92,7 @@ def test_append_ragged_and_empty(cuda_device):
 
 # ---------------------------------------------------------------- selection
 
-def _select_both(ops, q, st, topk, device):
+def _select_both(ops, q, st, topk, device, view=None):
     summ = oracle.summaries(st["kv_cache"], st["kv_indices"], st["kv_indptr"], st["kv_last_page_len"],
                             st["summary_stride"])
     sc = oracle.scores(q, summ, st["kv_indptr"])
@@ -106,7 +106,7 @@ def _select_both(ops, q, st, topk, device):
     out_l = torch.empty(B, Hkv, topk + 1, dtype=torch.int32, device=device)
     out_s = torch.full((B, Hkv, st["summary_stride"]), float("nan"), device=device)
     out_p = ops.select_pages(q.to(device), summ_g, d["kv_indices"], d["kv_indptr"], d["kv_last_page_len"], topk,
-                             st["num_pages"], out_logical=out_l, out_scores=out_s, status=status)
+                             st["num_pages"], out_logical=out_l, out_scores=out_s, status=status, view=view)
     ops.raise_on_status(status)
     return (phys, logical, sc), (out_p.cpu(), out_l.cpu(), out_s.cpu()), d, summ_g
 
@@ -144,6 +144,44 @@ def test_select_bit_exact_random(cuda_device, dtype, G, Hkv, topk, lens):
     (phys, logical, sc), (gp, gl, gs), _, _ = _select_both(ops, q, st, topk, cuda_device)
     assert torch.equal(gl, logical)
     assert torch.equal(gp, phys)
+
+
+@pytest.mark.parametrize("order", [None, "longest_first", "shuffled"])
+def test_select_many_ragged_items_per_cta(cuda_device, order):
+    """More (sequence, kv head) items than resident CTAs: every CTA streams several items of different lengths
+    back to back through its ring (the stage <-> warp assignment carries over from item to item), some of them
+    empty or shorter than the budget.  With a sequence order in the view the CTAs take the sequences in that
+    order, every other round reversed; the rows written must not depend on it."""
+    ops = _ops()
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(77)
+    lens = torch.randint(17, 3000, (470,), generator=g).tolist()
+    lens[5], lens[6], lens[100], lens[469] = 1, 16, 0, 16 * 24 + 1
+    q, k, v = random_case(12, len(lens), 2, 2, lens, dtype)
+    st = paged_state(k, v, lens, dtype, seed=21)
+    view = None
+    if order is not None:
+        perm = torch.argsort(torch.tensor(lens), descending=True, stable=True) if order == "longest_first" \
+            else torch.randperm(len(lens), generator=g)
+        view = ops.PageView(0, 1, None, None, perm.to(torch.int32).to(cuda_device))
+    (phys, logical, sc), (gp, gl, gs), _, _ = _select_both(ops, q, st, 24, cuda_device, view=view)
+    assert torch.equal(gl, logical)
+    assert torch.equal(gp, phys)
+
+
+def test_select_reports_an_order_entry_that_is_no_sequence(cuda_device):
+    ops = _ops()
+    lens = [100, 200, 300]
+    q, k, v = random_case(3, 3, 1, 2, lens, torch.bfloat16)
+    st = to_dev(paged_state(k, v, lens, torch.bfloat16, seed=2), cuda_device)
+    summ = torch.zeros(3, 1, st["summary_stride"], 128, device=cuda_device, dtype=torch.bfloat16)
+    status = ops.new_status(cuda_device)
+    ops.build_summaries(st["kv_cache"], summ, st["kv_indices"], st["kv_indptr"], st["kv_last_page_len"], status=status)
+    view = ops.PageView(0, 1, None, None, torch.tensor([2, 7, 0], dtype=torch.int32, device=cuda_device))
+    ops.select_pages(q.to(cuda_device), summ, st["kv_indices"], st["kv_indptr"], st["kv_last_page_len"], 4,
+                     st["num_pages"], status=status, view=view)
+    with pytest.raises(RuntimeError):
+        ops.raise_on_status(status)
 
 
 def test_select_ties_go_to_lowest_page(cuda_device):
