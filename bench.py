@@ -968,6 +968,7 @@ def run_full_model(args):
         for _ in range(max(1, args.reps)):
             e0.record()
             for _ in range(args.steps):
+                eng.kv.wait_for_table_copies()               # (the device has started the previous step)
                 t0 = time.perf_counter()
                 eng.kv.prepare_step(slots)                   # (timed apart: the host share of a step)
                 host_ms.append((time.perf_counter() - t0) * 1e3)

@@ -381,6 +381,13 @@ KTK_API int ktk_rank_barrier(const void* flag_ptrs, void* launch_count, int32_t 
  */
 KTK_API int ktk_silu_mul(const void* gate, const void* up, void* out, int64_t n, int32_t dtype,
                  void* stream);
+/*
+ * The same over [rows, cols] operands whose rows lie in_row_stride elements apart -- the two halves of ONE GEMM
+ * output [rows, 2 * cols] when gate_proj and up_proj (benchmark/blocktopk_decoder.py:235, LiteSys qwen3.py:81-83)
+ * are multiplied as one stacked weight.  `out` is contiguous [rows, cols]; cols a multiple of 8, rows 16-byte aligned.
+ */
+KTK_API int ktk_silu_mul_rows(const void* gate, const void* up, void* out, int64_t rows, int64_t cols,
+                              int64_t in_row_stride, int32_t dtype, void* stream);
 
 /*
  * The same four operations under a ktk_view (null view = the plain entry points above).

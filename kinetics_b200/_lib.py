@@ -118,6 +118,7 @@ _SIGNATURES = {
     "ktk_pool_release": (c_int32, [c_void_p, c_int32]),
     "ktk_pool_export": (c_int64, [c_void_p, c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_void_p]),
     "ktk_silu_mul": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
+    "ktk_silu_mul_rows": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int32, c_void_p]),
 }
 
 #: every symbol include/ktk.h declares

@@ -6,6 +6,8 @@
 namespace ktk {
 
 int silu_mul_vectorised(const void* gate, const void* up, void* out, int64_t n, int dtype, cudaStream_t st);
+int silu_mul_rows(const void* gate, const void* up, void* out, int64_t rows, int64_t cols, int64_t in_stride, int dtype,
+                  cudaStream_t st);
 
 // One CTA per (sequence, kv head), one thread per head-dim element.
 // Writes the new key/value at (last page, last slot) and rewrites that page's
@@ -392,6 +394,24 @@ extern "C" int ktk_rmsnorm(const void* x, const void* w, float eps, void* out, i
     }
     KTK_CUDA_TRY(cudaGetLastError(), "ktk_rmsnorm");
     return KTK_OK;
+}
+
+extern "C" int ktk_silu_mul_rows(const void* gate, const void* up, void* out, int64_t rows, int64_t cols,
+                                 int64_t in_row_stride, int32_t dtype, void* stream) {
+    const int64_t esz = dtype == KTK_F32 ? 4 : 2;
+    if (rows < 0 || cols < 0 || in_row_stride < cols || (dtype != KTK_F32 && dtype != KTK_BF16)) {
+        set_error("ktk_silu_mul_rows: bad arguments rows=%lld cols=%lld stride=%lld dtype=%d", (long long)rows,
+                  (long long)cols, (long long)in_row_stride, dtype);
+        return KTK_ERR_ARG;
+    }
+    if (rows == 0 || cols == 0) return KTK_OK;
+    if (!gate || !up || !out) { set_error("ktk_silu_mul_rows: null pointer argument"); return KTK_ERR_ARG; }
+    if (cols % 8 != 0 || (in_row_stride * esz) % 16 != 0 ||
+        ((((uintptr_t)gate | (uintptr_t)up | (uintptr_t)out) & 15u) != 0)) {
+        set_error("ktk_silu_mul_rows: cols must be a multiple of 8 and rows 16-byte aligned");
+        return KTK_ERR_ARG;
+    }
+    return silu_mul_rows(gate, up, out, rows, cols, in_row_stride, dtype, (cudaStream_t)stream);
 }
 
 extern "C" int ktk_silu_mul(const void* gate, const void* up, void* out, int64_t n, int32_t dtype,

@@ -154,6 +154,25 @@ silu_mul_vec_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __r
     }
 }
 
+// the same over [rows, cols] operands whose rows lie `in_stride` elements apart (the two halves of one GEMM
+// output [rows, 2 * cols]); `out` is contiguous
+template <typename T>
+__global__ void __launch_bounds__(256)
+silu_mul_rows_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out, int64_t rows,
+                     int64_t vec_per_row, int64_t in_stride) {
+    const int64_t nvec = rows * vec_per_row;
+    const int64_t stride = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < nvec; i += stride) {
+        const int64_t r = i / vec_per_row, c = (i - r * vec_per_row) * 8;
+        float g[8], u[8], o[8];
+        Vec8<T>::load(gate + r * in_stride + c, g);
+        Vec8<T>::load(up + r * in_stride + c, u);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = g[e] / (1.0f + __expf(-g[e])) * u[e];
+        Vec8<T>::store(out + i * 8, o);
+    }
+}
+
 template <typename T>
 static int add_rmsnorm_launch(const void* x, const void* residual, const void* w, float eps, void* out_sum,
                               void* out_norm, int64_t rows, int cols, cudaStream_t st) {
@@ -187,6 +206,25 @@ static int silu_vec_launch(const void* gate, const void* up, void* out, int64_t 
     silu_mul_vec_kernel<T><<<(unsigned)blocks, 256, 0, st>>>((const T*)gate, (const T*)up, (T*)out, nvec);
     KTK_CUDA_TRY(cudaGetLastError(), "ktk_silu_mul");
     return KTK_OK;
+}
+
+template <typename T>
+static int silu_rows_launch(const void* gate, const void* up, void* out, int64_t rows, int64_t cols, int64_t in_stride,
+                            cudaStream_t st) {
+    const int64_t nvec = rows * (cols / 8);
+    int64_t blocks = (nvec + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    silu_mul_rows_kernel<T><<<(unsigned)blocks, 256, 0, st>>>((const T*)gate, (const T*)up, (T*)out, rows, cols / 8,
+                                                               in_stride);
+    KTK_CUDA_TRY(cudaGetLastError(), "ktk_silu_mul_rows");
+    return KTK_OK;
+}
+
+int silu_mul_rows(const void* gate, const void* up, void* out, int64_t rows, int64_t cols, int64_t in_stride, int dtype,
+                  cudaStream_t st) {
+    return dtype == KTK_F32 ? silu_rows_launch<float>(gate, up, out, rows, cols, in_stride, st)
+                            : silu_rows_launch<__nv_bfloat16>(gate, up, out, rows, cols, in_stride, st);
 }
 
 // used by ktk_silu_mul when the length and the pointers allow 16-byte accesses

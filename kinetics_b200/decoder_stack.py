@@ -55,8 +55,9 @@ class DecoderStack:
                 wqkv, _ = tp.shard_wqkv(wqkv, None, Hq, Hkv, D, self.rank, self.world)
                 wo = tp.shard_wo(wo, Hq, D, self.rank, self.world)
                 up, gate, down = tp.shard_mlp(up, gate, down, self.rank, self.world)
+            # gate_proj and up_proj as one stacked weight: one GEMM, whose halves the activation kernel reads
             self.layers.append(dict(
-                wqkv=wqkv, wo=wo, up=up, gate=gate, down=down,
+                wqkv=wqkv, wo=wo, gate_up=torch.cat((gate, up), dim=0).contiguous(), down=down,
                 qnorm=torch.ones(D, device=self.device, dtype=dtype), knorm=torch.ones(D, device=self.device, dtype=dtype),
                 input_norm=torch.ones(H, device=self.device, dtype=dtype),
                 post_norm=torch.ones(H, device=self.device, dtype=dtype)))
@@ -103,7 +104,9 @@ class DecoderStack:
                                         shape(v, self.num_kv_heads), i, batch_idx)
             attn = attn.reshape(rows, self.num_heads * self.head_dim)
             x, n = self._reduce_add_norm(self.ex_o, attn, L["wo"].t(), x, L["post_norm"])
-            act = ops.silu_mul(torch.mm(n, L["gate"].t()), torch.mm(n, L["up"].t()))
+            gu = torch.mm(n, L["gate_up"].t())
+            half = gu.shape[1] // 2
+            act = ops.silu_mul(gu[:, :half], gu[:, half:])
             nxt = self.layers[i + 1]["input_norm"] if i + 1 < self.num_layers else self.norm_weight
             x, n = self._reduce_add_norm(self.ex_d, act, L["down"].t(), x, nxt)
         # n is the final RMSNorm of the residual stream (qwen3.py:139)

@@ -157,6 +157,7 @@ class PooledKVManager(BatchKVManager):
         self._table_val = None
         self._step_table = None          # set by prepare_step: the table every layer of the step uses
         self._step_offsets_advanced = False
+        self._copies_done = None         # event behind the last step's table copies
         self._static = None              # static device buffers + pinned mirrors of that table
 
     # ---- admission / retirement
@@ -190,6 +191,13 @@ class PooledKVManager(BatchKVManager):
                 d_indptr=mk(n + 1).to(dev), d_last=mk(n).to(dev), d_slot=mk(n).to(dev), d_order=mk(n).to(dev))
         return self._static
 
+    def wait_for_table_copies(self) -> None:
+        """The previous step's table copies read the pinned buffers when the stream reaches them: a host that
+        runs ahead of the device must not overwrite them before that (the wait ends when the device has started
+        the previous step, so host and device still overlap by one step)."""
+        if self._copies_done is not None:
+            self._copies_done.synchronize()
+
     def prepare_step(self, slots: Sequence[int]) -> None:
         """All the host work of one decode step over `slots` (every layer appends one token): the pool grows
         where a sequence crosses a page boundary, the CSR table goes into pinned memory and from there, with
@@ -198,6 +206,7 @@ class PooledKVManager(BatchKVManager):
         slots = list(slots)
         n = len(slots)
         st = self._static_buffers()
+        self.wait_for_table_copies()
         idx = np.asarray(slots, dtype=np.int64)
         lengths = self._host_len[0, idx] + 1
         pool_tokens = lambda ln: np.where(ln > 0, PAGE + np.maximum(ln - SINK, 0), 0)
@@ -214,6 +223,9 @@ class PooledKVManager(BatchKVManager):
         st["d_last"][:n].copy_(st["h_last"][:n], non_blocking=True)
         st["d_slot"][:n].copy_(st["h_slot"][:n], non_blocking=True)
         st["d_order"][:n].copy_(st["h_order"][:n], non_blocking=True)
+        if self._copies_done is None:
+            self._copies_done = torch.cuda.Event()
+        self._copies_done.record()
         view = ops.PageView(SINK, self.local, None, st["d_slot"][:n], st["d_order"][:n])
         self._step_table = (st["d_indices"], st["d_indptr"][:n + 1], st["d_last"][:n], view)
         self._step_offsets_advanced = False

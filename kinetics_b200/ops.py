@@ -470,9 +470,19 @@ def qkv_norm(proj: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor, eps: float,
 
 def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """silu(gate) * up (benchmark/blocktopk_decoder.py:235-236)."""
-    _cuda(gate, up)
     if gate.shape != up.shape or gate.dtype != up.dtype:
         raise ValueError("silu_mul: gate and up must match")
+    if (gate.dim() == 2 and not gate.is_contiguous() and gate.stride(1) == 1 and up.stride(1) == 1
+            and gate.stride(0) == up.stride(0)):
+        # the two halves of one stacked gate/up GEMM output: rows a fixed stride apart
+        if not (gate.is_cuda and up.is_cuda):
+            raise ValueError("silu_mul: CUDA tensors")
+        out = torch.empty(gate.shape, device=gate.device, dtype=gate.dtype)
+        check(_lib.load().ktk_silu_mul_rows(_ptr(gate), _ptr(up), _ptr(out), gate.shape[0], gate.shape[1],
+                                            gate.stride(0), _dtype_code(gate), _stream()))
+        _launched()
+        return out
+    _cuda(gate, up)
     out = torch.empty_like(gate)
     check(_lib.load().ktk_silu_mul(_ptr(gate), _ptr(up), _ptr(out), gate.numel(), _dtype_code(gate), _stream()))
     _launched()

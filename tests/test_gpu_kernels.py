@@ -479,6 +479,18 @@ def test_silu_mul(cuda_device, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul_on_the_halves_of_one_gemm_output(cuda_device, dtype):
+    """gate and up as the two halves of a [rows, 2 * cols] tensor give the bits of the contiguous call."""
+    ops = _ops()
+    torch.manual_seed(3)
+    gu = torch.randn(37, 2 * 768).to(dtype).to(cuda_device)
+    g, u = gu[:, :768], gu[:, 768:]
+    out = ops.silu_mul(g, u)
+    ref = ops.silu_mul(g.contiguous(), u.contiguous())
+    assert out.is_contiguous() and torch.equal(_bits(out.cpu()), _bits(ref.cpu()))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("cols", [512, 4096, 5120])
 def test_add_rmsnorm(cuda_device, dtype, cols):
     ops = _ops()
