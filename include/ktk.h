@@ -65,6 +65,7 @@ extern "C" {
 #define KTK_VARIANT_AUTO 0
 #define KTK_VARIANT_SIMT 1       /* fp32 FMA path (the only one for KTK_F32)     */
 #define KTK_VARIANT_MMA 2        /* bf16 tensor-core path with TMA-staged pages  */
+#define KTK_VARIANT_UMMA 3       /* prefill only: bf16 on tcgen05 with accumulators in tensor memory */
 
 /* num_splits value: cut the concatenated page lists evenly over one CTA per resident slot
  * (bf16 tensor-core path only); see ktk_decode_num_splits */

@@ -12,7 +12,7 @@ _PKG = Path(__file__).resolve().parent
 LIB_PATH = _PKG / "libktk.so"
 
 KTK_F32, KTK_BF16 = 0, 1
-VARIANT_AUTO, VARIANT_SIMT, VARIANT_MMA = 0, 1, 2
+VARIANT_AUTO, VARIANT_SIMT, VARIANT_MMA, VARIANT_UMMA = 0, 1, 2, 3
 ALLREDUCE_AUTO, ALLREDUCE_MULTICAST, ALLREDUCE_PEER = 0, 1, 2
 EXCHANGE_ALLREDUCE_NORM, EXCHANGE_ALLREDUCE, EXCHANGE_SCATTER = 0, 1, 2
 KTK_OK, KTK_ERR_ARG, KTK_ERR_UNSUPPORTED, KTK_ERR_WORKSPACE, KTK_ERR_CUDA, KTK_ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5

@@ -19,6 +19,7 @@
 // page count and fill level (`prefill_rows_kernel` writes those three ints per row), which runs the fp32
 // FMA decode kernel over the same page list.
 #include "ktk_decode_mma.cuh"
+#include "ktk_prefill_umma.cuh"
 
 namespace ktk {
 
@@ -269,13 +270,14 @@ extern "C" int ktk_prefill_attention(const void* q, const int32_t* q_indptr, int
         set_error("%s: null pointer or negative size", who);
         return KTK_ERR_ARG;
     }
-    if (variant != KTK_VARIANT_AUTO && variant != KTK_VARIANT_SIMT && variant != KTK_VARIANT_MMA) {
+    if (variant != KTK_VARIANT_AUTO && variant != KTK_VARIANT_SIMT && variant != KTK_VARIANT_MMA &&
+        variant != KTK_VARIANT_UMMA) {
         set_error("%s: unknown variant %d", who, variant);
         return KTK_ERR_ARG;
     }
     const int G = s->group_size;
     const bool mma_ok = s->dtype == KTK_BF16 && (G == 1 || G == 2 || G == 4 || G == 8);
-    if (variant == KTK_VARIANT_MMA && !mma_ok) {
+    if ((variant == KTK_VARIANT_MMA || variant == KTK_VARIANT_UMMA) && !mma_ok) {
         set_error("%s: the tensor-core variant needs bf16 and a group size of 1, 2, 4 or 8", who);
         return KTK_ERR_UNSUPPORTED;
     }
@@ -285,6 +287,14 @@ extern "C" int ktk_prefill_attention(const void* q, const int32_t* q_indptr, int
         if (s->batch > 65535 || s->num_kv_heads > 65535) {
             set_error("%s: more than 65535 sequences or kv heads in one launch", who);
             return KTK_ERR_TOO_LARGE;
+        }
+        if (variant == KTK_VARIANT_UMMA) {
+            PrefillUmmaParams u;
+            u.q = q; u.o = o; u.cache = kv_cache; u.q_indptr = q_indptr; u.kv_indices = kv_indices;
+            u.kv_indptr = kv_indptr; u.kv_last_page_len = kv_last_page_len; u.page_count = view.page_count;
+            u.sink_tokens = view.sink_tokens; u.batch = s->batch; u.Hkv = s->num_kv_heads; u.G = G;
+            u.num_pages = s->num_pages; u.scale_log2 = sm_scale * kLog2e; u.status = status;
+            return launch_prefill_umma(u, max_new_tokens, st);
         }
         PrefillParams p;
         p.q = q; p.o = o; p.q_indptr = q_indptr; p.kv_indices = kv_indices; p.kv_indptr = kv_indptr;

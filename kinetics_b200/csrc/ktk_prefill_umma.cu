@@ -1,0 +1,345 @@
+// Causal prefill attention over the paged KV cache on the fifth-generation tensor cores (tcgen05, accumulators
+// in tensor memory).  Same contract as prefill_mma_kernel (ktk_prefill.cu); replaces
+// flashinfer.single_prefill_with_kv_cache of LiteSys/litesys/attention/batch_cache.py:129-145.
+//
+// One CTA per (sequence, kv head, tile of 128 / G new tokens): the 128 rows of the tile are the (token, head of
+// the query group) pairs, row r = thread r = lane r of tensor memory.  The history is walked in blocks of 64 keys
+// (four pages).  Per block:
+//     all threads   K and V of the four pages -> shared memory, 16-byte cp.async into the 128-byte swizzle
+//                   pattern the tensor cores read (rows past a page's fill level are zero-filled)
+//     one thread    S[128 x 64]   = Q[128 x 128] . K^T      8 x tcgen05.mma (M 128, N 64, K 16), D in TMEM
+//     thread r      row r of S <- tcgen05.ld; scale, causal mask, running max and sum, P = exp2(S - max) as bf16
+//                   into shared memory (swizzled, K-major); O row in TMEM rescaled when the max moved
+//     one thread    O[128 x 128] += P[128 x 64] . V[64 x 128]   4 x tcgen05.mma (M 128, N 128, K 16), V read
+//                   MN-major: exactly the rows the pages hold
+// and at the end row r of O is read back, divided by the row sum and stored.  The phases of one CTA run one after
+// the other; two CTAs per SM (80 KiB of shared memory and 256 TMEM columns each) overlap one another's phases.
+// Every wait is bounded; tensor memory is released on every path.
+#include "ktk_decode.cuh"
+#include "ktk_pipeline.cuh"
+#include "ktk_prefill_umma.cuh"
+
+namespace ktk {
+
+constexpr int kUmRows = 128;                 // rows of a tile = threads of a CTA
+constexpr int kUmKeys = 64;                  // keys per block
+constexpr int kUmPagesPerBlock = kUmKeys / kPageSize;
+constexpr int kUmTmemCols = 256;             // S: columns [0, 64), O: columns [64, 192)
+constexpr int kUmColS = 0, kUmColO = 64;
+constexpr int kUmQBytes = 2 * kUmRows * 128; // two tiles of [128 rows][64 dims]
+constexpr int kUmKBytes = 2 * kUmKeys * 128; // two tiles of [64 keys][64 dims]
+constexpr int kUmPBytes = kUmRows * 128;     // [128 rows][64 keys]
+constexpr int kUmSmem = kUmQBytes + 2 * kUmKBytes + kUmPBytes + 1024;
+
+// ---- tcgen05 wrappers -------------------------------------------------------------------------------------
+// shared-memory operand descriptor: start address, leading / stride byte offsets (all >> 4), version 1,
+// 128-byte swizzle
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// instruction descriptor of kind::f16: fp32 accumulate, bf16 A and B, A K-major, M = 128
+__device__ __forceinline__ uint32_t umma_idesc(int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(kUmRows >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// 32 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+          "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+          "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+          "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])),
+          "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
+          "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+          "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
+          "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// byte offset of the 16-byte chunk `chunk` (0..7) of row `row` in a [rows][128 B] tile under the 128-byte swizzle
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+    return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+__global__ void __launch_bounds__(kUmRows, 2)
+prefill_umma_kernel(const PrefillUmmaParams p) {
+    extern __shared__ uint8_t um_raw[];
+    __shared__ __align__(8) uint64_t bar_s, bar_o;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int kpos[kUmKeys];                 // position of the key in row c of the block (INT_MAX: none)
+    __shared__ int abort_flag;
+
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(um_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sQ = sm;
+    uint8_t* sK = sQ + kUmQBytes;
+    uint8_t* sV = sK + kUmKBytes;
+    uint8_t* sP = sV + kUmKBytes;
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int G = p.G, Hq = p.Hkv * G;
+    const int tpc = kUmRows / G;                    // new tokens per CTA
+    const int q0 = p.q_indptr[b];
+    const int n_new = p.q_indptr[b + 1] - q0;
+    const int tok0 = blockIdx.x * tpc;
+    if (tok0 >= n_new) return;                      // uniform for the CTA: nothing allocated yet
+
+    const SeqPages sp = seq_pages(p.kv_indptr, p.page_count, p.kv_last_page_len, p.sink_tokens, b);
+    const int base_pos = sp.total - n_new;          // position of the sequence's first new token
+    if (sp.bad || base_pos < 0) {
+        if (tid == 0) report(p.status, KTK_STATUS_BAD_TABLE);
+        return;
+    }
+    const int tok_hi = (tok0 + tpc < n_new ? tok0 + tpc : n_new) - 1;
+    int n_need, last_unused;
+    pages_for(base_pos + tok_hi + 1, sp.first_fill, n_need, last_unused);
+    if (n_need > sp.n_pages) n_need = sp.n_pages;
+    const int n_blocks = (n_need + kUmPagesPerBlock - 1) / kUmPagesPerBlock;
+
+    // this thread's row
+    const int my_tok = tok0 + tid / G, my_head = h * G + tid % G;
+    const bool row_on = my_tok < n_new;
+    const int vis = row_on ? base_pos + my_tok + 1 : 0;     // keys at positions < vis are seen
+
+    if (tid == 0) {
+        mbar_init(&bar_s, 1);
+        mbar_init(&bar_o, 1);
+        abort_flag = 0;
+        mbar_init_fence();
+    }
+    // Q row -> two swizzled tiles (zeros for rows past the last new token)
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(
+            (const __nv_bfloat16*)p.q + ((int64_t)(q0 + (row_on ? my_tok : 0)) * Hq + my_head) * kHeadDim);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            const uint4 v = row_on ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(sQ + (c >> 3) * (kUmRows * 128) + swz(tid, c & 7)) = v;
+        }
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_s)), "r"(kUmTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_base_s;
+    const uint32_t my_tmem = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 lanes
+
+    const uint32_t idesc_s = umma_idesc(kUmKeys, false);
+    const uint32_t idesc_o = umma_idesc(kHeadDim, true);
+    float m_run = -INFINITY, l_run = 0.0f;
+    const __nv_bfloat16* cache = (const __nv_bfloat16*)p.cache;
+    const int64_t tok_stride = (int64_t)p.Hkv * kHeadDim;            // elements between the tokens of a page
+    bool alive = true;
+
+    for (int blk = 0; blk < n_blocks; ++blk) {
+        // ---- K and V of the block's pages -> shared memory ----
+        if (tid < kUmKeys) {
+            const int e = blk * kUmPagesPerBlock + (tid >> 4), slot = tid & 15;
+            int pos = 0x7fffffff;
+            if (e < n_need) {
+                const int ntok = (e == sp.n_pages - 1) ? sp.last_fill : (e == 0 ? sp.first_fill : kPageSize);
+                if (slot < ntok) pos = page_first_pos(e, sp.first_fill) + slot;
+            }
+            kpos[tid] = pos;
+        }
+        for (int i = tid; i < kUmKeys * 16; i += kUmRows) {
+            const int row = i >> 4, c = i & 15;
+            const int e = blk * kUmPagesPerBlock + (row >> 4), slot = row & 15;
+            bool live = false;
+            int64_t page = 0;
+            if (e < n_need) {
+                const int ntok = (e == sp.n_pages - 1) ? sp.last_fill : (e == 0 ? sp.first_fill : kPageSize);
+                page = p.kv_indices[sp.start + e];
+                if (page < 0 || page >= p.num_pages) {
+                    if (c == 0 && slot == 0) report(p.status, KTK_STATUS_BAD_PAGE);
+                } else {
+                    live = slot < ntok;
+                }
+            }
+            const uint32_t off = (uint32_t)((c >> 3) * (kUmKeys * 128)) + swz(row, c & 7);
+            if (live) {
+                const __nv_bfloat16* src = cache + ((page * 2) * kPageSize + slot) * tok_stride + (int64_t)h * kHeadDim + c * 8;
+                cp_async16(smem_u32(sK + off), src);
+                cp_async16(smem_u32(sV + off), src + (int64_t)kPageSize * tok_stride);
+            } else {
+                *reinterpret_cast<uint4*>(sK + off) = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(sV + off) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        cp_async_wait_all();
+        fence_proxy_async();
+        __syncthreads();
+
+        // ---- S = Q . K^T ----
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int s = 0; s < kHeadDim / 16; ++s) {
+                const uint64_t a = umma_desc(smem_u32(sQ) + (s >> 2) * (kUmRows * 128) + (s & 3) * 32, 0, 1024);
+                const uint64_t bd = umma_desc(smem_u32(sK) + (s >> 2) * (kUmKeys * 128) + (s & 3) * 32, 0, 1024);
+                umma_f16(tmem + kUmColS, a, bd, idesc_s, s > 0 ? 1u : 0u);
+            }
+            umma_commit(&bar_s);
+        }
+        if (!mbar_wait(&bar_s, blk & 1, &abort_flag)) alive = false;
+        if (!__syncthreads_and(alive)) { alive = false; break; }
+        tc_fence_after();
+
+        // ---- row r: mask, running max / sum, P, rescale of O ----
+        float alpha = 1.0f;
+        {
+            float s_lo[32], s_hi[32];
+            tmem_ld32(my_tmem + kUmColS, s_lo);
+            tmem_ld32(my_tmem + kUmColS + 32, s_hi);
+            float mx = m_run;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                s_lo[c] = kpos[c] < vis ? s_lo[c] * p.scale_log2 : -INFINITY;
+                s_hi[c] = kpos[32 + c] < vis ? s_hi[c] * p.scale_log2 : -INFINITY;
+                mx = fmaxf(mx, fmaxf(s_lo[c], s_hi[c]));
+            }
+            const float m_use = mx == -INFINITY ? 0.0f : mx;       // a row that has seen nothing yet
+            alpha = exp2f(m_run - m_use);                          // m_run = -inf: 0
+            float sum = 0.0f;
+            uint32_t packed[32];
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const __nv_bfloat16 p0 = __float2bfloat16_rn(exp2f(s_lo[2 * c] - m_use));
+                const __nv_bfloat16 p1 = __float2bfloat16_rn(exp2f(s_lo[2 * c + 1] - m_use));
+                const __nv_bfloat16 p2 = __float2bfloat16_rn(exp2f(s_hi[2 * c] - m_use));
+                const __nv_bfloat16 p3 = __float2bfloat16_rn(exp2f(s_hi[2 * c + 1] - m_use));
+                sum += (__bfloat162float(p0) + __bfloat162float(p1)) + (__bfloat162float(p2) + __bfloat162float(p3));
+                packed[c] = (uint32_t)__bfloat16_as_ushort(p0) | ((uint32_t)__bfloat16_as_ushort(p1) << 16);
+                packed[16 + c] = (uint32_t)__bfloat16_as_ushort(p2) | ((uint32_t)__bfloat16_as_ushort(p3) << 16);
+            }
+            l_run = l_run * alpha + sum;
+            m_run = mx;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(sP + swz(tid, c)) =
+                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+        }
+        if (blk > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {     // warp-uniform: tcgen05.ld / st are warp-wide
+#pragma unroll
+            for (int c = 0; c < kHeadDim; c += 32) {
+                float o[32];
+                tmem_ld32(my_tmem + kUmColO + c, o);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] *= alpha;
+                tmem_st32(my_tmem + kUmColO + c, o);
+            }
+            tmem_st_wait();
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncthreads();
+
+        // ---- O += P . V ----
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int s = 0; s < kUmKeys / 16; ++s) {
+                const uint64_t a = umma_desc(smem_u32(sP) + s * 32, 0, 1024);
+                const uint64_t bd = umma_desc(smem_u32(sV) + s * (16 * 128), kUmVLbo, kUmVSbo);
+                umma_f16(tmem + kUmColO, a, bd, idesc_o, (blk > 0 || s > 0) ? 1u : 0u);
+            }
+            umma_commit(&bar_o);
+        }
+        if (!mbar_wait(&bar_o, blk & 1, &abort_flag)) alive = false;
+        if (!__syncthreads_and(alive)) { alive = false; break; }
+        tc_fence_after();
+    }
+
+    if (alive) {
+        const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+        __nv_bfloat16* dst = (__nv_bfloat16*)p.o + ((int64_t)(q0 + (row_on ? my_tok : 0)) * Hq + my_head) * kHeadDim;
+#pragma unroll
+        for (int c = 0; c < kHeadDim; c += 32) {
+            float o[32];
+            if (n_blocks > 0) {                     // uniform for the CTA (the loads are warp-wide)
+                tmem_ld32(my_tmem + kUmColO + c, o);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = 0.0f;
+            }
+            if (row_on) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    uint4 v;
+                    v.x = pack_bf16(o[i] * inv, o[i + 1] * inv);
+                    v.y = pack_bf16(o[i + 2] * inv, o[i + 3] * inv);
+                    v.z = pack_bf16(o[i + 4] * inv, o[i + 5] * inv);
+                    v.w = pack_bf16(o[i + 6] * inv, o[i + 7] * inv);
+                    *reinterpret_cast<uint4*>(dst + c + i) = v;
+                }
+            }
+        }
+    } else if (tid == 0) {
+        report(p.status, KTK_STATUS_TIMEOUT);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kUmTmemCols) : "memory");
+}
+
+int launch_prefill_umma(const PrefillUmmaParams& p, int max_new_tokens, cudaStream_t st) {
+    KTK_CUDA_TRY(cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kUmSmem),
+                 "ktk_prefill_attention");
+    const int tpc = kUmRows / p.G;
+    const dim3 grid((unsigned)((max_new_tokens + tpc - 1) / tpc), (unsigned)p.Hkv, (unsigned)p.batch);
+    prefill_umma_kernel<<<grid, kUmRows, kUmSmem, st>>>(p);
+    KTK_CUDA_TRY(cudaGetLastError(), "ktk_prefill_attention");
+    return KTK_OK;
+}
+
+}  // namespace ktk
