@@ -428,8 +428,10 @@ KTK_API int ktk_append_tokens(const void* k, const void* v, const int32_t* appen
  *   page table       the state AFTER the append: sequence b holds n tokens in all, its new tokens are the
  *                    last q_indptr[b+1] - q_indptr[b] of them.  `view` as for the other entry points (sink page,
  *                    page_count); local_tokens plays no part, every visible token is attended.
- *   variant          KTK_VARIANT_AUTO: tensor cores for bf16 with a group size of 1, 2, 4 or 8 (one CTA per
- *                    sequence, kv head and tile of 32 / G tokens; each page staged once per tile by TMA);
+ *   variant          KTK_VARIANT_AUTO: tensor cores for bf16 with a group size of 1, 2, 4 or 8 -- the tcgen05
+ *                    kernel (KTK_VARIANT_UMMA: one CTA per sequence, kv head and tile of 128 / G tokens, history
+ *                    in blocks of 64 keys, S and O accumulated in tensor memory); KTK_VARIANT_MMA asks for the
+ *                    earlier mma.sync kernel (tiles of 32 / G tokens, each page staged once per tile by TMA);
  *                    otherwise, and for KTK_VARIANT_SIMT, every new token runs as one row of the dense paged
  *                    decode with its own horizon, which needs `workspace` of ktk_prefill_workspace_bytes()
  *                    bytes (three ints per new token).

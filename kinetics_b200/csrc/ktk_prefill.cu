@@ -288,7 +288,7 @@ extern "C" int ktk_prefill_attention(const void* q, const int32_t* q_indptr, int
             set_error("%s: more than 65535 sequences or kv heads in one launch", who);
             return KTK_ERR_TOO_LARGE;
         }
-        if (variant == KTK_VARIANT_UMMA) {
+        if (variant != KTK_VARIANT_MMA) {             // KTK_VARIANT_AUTO and KTK_VARIANT_UMMA: the tcgen05 kernel
             PrefillUmmaParams u;
             u.q = q; u.o = o; u.cache = kv_cache; u.q_indptr = q_indptr; u.kv_indices = kv_indices;
             u.kv_indptr = kv_indptr; u.kv_last_page_len = kv_last_page_len; u.page_count = view.page_count;

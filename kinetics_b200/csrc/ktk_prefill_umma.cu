@@ -28,8 +28,9 @@ constexpr int kUmTmemCols = 256;             // S: columns [0, 64), O: columns [
 constexpr int kUmColS = 0, kUmColO = 64;
 constexpr int kUmQBytes = 2 * kUmRows * 128; // two tiles of [128 rows][64 dims]
 constexpr int kUmKBytes = 2 * kUmKeys * 128; // two tiles of [64 keys][64 dims]
-constexpr int kUmPBytes = kUmRows * 128;     // [128 rows][64 keys]
-constexpr int kUmSmem = kUmQBytes + 2 * kUmKBytes + kUmPBytes + 1024;
+constexpr int kUmPBytes = kUmRows * 128;     // [128 rows][64 keys]: laid over the K tiles of its block (dead by then)
+static_assert(kUmPBytes <= kUmKBytes, "P reuses the K buffer");
+constexpr int kUmSmem = kUmQBytes + 4 * kUmKBytes + 1024;     // Q | K, V of two blocks in flight
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------------------
 // shared-memory operand descriptor: start address, leading / stride byte offsets (all >> 4), version 1,
@@ -99,7 +100,9 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // byte offset of the 16-byte chunk `chunk` (0..7) of row `row` in a [rows][128 B] tile under the 128-byte swizzle
 __device__ __forceinline__ uint32_t swz(int row, int chunk) {
@@ -111,14 +114,12 @@ prefill_umma_kernel(const PrefillUmmaParams p) {
     extern __shared__ uint8_t um_raw[];
     __shared__ __align__(8) uint64_t bar_s, bar_o;
     __shared__ uint32_t tmem_base_s;
-    __shared__ int kpos[kUmKeys];                 // position of the key in row c of the block (INT_MAX: none)
+    __shared__ int kpos[2][kUmKeys];              // position of the key in row c of the block (INT_MAX: none)
     __shared__ int abort_flag;
 
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(um_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = sm;
-    uint8_t* sK = sQ + kUmQBytes;
-    uint8_t* sV = sK + kUmKBytes;
-    uint8_t* sP = sV + kUmKBytes;
+    uint8_t* sKV = sQ + kUmQBytes;                // [buffer][K | V]
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int b = blockIdx.z, h = blockIdx.y;
@@ -175,47 +176,72 @@ prefill_umma_kernel(const PrefillUmmaParams p) {
 
     const uint32_t idesc_s = umma_idesc(kUmKeys, false);
     const uint32_t idesc_o = umma_idesc(kHeadDim, true);
-    float m_run = -INFINITY, l_run = 0.0f;
+    float m_run = -INFINITY, m_ref = 0.0f, l_run = 0.0f;   // running max, reference point of the exponentials, row sum
     const __nv_bfloat16* cache = (const __nv_bfloat16*)p.cache;
     const int64_t tok_stride = (int64_t)p.Hkv * kHeadDim;            // elements between the tokens of a page
     bool alive = true;
 
+    // K and V of block `blk` -> buffer `buf`: thread t copies half a row (128 B of K, 128 B of V) of key row t / 2
+    auto issue_loads = [&](int blk, int buf) {
+        const int row = tid >> 1, half = tid & 1;
+        const int e = blk * kUmPagesPerBlock + (row >> 4), slot = row & 15;
+        bool live = false;
+        int64_t page = 0;
+        int pos = 0x7fffffff;
+        if (e < n_need) {
+            const int ntok = (e == sp.n_pages - 1) ? sp.last_fill : (e == 0 ? sp.first_fill : kPageSize);
+            page = p.kv_indices[sp.start + e];
+            if (page < 0 || page >= p.num_pages) {
+                if (slot == 0 && half == 0) report(p.status, KTK_STATUS_BAD_PAGE);
+            } else if (slot < ntok) {
+                live = true;
+                pos = page_first_pos(e, sp.first_fill) + slot;
+            }
+        }
+        if (half == 0) kpos[buf][row] = pos;
+        uint8_t* dK = sKV + buf * (2 * kUmKBytes) + half * (kUmKeys * 128);
+        uint8_t* dV = dK + kUmKBytes;
+        if (live) {
+            const __nv_bfloat16* src =
+                cache + ((page * 2) * kPageSize + slot) * tok_stride + (int64_t)h * kHeadDim + half * 64;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                cp_async16(smem_u32(dK + swz(row, c)), src + c * 8);
+                cp_async16(smem_u32(dV + swz(row, c)), src + (int64_t)kPageSize * tok_stride + c * 8);
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                *reinterpret_cast<uint4*>(dK + swz(row, c)) = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(dV + swz(row, c)) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        cp_async_commit();
+    };
+    // a block every row of the tile sees in full (no fill-level or diagonal mask): four full pages that end
+    // before the first row's horizon
+    const int tile_min_vis = base_pos + tok0 + 1;
+    auto block_is_clean = [&](int blk) {
+        const int e0 = blk * kUmPagesPerBlock, e1 = e0 + kUmPagesPerBlock - 1;
+        if (e1 >= n_need) return false;
+        if (e0 == 0 && sp.first_fill != kPageSize) return false;
+        if (e1 == sp.n_pages - 1 && sp.last_fill != kPageSize) return false;
+        return page_first_pos(e1, sp.first_fill) + kPageSize <= tile_min_vis;
+    };
+
+    if (n_blocks > 0) issue_loads(0, 0);
     for (int blk = 0; blk < n_blocks; ++blk) {
-        // ---- K and V of the block's pages -> shared memory ----
-        if (tid < kUmKeys) {
-            const int e = blk * kUmPagesPerBlock + (tid >> 4), slot = tid & 15;
-            int pos = 0x7fffffff;
-            if (e < n_need) {
-                const int ntok = (e == sp.n_pages - 1) ? sp.last_fill : (e == 0 ? sp.first_fill : kPageSize);
-                if (slot < ntok) pos = page_first_pos(e, sp.first_fill) + slot;
-            }
-            kpos[tid] = pos;
+        const int buf = blk & 1;
+        uint8_t* sK = sKV + buf * (2 * kUmKBytes);
+        uint8_t* sV = sK + kUmKBytes;
+        uint8_t* sP = sK;                           // written after S is complete, when K is dead
+        // the next block's loads fly during this block's arithmetic (its buffer was released by bar_o of blk - 1)
+        if (blk + 1 < n_blocks) {
+            issue_loads(blk + 1, buf ^ 1);
+            cp_async_wait_group<1>();
+        } else {
+            cp_async_wait_group<0>();
         }
-        for (int i = tid; i < kUmKeys * 16; i += kUmRows) {
-            const int row = i >> 4, c = i & 15;
-            const int e = blk * kUmPagesPerBlock + (row >> 4), slot = row & 15;
-            bool live = false;
-            int64_t page = 0;
-            if (e < n_need) {
-                const int ntok = (e == sp.n_pages - 1) ? sp.last_fill : (e == 0 ? sp.first_fill : kPageSize);
-                page = p.kv_indices[sp.start + e];
-                if (page < 0 || page >= p.num_pages) {
-                    if (c == 0 && slot == 0) report(p.status, KTK_STATUS_BAD_PAGE);
-                } else {
-                    live = slot < ntok;
-                }
-            }
-            const uint32_t off = (uint32_t)((c >> 3) * (kUmKeys * 128)) + swz(row, c & 7);
-            if (live) {
-                const __nv_bfloat16* src = cache + ((page * 2) * kPageSize + slot) * tok_stride + (int64_t)h * kHeadDim + c * 8;
-                cp_async16(smem_u32(sK + off), src);
-                cp_async16(smem_u32(sV + off), src + (int64_t)kPageSize * tok_stride);
-            } else {
-                *reinterpret_cast<uint4*>(sK + off) = make_uint4(0u, 0u, 0u, 0u);
-                *reinterpret_cast<uint4*>(sV + off) = make_uint4(0u, 0u, 0u, 0u);
-            }
-        }
-        cp_async_wait_all();
         fence_proxy_async();
         __syncthreads();
 
@@ -241,25 +267,40 @@ prefill_umma_kernel(const PrefillUmmaParams p) {
             tmem_ld32(my_tmem + kUmColS, s_lo);
             tmem_ld32(my_tmem + kUmColS + 32, s_hi);
             float mx = m_run;
+            if (block_is_clean(blk)) {              // uniform for the CTA
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                s_lo[c] = kpos[c] < vis ? s_lo[c] * p.scale_log2 : -INFINITY;
-                s_hi[c] = kpos[32 + c] < vis ? s_hi[c] * p.scale_log2 : -INFINITY;
-                mx = fmaxf(mx, fmaxf(s_lo[c], s_hi[c]));
+                for (int c = 0; c < 32; ++c) {
+                    s_lo[c] *= p.scale_log2;
+                    s_hi[c] *= p.scale_log2;
+                    mx = fmaxf(mx, fmaxf(s_lo[c], s_hi[c]));
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    s_lo[c] = kpos[buf][c] < vis ? s_lo[c] * p.scale_log2 : -INFINITY;
+                    s_hi[c] = kpos[buf][32 + c] < vis ? s_hi[c] * p.scale_log2 : -INFINITY;
+                    mx = fmaxf(mx, fmaxf(s_lo[c], s_hi[c]));
+                }
             }
-            const float m_use = mx == -INFINITY ? 0.0f : mx;       // a row that has seen nothing yet
-            alpha = exp2f(m_run - m_use);                          // m_run = -inf: 0
+            // The reference point of the exponentials follows the running maximum only when that moved by more
+            // than 2^8: P then stays below 256 (exact in fp32, fine in bf16) and the O row in tensor memory is
+            // rescaled rarely instead of at almost every block.  The final division by the row sum, taken against
+            // the same reference point, makes the result independent of it.
+            float m_use;
+            if (mx == -INFINITY) m_use = 0.0f;                     // a row that has seen nothing yet
+            else if (m_run == -INFINITY || mx - m_ref > 8.0f) m_use = mx;
+            else m_use = m_ref;
+            alpha = (m_run == -INFINITY) ? 0.0f : exp2f(m_ref - m_use);
+            m_ref = m_use;
             float sum = 0.0f;
             uint32_t packed[32];
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
-                const __nv_bfloat16 p0 = __float2bfloat16_rn(exp2f(s_lo[2 * c] - m_use));
-                const __nv_bfloat16 p1 = __float2bfloat16_rn(exp2f(s_lo[2 * c + 1] - m_use));
-                const __nv_bfloat16 p2 = __float2bfloat16_rn(exp2f(s_hi[2 * c] - m_use));
-                const __nv_bfloat16 p3 = __float2bfloat16_rn(exp2f(s_hi[2 * c + 1] - m_use));
-                sum += (__bfloat162float(p0) + __bfloat162float(p1)) + (__bfloat162float(p2) + __bfloat162float(p3));
-                packed[c] = (uint32_t)__bfloat16_as_ushort(p0) | ((uint32_t)__bfloat16_as_ushort(p1) << 16);
-                packed[16 + c] = (uint32_t)__bfloat16_as_ushort(p2) | ((uint32_t)__bfloat16_as_ushort(p3) << 16);
+                const float p0 = exp2f(s_lo[2 * c] - m_use), p1 = exp2f(s_lo[2 * c + 1] - m_use);
+                const float p2 = exp2f(s_hi[2 * c] - m_use), p3 = exp2f(s_hi[2 * c + 1] - m_use);
+                sum += (p0 + p1) + (p2 + p3);
+                packed[c] = pack_bf16(p0, p1);
+                packed[16 + c] = pack_bf16(p2, p3);
             }
             l_run = l_run * alpha + sum;
             m_run = mx;

@@ -28,7 +28,7 @@ def _reference(q, k, v, G):
     return torch.einsum("hnt,htd->nhd", torch.softmax(logits, dim=-1), vv)
 
 
-@pytest.mark.parametrize("dtype,variant", [(torch.bfloat16, 0), (torch.bfloat16, 1), (torch.bfloat16, 3),
+@pytest.mark.parametrize("dtype,variant", [(torch.bfloat16, 0), (torch.bfloat16, 1), (torch.bfloat16, 2), (torch.bfloat16, 3),
                                            (torch.float32, 0)])
 @pytest.mark.parametrize("G,Hkv,sink", [(4, 2, 0), (8, 1, 4), (2, 2, 4), (1, 3, 0)])
 def test_prefill_matches_causal_attention(cuda_device, dtype, variant, G, Hkv, sink):
