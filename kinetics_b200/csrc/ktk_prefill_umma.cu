@@ -24,8 +24,8 @@ namespace ktk {
 constexpr int kUmRows = 128;                 // rows of a tile = threads of a CTA
 constexpr int kUmKeys = 64;                  // keys per block
 constexpr int kUmPagesPerBlock = kUmKeys / kPageSize;
-constexpr int kUmTmemCols = 256;             // S: columns [0, 64), O: columns [64, 192)
-constexpr int kUmColS = 0, kUmColO = 64;
+constexpr int kUmTmemCols = 256;             // S of two blocks: columns [0, 64) and [64, 128); O: [128, 256)
+constexpr int kUmColS = 0, kUmColO = 128;
 constexpr int kUmQBytes = 2 * kUmRows * 128; // two tiles of [128 rows][64 dims]
 constexpr int kUmKBytes = 2 * kUmKeys * 128; // two tiles of [64 keys][64 dims]
 constexpr int kUmPBytes = kUmRows * 128;     // [128 rows][64 keys]: laid over the K tiles of its block (dead by then)
@@ -54,6 +54,14 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a, uint64_t b
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// the same with the A operand in tensor memory (lane = row, two bf16 per column)
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -95,6 +103,17 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
           "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
         : "memory");
 }
+__device__ __forceinline__ void tmem_st32_u32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -112,7 +131,7 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
 __global__ void __launch_bounds__(kUmRows, 2)
 prefill_umma_kernel(const PrefillUmmaParams p) {
     extern __shared__ uint8_t um_raw[];
-    __shared__ __align__(8) uint64_t bar_s, bar_o;
+    __shared__ __align__(8) uint64_t bar_s[2], bar_o;
     __shared__ uint32_t tmem_base_s;
     __shared__ int kpos[2][kUmKeys];              // position of the key in row c of the block (INT_MAX: none)
     __shared__ int abort_flag;
@@ -148,7 +167,8 @@ prefill_umma_kernel(const PrefillUmmaParams p) {
     const int vis = row_on ? base_pos + my_tok + 1 : 0;     // keys at positions < vis are seen
 
     if (tid == 0) {
-        mbar_init(&bar_s, 1);
+        mbar_init(&bar_s[0], 1);
+        mbar_init(&bar_s[1], 1);
         mbar_init(&bar_o, 1);
         abort_flag = 0;
         mbar_init_fence();
@@ -181,42 +201,54 @@ prefill_umma_kernel(const PrefillUmmaParams p) {
     const int64_t tok_stride = (int64_t)p.Hkv * kHeadDim;            // elements between the tokens of a page
     bool alive = true;
 
-    // K and V of block `blk` -> buffer `buf`: thread t copies half a row (128 B of K, 128 B of V) of key row t / 2
-    auto issue_loads = [&](int blk, int buf) {
-        const int row = tid >> 1, half = tid & 1;
-        const int e = blk * kUmPagesPerBlock + (row >> 4), slot = row & 15;
-        bool live = false;
-        int64_t page = 0;
-        int pos = 0x7fffffff;
-        if (e < n_need) {
-            const int ntok = (e == sp.n_pages - 1) ? sp.last_fill : (e == 0 ? sp.first_fill : kPageSize);
-            page = p.kv_indices[sp.start + e];
-            if (page < 0 || page >= p.num_pages) {
-                if (slot == 0 && half == 0) report(p.status, KTK_STATUS_BAD_PAGE);
-            } else if (slot < ntok) {
-                live = true;
-                pos = page_first_pos(e, sp.first_fill) + slot;
+    // K (which = 0) or V (which = 1) of block `blk` -> its buffer blk & 1: thread t copies half a row (128 B) of
+    // key row t / 2; rows past a page's fill level or past the last page are zero-filled.  One cp.async group per
+    // call, also when there is nothing to load, so that the group counts below hold at the ends.  The V call
+    // also records the key positions of the block.
+    auto issue_loads = [&](int blk, int which) {
+        if (blk < n_blocks) {
+            const int buf = blk & 1;
+            const int row = tid >> 1, half = tid & 1;
+            const int e = blk * kUmPagesPerBlock + (row >> 4), slot = row & 15;
+            bool live = false;
+            int64_t page = 0;
+            int pos = 0x7fffffff;
+            if (e < n_need) {
+                const int ntok = (e == sp.n_pages - 1) ? sp.last_fill : (e == 0 ? sp.first_fill : kPageSize);
+                page = p.kv_indices[sp.start + e];
+                if (page < 0 || page >= p.num_pages) {
+                    if (slot == 0 && half == 0 && which == 0) report(p.status, KTK_STATUS_BAD_PAGE);
+                } else if (slot < ntok) {
+                    live = true;
+                    pos = page_first_pos(e, sp.first_fill) + slot;
+                }
             }
-        }
-        if (half == 0) kpos[buf][row] = pos;
-        uint8_t* dK = sKV + buf * (2 * kUmKBytes) + half * (kUmKeys * 128);
-        uint8_t* dV = dK + kUmKBytes;
-        if (live) {
-            const __nv_bfloat16* src =
-                cache + ((page * 2) * kPageSize + slot) * tok_stride + (int64_t)h * kHeadDim + half * 64;
+            if (which == 1 && half == 0) kpos[buf][row] = pos;
+            uint8_t* dst = sKV + buf * (2 * kUmKBytes) + which * kUmKBytes + half * (kUmKeys * 128);
+            if (live) {
+                const __nv_bfloat16* src = cache + ((page * 2 + which) * kPageSize + slot) * tok_stride +
+                                           (int64_t)h * kHeadDim + half * 64;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                cp_async16(smem_u32(dK + swz(row, c)), src + c * 8);
-                cp_async16(smem_u32(dV + swz(row, c)), src + (int64_t)kPageSize * tok_stride + c * 8);
-            }
-        } else {
+                for (int c = 0; c < 8; ++c) cp_async16(smem_u32(dst + swz(row, c)), src + c * 8);
+            } else {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                *reinterpret_cast<uint4*>(dK + swz(row, c)) = make_uint4(0u, 0u, 0u, 0u);
-                *reinterpret_cast<uint4*>(dV + swz(row, c)) = make_uint4(0u, 0u, 0u, 0u);
+                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + swz(row, c)) = make_uint4(0u, 0u, 0u, 0u);
             }
         }
         cp_async_commit();
+    };
+    // S of block `blk` = Q . K^T into S buffer blk & 1 (one thread)
+    auto issue_s = [&](int blk) {
+        const int buf = blk & 1;
+        const uint32_t kaddr = smem_u32(sKV + buf * (2 * kUmKBytes));
+        tc_fence_after();
+#pragma unroll
+        for (int s = 0; s < kHeadDim / 16; ++s) {
+            const uint64_t a = umma_desc(smem_u32(sQ) + (s >> 2) * (kUmRows * 128) + (s & 3) * 32, 0, 1024);
+            const uint64_t bd = umma_desc(kaddr + (s >> 2) * (kUmKeys * 128) + (s & 3) * 32, 0, 1024);
+            umma_f16(tmem + kUmColS + buf * kUmKeys, a, bd, idesc_s, s > 0 ? 1u : 0u);
+        }
+        umma_commit(&bar_s[buf]);
     };
     // a block every row of the tile sees in full (no fill-level or diagonal mask): four full pages that end
     // before the first row's horizon
@@ -229,45 +261,41 @@ prefill_umma_kernel(const PrefillUmmaParams p) {
         return page_first_pos(e1, sp.first_fill) + kPageSize <= tile_min_vis;
     };
 
-    if (n_blocks > 0) issue_loads(0, 0);
-    for (int blk = 0; blk < n_blocks; ++blk) {
-        const int buf = blk & 1;
-        uint8_t* sK = sKV + buf * (2 * kUmKBytes);
-        uint8_t* sV = sK + kUmKBytes;
-        uint8_t* sP = sK;                           // written after S is complete, when K is dead
-        // the next block's loads fly during this block's arithmetic (its buffer was released by bar_o of blk - 1)
-        if (blk + 1 < n_blocks) {
-            issue_loads(blk + 1, buf ^ 1);
-            cp_async_wait_group<1>();
-        } else {
-            cp_async_wait_group<0>();
-        }
+    // Software pipeline, one block ahead: while the threads work on S of block j, the tensor cores already
+    // compute S of block j + 1 and then O += P.V of block j; the loads run two (K) and one (V) blocks ahead.
+    // cp.async groups in issue order: K0 K1 V0 | K2 V1 | K3 V2 | ...
+    if (n_blocks > 0) {
+        issue_loads(0, 0);
+        issue_loads(1, 0);
+        issue_loads(0, 1);
+        cp_async_wait_group<2>();                   // K0
         fence_proxy_async();
         __syncthreads();
-
-        // ---- S = Q . K^T ----
-        if (tid == 0) {
-            tc_fence_after();
-#pragma unroll
-            for (int s = 0; s < kHeadDim / 16; ++s) {
-                const uint64_t a = umma_desc(smem_u32(sQ) + (s >> 2) * (kUmRows * 128) + (s & 3) * 32, 0, 1024);
-                const uint64_t bd = umma_desc(smem_u32(sK) + (s >> 2) * (kUmKeys * 128) + (s & 3) * 32, 0, 1024);
-                umma_f16(tmem + kUmColS, a, bd, idesc_s, s > 0 ? 1u : 0u);
-            }
-            umma_commit(&bar_s);
+        if (tid == 0) issue_s(0);
+    }
+    for (int j = 0; j < n_blocks; ++j) {
+        const int buf = j & 1;
+        const uint32_t s_col = kUmColS + buf * kUmKeys;
+        // ---- S of the next block goes to the tensor cores before this block's softmax ----
+        if (j + 1 < n_blocks) {
+            cp_async_wait_group<1>();               // K of block j + 1 (only V of block j may still fly)
+            fence_proxy_async();
+            if (!__syncthreads_and(alive)) { alive = false; break; }
+            if (tid == 0) issue_s(j + 1);
         }
-        if (!mbar_wait(&bar_s, blk & 1, &abort_flag)) alive = false;
-        if (!__syncthreads_and(alive)) { alive = false; break; }
+        // ---- S of this block ----
+        if (!mbar_wait(&bar_s[buf], (j >> 1) & 1, &abort_flag)) alive = false;
         tc_fence_after();
+        issue_loads(j + 2, 0);                      // K of block j + 2 over K of block j, which S no longer needs
 
-        // ---- row r: mask, running max / sum, P, rescale of O ----
         float alpha = 1.0f;
+        uint32_t packed[32];
         {
             float s_lo[32], s_hi[32];
-            tmem_ld32(my_tmem + kUmColS, s_lo);
-            tmem_ld32(my_tmem + kUmColS + 32, s_hi);
+            tmem_ld32(my_tmem + s_col, s_lo);
+            tmem_ld32(my_tmem + s_col + 32, s_hi);
             float mx = m_run;
-            if (block_is_clean(blk)) {              // uniform for the CTA
+            if (block_is_clean(j)) {                // uniform for the CTA
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
                     s_lo[c] *= p.scale_log2;
@@ -293,23 +321,24 @@ prefill_umma_kernel(const PrefillUmmaParams p) {
             alpha = (m_run == -INFINITY) ? 0.0f : exp2f(m_ref - m_use);
             m_ref = m_use;
             float sum = 0.0f;
-            uint32_t packed[32];
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
                 const float p0 = exp2f(s_lo[2 * c] - m_use), p1 = exp2f(s_lo[2 * c + 1] - m_use);
                 const float p2 = exp2f(s_hi[2 * c] - m_use), p3 = exp2f(s_hi[2 * c + 1] - m_use);
                 sum += (p0 + p1) + (p2 + p3);
-                packed[c] = pack_bf16(p0, p1);
-                packed[16 + c] = pack_bf16(p2, p3);
+                packed[c] = pack_bf16(p0, p1);      // keys 2c, 2c + 1 -> column c of P
+                packed[16 + c] = pack_bf16(p2, p3); // keys 32 + 2c, 33 + 2c -> column 16 + c
             }
             l_run = l_run * alpha + sum;
             m_run = mx;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(sP + swz(tid, c)) =
-                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
         }
-        if (blk > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {     // warp-uniform: tcgen05.ld / st are warp-wide
+        // ---- O += P.V of the previous block has to be over: O is rescaled, its V buffer reloaded ----
+        if (j > 0) {
+            if (!mbar_wait(&bar_o, (j - 1) & 1, &abort_flag)) alive = false;
+            tc_fence_after();
+        }
+        issue_loads(j + 1, 1);                      // V of block j + 1 (and the key positions of that block)
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {     // warp-uniform: tcgen05.ld / st are warp-wide
 #pragma unroll
             for (int c = 0; c < kHeadDim; c += 32) {
                 float o[32];
@@ -318,27 +347,32 @@ prefill_umma_kernel(const PrefillUmmaParams p) {
                 for (int i = 0; i < 32; ++i) o[i] *= alpha;
                 tmem_st32(my_tmem + kUmColO + c, o);
             }
-            tmem_st_wait();
         }
+        // P as bf16 pairs over the first 32 columns of this block's S (read into registers above)
+        tmem_st32_u32(my_tmem + s_col, packed);
+        tmem_st_wait();
+        cp_async_wait_group<2>();                   // V of block j
         fence_proxy_async();
         tc_fence_before();
-        __syncthreads();
+        if (!__syncthreads_and(alive)) { alive = false; break; }
 
         // ---- O += P . V ----
         if (tid == 0) {
             tc_fence_after();
+            const uint32_t vaddr = smem_u32(sKV + buf * (2 * kUmKBytes) + kUmKBytes);
 #pragma unroll
             for (int s = 0; s < kUmKeys / 16; ++s) {
-                const uint64_t a = umma_desc(smem_u32(sP) + s * 32, 0, 1024);
-                const uint64_t bd = umma_desc(smem_u32(sV) + s * (16 * 128), kUmVLbo, kUmVSbo);
-                umma_f16(tmem + kUmColO, a, bd, idesc_o, (blk > 0 || s > 0) ? 1u : 0u);
+                const uint64_t bd = umma_desc(vaddr + s * (16 * 128), kUmVLbo, kUmVSbo);
+                umma_f16_ts(tmem + kUmColO, tmem + s_col + s * 8, bd, idesc_o, (j > 0 || s > 0) ? 1u : 0u);
             }
             umma_commit(&bar_o);
         }
-        if (!mbar_wait(&bar_o, blk & 1, &abort_flag)) alive = false;
-        if (!__syncthreads_and(alive)) { alive = false; break; }
+    }
+    if (alive && n_blocks > 0) {
+        if (!mbar_wait(&bar_o, (n_blocks - 1) & 1, &abort_flag)) alive = false;
         tc_fence_after();
     }
+    alive = __syncthreads_and(alive);
 
     if (alive) {
         const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
