@@ -123,6 +123,13 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// 2^x on the special-function unit (-inf -> 0)
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // byte offset of the 16-byte chunk `chunk` (0..7) of row `row` in a [rows][128 B] tile under the 128-byte swizzle
 __device__ __forceinline__ uint32_t swz(int row, int chunk) {
     return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4));
@@ -146,7 +153,8 @@ prefill_umma_kernel(const PrefillUmmaParams p) {
     const int tpc = kUmRows / G;                    // new tokens per CTA
     const int q0 = p.q_indptr[b];
     const int n_new = p.q_indptr[b + 1] - q0;
-    const int tok0 = blockIdx.x * tpc;
+    // tiles late in a sequence see the longest history: they are launched first
+    const int tok0 = (int)(gridDim.x - 1 - blockIdx.x) * tpc;
     if (tok0 >= n_new) return;                      // uniform for the CTA: nothing allocated yet
 
     const SeqPages sp = seq_pages(p.kv_indptr, p.page_count, p.kv_last_page_len, p.sink_tokens, b);
@@ -294,22 +302,23 @@ prefill_umma_kernel(const PrefillUmmaParams p) {
             float s_lo[32], s_hi[32];
             tmem_ld32(my_tmem + s_col, s_lo);
             tmem_ld32(my_tmem + s_col + 32, s_hi);
-            float mx = m_run;
-            if (block_is_clean(j)) {                // uniform for the CTA
+            // masked columns become -inf; the scale (positive) is applied inside the exponent below
+            if (!block_is_clean(j)) {               // uniform for the CTA
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
-                    s_lo[c] *= p.scale_log2;
-                    s_hi[c] *= p.scale_log2;
-                    mx = fmaxf(mx, fmaxf(s_lo[c], s_hi[c]));
-                }
-            } else {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    s_lo[c] = kpos[buf][c] < vis ? s_lo[c] * p.scale_log2 : -INFINITY;
-                    s_hi[c] = kpos[buf][32 + c] < vis ? s_hi[c] * p.scale_log2 : -INFINITY;
-                    mx = fmaxf(mx, fmaxf(s_lo[c], s_hi[c]));
+                    s_lo[c] = kpos[buf][c] < vis ? s_lo[c] : -INFINITY;
+                    s_hi[c] = kpos[buf][32 + c] < vis ? s_hi[c] : -INFINITY;
                 }
             }
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+                mx0 = fmaxf(mx0, s_lo[c]);
+                mx1 = fmaxf(mx1, s_lo[c + 1]);
+                mx2 = fmaxf(mx2, s_hi[c]);
+                mx3 = fmaxf(mx3, s_hi[c + 1]);
+            }
+            const float mx = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2);
             // The reference point of the exponentials follows the running maximum only when that moved by more
             // than 2^8: P then stays below 256 (exact in fp32, fine in bf16) and the O row in tensor memory is
             // rescaled rarely instead of at almost every block.  The final division by the row sum, taken against
@@ -323,8 +332,10 @@ prefill_umma_kernel(const PrefillUmmaParams p) {
             float sum = 0.0f;
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
-                const float p0 = exp2f(s_lo[2 * c] - m_use), p1 = exp2f(s_lo[2 * c + 1] - m_use);
-                const float p2 = exp2f(s_hi[2 * c] - m_use), p3 = exp2f(s_hi[2 * c + 1] - m_use);
+                const float p0 = ex2(fmaf(s_lo[2 * c], p.scale_log2, -m_use));
+                const float p1 = ex2(fmaf(s_lo[2 * c + 1], p.scale_log2, -m_use));
+                const float p2 = ex2(fmaf(s_hi[2 * c], p.scale_log2, -m_use));
+                const float p3 = ex2(fmaf(s_hi[2 * c + 1], p.scale_log2, -m_use));
                 sum += (p0 + p1) + (p2 + p3);
                 packed[c] = pack_bf16(p0, p1);      // keys 2c, 2c + 1 -> column c of P
                 packed[16 + c] = pack_bf16(p2, p3); // keys 32 + 2c, 33 + 2c -> column 16 + c
