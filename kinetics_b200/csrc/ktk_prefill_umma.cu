@@ -15,8 +15,7 @@
 // and at the end row r of O is read back, divided by the row sum and stored.  The phases of one CTA run one after
 // the other; two CTAs per SM (80 KiB of shared memory and 256 TMEM columns each) overlap one another's phases.
 // Every wait is bounded; tensor memory is released on every path.
-#include "ktk_decode.cuh"
-#include "ktk_pipeline.cuh"
+#include "ktk_decode_mma.cuh"
 #include "ktk_prefill_umma.cuh"
 
 namespace ktk {
@@ -116,13 +115,6 @@ __device__ __forceinline__ void tmem_st32_u32(uint32_t taddr, const uint32_t (&v
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 // 2^x on the special-function unit (-inf -> 0)
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -136,9 +128,10 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
 }
 
 __global__ void __launch_bounds__(kUmRows, 2)
-prefill_umma_kernel(const PrefillUmmaParams p) {
+prefill_umma_kernel(const PrefillUmmaParams p, const __grid_constant__ CUtensorMap kv_map) {
     extern __shared__ uint8_t um_raw[];
-    __shared__ __align__(8) uint64_t bar_s[2], bar_o;
+    __shared__ __align__(8) uint64_t bar_s[2], bar_o, bar_k[2], bar_v[2];
+    __shared__ int vholes[2];                     // the V rows of the block in this buffer need clearing / masking
     __shared__ uint32_t tmem_base_s;
     __shared__ int kpos[2][kUmKeys];              // position of the key in row c of the block (INT_MAX: none)
     __shared__ int abort_flag;
@@ -178,6 +171,7 @@ prefill_umma_kernel(const PrefillUmmaParams p) {
         mbar_init(&bar_s[0], 1);
         mbar_init(&bar_s[1], 1);
         mbar_init(&bar_o, 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(&bar_k[i], 1); mbar_init(&bar_v[i], 1); }
         abort_flag = 0;
         mbar_init_fence();
     }
@@ -205,50 +199,65 @@ prefill_umma_kernel(const PrefillUmmaParams p) {
     const uint32_t idesc_s = umma_idesc(kUmKeys, false);
     const uint32_t idesc_o = umma_idesc(kHeadDim, true);
     float m_run = -INFINITY, m_ref = 0.0f, l_run = 0.0f;   // running max, reference point of the exponentials, row sum
-    const __nv_bfloat16* cache = (const __nv_bfloat16*)p.cache;
-    const int64_t tok_stride = (int64_t)p.Hkv * kHeadDim;            // elements between the tokens of a page
     bool alive = true;
 
-    // K (which = 0) or V (which = 1) of block `blk` -> its buffer blk & 1: thread t copies half a row (128 B) of
-    // key row t / 2; rows past a page's fill level or past the last page are zero-filled.  One cp.async group per
-    // call, also when there is nothing to load, so that the group counts below hold at the ends.  The V call
-    // also records the key positions of the block.
-    auto issue_loads = [&](int blk, int which) {
-        if (blk < n_blocks) {
-            const int buf = blk & 1;
-            const int row = tid >> 1, half = tid & 1;
-            const int e = blk * kUmPagesPerBlock + (row >> 4), slot = row & 15;
-            bool live = false;
-            int64_t page = 0;
-            int pos = 0x7fffffff;
+    // K (which = 0) or V (which = 1) of block `blk` -> its buffer blk & 1, issued by one thread: per page two TMA
+    // boxes of 16 rows x 128 B (the two 64-dim halves) into the 128-byte swizzle pattern the tensor cores read.
+    // The V call also notes whether rows of the block will be left without data (a page past the needed ones, an
+    // invalid page id, a page that is not full): those rows of V are cleared before the block is used.
+    auto issue_tma = [&](int blk, int which) {
+        if (blk >= n_blocks) return;
+        const int buf = blk & 1;
+        uint64_t* bar = which ? &bar_v[buf] : &bar_k[buf];
+        uint8_t* dst = sKV + buf * (2 * kUmKBytes) + which * kUmKBytes;
+        int64_t pages[kUmPagesPerBlock];
+        uint32_t bytes = 0;
+        bool holes = false;
+#pragma unroll
+        for (int pi = 0; pi < kUmPagesPerBlock; ++pi) {
+            const int e = blk * kUmPagesPerBlock + pi;
+            pages[pi] = -1;
             if (e < n_need) {
-                const int ntok = (e == sp.n_pages - 1) ? sp.last_fill : (e == 0 ? sp.first_fill : kPageSize);
-                page = p.kv_indices[sp.start + e];
-                if (page < 0 || page >= p.num_pages) {
-                    if (slot == 0 && half == 0 && which == 0) report(p.status, KTK_STATUS_BAD_PAGE);
-                } else if (slot < ntok) {
-                    live = true;
-                    pos = page_first_pos(e, sp.first_fill) + slot;
+                const int64_t pg = p.kv_indices[sp.start + e];
+                if (pg < 0 || pg >= p.num_pages) {
+                    if (which == 0) report(p.status, KTK_STATUS_BAD_PAGE);
+                } else {
+                    pages[pi] = pg;
+                    bytes += 2u * kPageSize * 128u;
                 }
+                const int ntok = (e == sp.n_pages - 1) ? sp.last_fill : (e == 0 ? sp.first_fill : kPageSize);
+                if (ntok != kPageSize) holes = true;
             }
-            if (which == 1 && half == 0) kpos[buf][row] = pos;
-            uint8_t* dst = sKV + buf * (2 * kUmKBytes) + which * kUmKBytes + half * (kUmKeys * 128);
-            if (live) {
-                const __nv_bfloat16* src = cache + ((page * 2 + which) * kPageSize + slot) * tok_stride +
-                                           (int64_t)h * kHeadDim + half * 64;
-#pragma unroll
-                for (int c = 0; c < 8; ++c) cp_async16(smem_u32(dst + swz(row, c)), src + c * 8);
-            } else {
-#pragma unroll
-                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + swz(row, c)) = make_uint4(0u, 0u, 0u, 0u);
-            }
+            if (pages[pi] < 0) holes = true;
         }
-        cp_async_commit();
+        if (which == 1) vholes[buf] = holes ? 1 : 0;
+        if (bytes) mbar_arrive_expect_tx(bar, bytes);
+        else mbar_arrive(bar);
+#pragma unroll
+        for (int pi = 0; pi < kUmPagesPerBlock; ++pi) {
+            if (pages[pi] < 0) continue;
+            const int z = (int)(pages[pi] * (2 * kPageSize)) + which * kPageSize;    // token row of slot 0
+            tma_load_3d(dst + pi * (kPageSize * 128), &kv_map, bar, 0, h, z);
+            tma_load_3d(dst + kUmKeys * 128 + pi * (kPageSize * 128), &kv_map, bar, 64, h, z);
+        }
+    };
+    // positions of the keys of block `blk` (threads 0..63, one row each)
+    auto note_positions = [&](int blk) {
+        if (blk >= n_blocks || tid >= kUmKeys) return;
+        const int e = blk * kUmPagesPerBlock + (tid >> 4), slot = tid & 15;
+        int pos = 0x7fffffff;
+        if (e < n_need) {
+            const int ntok = (e == sp.n_pages - 1) ? sp.last_fill : (e == 0 ? sp.first_fill : kPageSize);
+            const int64_t pg = p.kv_indices[sp.start + e];
+            if (pg >= 0 && pg < p.num_pages && slot < ntok) pos = page_first_pos(e, sp.first_fill) + slot;
+        }
+        kpos[blk & 1][tid] = pos;
     };
     // S of block `blk` = Q . K^T into S buffer blk & 1 (one thread)
     auto issue_s = [&](int blk) {
         const int buf = blk & 1;
         const uint32_t kaddr = smem_u32(sKV + buf * (2 * kUmKBytes));
+        if (!mbar_wait(&bar_k[buf], (blk >> 1) & 1, &abort_flag)) return;      // K of the block has landed
         tc_fence_after();
 #pragma unroll
         for (int s = 0; s < kHeadDim / 16; ++s) {
@@ -258,43 +267,38 @@ prefill_umma_kernel(const PrefillUmmaParams p) {
         }
         umma_commit(&bar_s[buf]);
     };
-    // a block every row of the tile sees in full (no fill-level or diagonal mask): four full pages that end
+    // a block every row of the tile sees in full (no fill-level or diagonal mask): no holes, and its last key lies
     // before the first row's horizon
     const int tile_min_vis = base_pos + tok0 + 1;
     auto block_is_clean = [&](int blk) {
-        const int e0 = blk * kUmPagesPerBlock, e1 = e0 + kUmPagesPerBlock - 1;
-        if (e1 >= n_need) return false;
-        if (e0 == 0 && sp.first_fill != kPageSize) return false;
-        if (e1 == sp.n_pages - 1 && sp.last_fill != kPageSize) return false;
-        return page_first_pos(e1, sp.first_fill) + kPageSize <= tile_min_vis;
+        const int e1 = blk * kUmPagesPerBlock + kUmPagesPerBlock - 1;
+        return !vholes[blk & 1] && page_first_pos(e1, sp.first_fill) + kPageSize <= tile_min_vis;
     };
 
     // Software pipeline, one block ahead: while the threads work on S of block j, the tensor cores already
     // compute S of block j + 1 and then O += P.V of block j; the loads run two (K) and one (V) blocks ahead.
-    // cp.async groups in issue order: K0 K1 V0 | K2 V1 | K3 V2 | ...
     if (n_blocks > 0) {
-        issue_loads(0, 0);
-        issue_loads(1, 0);
-        issue_loads(0, 1);
-        cp_async_wait_group<2>();                   // K0
-        fence_proxy_async();
+        // the copies are issued by lane 0 of warps 1 (K) and 2 (V): warp 0's lane 0 feeds the tensor cores
+        if (tid == 32) {
+            prefetch_tensormap(&kv_map);
+            issue_tma(0, 0);
+            issue_tma(1, 0);
+        }
+        if (tid == 64) issue_tma(0, 1);
+        note_positions(0);
         __syncthreads();
         if (tid == 0) issue_s(0);
     }
     for (int j = 0; j < n_blocks; ++j) {
         const int buf = j & 1;
         const uint32_t s_col = kUmColS + buf * kUmKeys;
-        // ---- S of the next block goes to the tensor cores before this block's softmax ----
-        if (j + 1 < n_blocks) {
-            cp_async_wait_group<1>();               // K of block j + 1 (only V of block j may still fly)
-            fence_proxy_async();
-            if (!__syncthreads_and(alive)) { alive = false; break; }
-            if (tid == 0) issue_s(j + 1);
-        }
+        // ---- S of the next block goes to the tensor cores before this block's softmax (its S buffer and
+        //      its K were released before the barrier that closed the previous iteration) ----
+        if (tid == 0 && j + 1 < n_blocks) issue_s(j + 1);
         // ---- S of this block ----
         if (!mbar_wait(&bar_s[buf], (j >> 1) & 1, &abort_flag)) alive = false;
         tc_fence_after();
-        issue_loads(j + 2, 0);                      // K of block j + 2 over K of block j, which S no longer needs
+        if (tid == 32) issue_tma(j + 2, 0);         // K of block j + 2 over K of block j, which S no longer needs
 
         float alpha = 1.0f;
         uint32_t packed[32];
@@ -348,7 +352,8 @@ prefill_umma_kernel(const PrefillUmmaParams p) {
             if (!mbar_wait(&bar_o, (j - 1) & 1, &abort_flag)) alive = false;
             tc_fence_after();
         }
-        issue_loads(j + 1, 1);                      // V of block j + 1 (and the key positions of that block)
+        if (tid == 64) issue_tma(j + 1, 1);         // V of block j + 1 ...
+        note_positions(j + 1);                      // ... and where its keys lie
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {     // warp-uniform: tcgen05.ld / st are warp-wide
 #pragma unroll
             for (int c = 0; c < kHeadDim; c += 32) {
@@ -362,13 +367,22 @@ prefill_umma_kernel(const PrefillUmmaParams p) {
         // P as bf16 pairs over the first 32 columns of this block's S (read into registers above)
         tmem_st32_u32(my_tmem + s_col, packed);
         tmem_st_wait();
-        cp_async_wait_group<2>();                   // V of block j
-        fence_proxy_async();
+        if (vholes[buf]) {                          // uniform: clear the rows of V that hold no key
+            if (tid < kUmKeys && kpos[buf][tid] == 0x7fffffff) {
+                if (!mbar_wait(&bar_v[buf], (j >> 1) & 1, &abort_flag)) alive = false;
+                uint8_t* vrow = sKV + buf * (2 * kUmKBytes) + kUmKBytes;
+#pragma unroll
+                for (int c = 0; c < 16; ++c)
+                    *reinterpret_cast<uint4*>(vrow + (c >> 3) * (kUmKeys * 128) + swz(tid, c & 7)) =
+                        make_uint4(0u, 0u, 0u, 0u);
+            }
+            fence_proxy_async();
+        }
         tc_fence_before();
         if (!__syncthreads_and(alive)) { alive = false; break; }
 
         // ---- O += P . V ----
-        if (tid == 0) {
+        if (tid == 0 && mbar_wait(&bar_v[buf], (j >> 1) & 1, &abort_flag)) {     // V of the block has landed
             tc_fence_after();
             const uint32_t vaddr = smem_u32(sKV + buf * (2 * kUmKBytes) + kUmKBytes);
 #pragma unroll
@@ -423,7 +437,12 @@ int launch_prefill_umma(const PrefillUmmaParams& p, int max_new_tokens, cudaStre
                  "ktk_prefill_attention");
     const int tpc = kUmRows / p.G;
     const dim3 grid((unsigned)((max_new_tokens + tpc - 1) / tpc), (unsigned)p.Hkv, (unsigned)p.batch);
-    prefill_umma_kernel<<<grid, kUmRows, kUmSmem, st>>>(p);
+    DecodeParams d{};                               // only what the tensor map needs
+    d.cache = p.cache; d.Hkv = p.Hkv; d.num_pages = p.num_pages;
+    CUtensorMap map;
+    const int rc = make_kv_tensor_map(&map, d);
+    if (rc != KTK_OK) return rc;
+    prefill_umma_kernel<<<grid, kUmRows, kUmSmem, st>>>(p, map);
     KTK_CUDA_TRY(cudaGetLastError(), "ktk_prefill_attention");
     return KTK_OK;
 }
