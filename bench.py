@@ -105,7 +105,8 @@ def parse():
     ap.add_argument("--one-rank-of", type=int, default=0,
                     help="full-model workloads on one GPU: run the compute of ONE rank of this many (heads and MLP "
                          "width divided, no exchange) -- what a step costs without the NVLink exchanges")
-    ap.add_argument("--micro", default="", choices=["", "select", "exchange"],
+    ap.add_argument("--prefill-tokens", type=int, default=4096, help="--micro prefill: tokens per prompt")
+    ap.add_argument("--micro", default="", choices=["", "select", "exchange", "prefill"],
                     help="time one kernel alone on the workload's shapes (select: only the page summaries are "
                          "allocated, so the full batch fits in a few GB; exchange: the NVLink exchange kernels "
                          "on [batch, hidden] under torchrun, every form, beside NCCL)")
@@ -867,6 +868,57 @@ def run_micro_select(args):
           "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / (ms * 1e-3) / 1e9})
 
 
+def run_micro_prefill(args):
+    """Causal prefill attention alone: `--batch` prompts (default 4) of `--prefill-tokens` tokens, the workload's heads
+    per rank, bf16, no history.  Times the tcgen05 kernel (the default) and the mma.sync kernel it replaced."""
+    from kinetics_b200 import ops, _lib
+    import kinetics_b200 as kb
+    wl = dict(WORKLOADS[args.workload])
+    cfg = kb.get_config(wl["model"])
+    tp = args.one_rank_of or wl.get("tp", 1)
+    hkv, hq = cfg.num_key_value_heads // tp, cfg.num_attention_heads // tp
+    B, n = args.batch or 4, args.prefill_tokens
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(args.seed)
+    pages_per = (n + PAGE - 1) // PAGE
+    cache = torch.randn(B * pages_per, 2, PAGE, hkv, HEAD_DIM, device=dev).to(torch.bfloat16)
+    q = torch.randn(B * n, hq, HEAD_DIM, device=dev).to(torch.bfloat16)
+    indptr = torch.arange(B + 1, dtype=torch.int32, device=dev) * pages_per
+    table = torch.arange(B * pages_per, dtype=torch.int32, device=dev)
+    last = torch.full((B,), n - (pages_per - 1) * PAGE, dtype=torch.int32, device=dev)
+    q_indptr = torch.arange(B + 1, dtype=torch.int32, device=dev) * n
+    status = ops.new_status(dev)
+    flop = B * hq * n * (n + 1) / 2 * HEAD_DIM * 4           # QK^T and PV over the causal half
+    out, outs = {"micro": "prefill", "prompts": B, "tokens": n, "kv_heads": hkv, "q_heads": hq, "causal_flop": flop,
+                 "kernels": {}}, {}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, variant in (("prefill_umma_kernel (tcgen05)", _lib.VARIANT_UMMA), ("prefill_mma_kernel (mma.sync)", _lib.VARIANT_MMA)):
+        run = lambda: ops.prefill_attention(q, q_indptr, n, cache, table, indptr, last, variant=variant, status=status)
+        for _ in range(max(3, args.warmup)):
+            outs[variant] = run()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        out["kernels"][name] = {"ms": ms, "tflops": flop / (ms * 1e-3) / 1e12}
+    ops.raise_on_status(status)
+    out["max_abs_difference_between_the_two"] = float(
+        (outs[_lib.VARIANT_UMMA].float() - outs[_lib.VARIANT_MMA].float()).abs().max())
+    peaks = {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except Exception:
+        pass
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    out["peak_tflops"] = peak
+    out["frac"] = out["kernels"]["prefill_umma_kernel (tcgen05)"]["tflops"] / peak
+    emit(out)
+
+
 def run_full_model(args):
     """A full-model decode step (Qwen3-1.7B, 512 sequences in continuous batching).  One process per GPU; the model is tensor parallel
     over the ranks of the run.  A step = Engine.decode_graphed: host page-table work (PagePool growth, CSR export,
@@ -1135,6 +1187,8 @@ def main():
         return run_micro_select(args)
     if args.micro == "exchange":
         return run_micro_exchange(args)
+    if args.micro == "prefill":
+        return run_micro_prefill(args)
     if args.impl == "reference":
         run_reference(args)
     elif WORKLOADS[args.workload].get("full_model"):

@@ -3,24 +3,30 @@
 // flashinfer.single_prefill_with_kv_cache of LiteSys/litesys/attention/batch_cache.py:129-145.
 //
 // One CTA per (sequence, kv head, tile of 128 / G new tokens): the 128 rows of the tile are the (token, head of
-// the query group) pairs, row r = thread r = lane r of tensor memory.  The history is walked in blocks of 64 keys
-// (four pages).  Per block:
-//     all threads   K and V of the four pages -> shared memory, 16-byte cp.async into the 128-byte swizzle
-//                   pattern the tensor cores read (rows past a page's fill level are zero-filled)
-//     one thread    S[128 x 64]   = Q[128 x 128] . K^T      8 x tcgen05.mma (M 128, N 64, K 16), D in TMEM
-//     thread r      row r of S <- tcgen05.ld; scale, causal mask, running max and sum, P = exp2(S - max) as bf16
-//                   into shared memory (swizzled, K-major); O row in TMEM rescaled when the max moved
-//     one thread    O[128 x 128] += P[128 x 64] . V[64 x 128]   4 x tcgen05.mma (M 128, N 128, K 16), V read
-//                   MN-major: exactly the rows the pages hold
-// and at the end row r of O is read back, divided by the row sum and stored.  The phases of one CTA run one after
-// the other; two CTAs per SM (80 KiB of shared memory and 256 TMEM columns each) overlap one another's phases.
-// Every wait is bounded; tensor memory is released on every path.
+// the query group) pairs; row r belongs to softmax thread r and lives in lane r of tensor memory.  The history is
+// walked in blocks of 64 keys (four pages).  Roles:
+//     issuing warp (one lane)   TMA: K and V of a block -> shared memory, 16-row x 128-byte boxes under the
+//                               128-byte swizzle, which is the operand layout tcgen05.mma reads; K two blocks
+//                               ahead, V one.
+//                               S[128 x 64]   = Q[128 x 128] . K^T    8 x tcgen05.mma (M 128, N 64, K 16), D in TMEM
+//                               O[128 x 128] += P[128 x 64] . V       4 x tcgen05.mma (M 128, N 128, K 16), A = P
+//                               from tensor memory, B = V read MN-major: the page rows as they lie
+//                               S of block j + 1 is issued before O += P.V of block j: the tensor cores work on it
+//                               while the threads do the softmax of block j.
+//     softmax thread r          row r of S <- tcgen05.ld; scale, causal / fill-level mask, running max and sum;
+//                               P = 2^(S - reference) as bf16 pairs back over the first 32 columns of that S
+//                               (tcgen05.st); the O row in tensor memory rescaled when the reference moved
+// and at the end row r of O is read back, divided by the row sum and stored.  tcgen05.commit -> mbarrier tells
+// the threads when S and O are complete; the softmax warps meet at one named barrier per block and one of them
+// then tells the issuing warp that P is in place.  Two CTAs per SM (97 KiB of shared memory, 256 TMEM columns
+// each).  Every wait is bounded; tensor memory is released on every path.
 #include "ktk_decode_mma.cuh"
 #include "ktk_prefill_umma.cuh"
 
 namespace ktk {
 
-constexpr int kUmRows = 128;                 // rows of a tile = threads of a CTA
+constexpr int kUmRows = 128;                 // rows of a tile = softmax threads of a CTA
+constexpr int kUmThreads = kUmRows + 64;     // + the warp that feeds the tensor cores + the warp that issues the copies
 constexpr int kUmKeys = 64;                  // keys per block
 constexpr int kUmPagesPerBlock = kUmKeys / kPageSize;
 constexpr int kUmTmemCols = 256;             // S of two blocks: columns [0, 64) and [64, 128); O: [128, 256)
@@ -127,11 +133,23 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
     return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
-__global__ void __launch_bounds__(kUmRows, 2)
+// barrier of the softmax warps (named barrier 1); returns whether any of them raised `flag`
+__device__ __forceinline__ bool softmax_sync_or(bool flag) {
+    uint32_t out;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+        "bar.red.or.pred p, 1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(out) : "r"((uint32_t)flag), "n"(kUmRows) : "memory");
+    return out != 0;
+}
+
+__global__ void __launch_bounds__(kUmThreads, 2)
 prefill_umma_kernel(const PrefillUmmaParams p, const __grid_constant__ CUtensorMap kv_map) {
     extern __shared__ uint8_t um_raw[];
-    __shared__ __align__(8) uint64_t bar_s[2], bar_o, bar_k[2], bar_v[2];
-    __shared__ int vholes[2];                     // the V rows of the block in this buffer need clearing / masking
+    // S complete (per S buffer) | O += P.V complete | K, V landed (per buffer) | P in place | V buffer read out
+    // (per-buffer barriers for the TMA warp: a barrier it waits on cannot run two phases ahead of it, because the next
+    // phase needs the very copy it is about to issue)
+    __shared__ __align__(8) uint64_t bar_s[2], bar_o, bar_k[2], bar_v[2], bar_p, bar_vfree[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int kpos[2][kUmKeys];              // position of the key in row c of the block (INT_MAX: none)
     __shared__ int abort_flag;
@@ -140,7 +158,9 @@ prefill_umma_kernel(const PrefillUmmaParams p, const __grid_constant__ CUtensorM
     uint8_t* sQ = sm;
     uint8_t* sKV = sQ + kUmQBytes;                // [buffer][K | V]
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool issuer = warp == kUmRows / 32;     // the fifth warp: tensor-core instructions (and TMEM allocation)
+    const bool loader = warp == kUmRows / 32 + 1; // the sixth warp: TMA
     const int b = blockIdx.z, h = blockIdx.y;
     const int G = p.G, Hq = p.Hkv * G;
     const int tpc = kUmRows / G;                    // new tokens per CTA
@@ -162,21 +182,38 @@ prefill_umma_kernel(const PrefillUmmaParams p, const __grid_constant__ CUtensorM
     if (n_need > sp.n_pages) n_need = sp.n_pages;
     const int n_blocks = (n_need + kUmPagesPerBlock - 1) / kUmPagesPerBlock;
 
-    // this thread's row
+    // a softmax thread's row
     const int my_tok = tok0 + tid / G, my_head = h * G + tid % G;
-    const bool row_on = my_tok < n_new;
+    const bool row_on = warp < kUmRows / 32 && my_tok < n_new;
     const int vis = row_on ? base_pos + my_tok + 1 : 0;     // keys at positions < vis are seen
+
+    // tokens held by logical page e, and whether block `blk` has rows without a key (a page past the needed ones
+    // or a page that is not full): those rows of V are cleared before use and the block is masked
+    auto page_tokens = [&](int e) { return e == sp.n_pages - 1 ? sp.last_fill : (e == 0 ? sp.first_fill : kPageSize); };
+    auto block_has_holes = [&](int blk) {
+        const int e0 = blk * kUmPagesPerBlock, e1 = e0 + kUmPagesPerBlock - 1;
+        if (e1 >= n_need) return true;
+        if (e0 == 0 && sp.first_fill != kPageSize) return true;
+        return e1 == sp.n_pages - 1 && sp.last_fill != kPageSize;
+    };
+    // positions of the keys of block `blk` (softmax threads 0..63, one row each)
+    auto note_positions = [&](int blk) {
+        if (blk >= n_blocks || tid >= kUmKeys) return;
+        const int e = blk * kUmPagesPerBlock + (tid >> 4), slot = tid & 15;
+        kpos[blk & 1][tid] = (e < n_need && slot < page_tokens(e)) ? page_first_pos(e, sp.first_fill) + slot : 0x7fffffff;
+    };
 
     if (tid == 0) {
         mbar_init(&bar_s[0], 1);
         mbar_init(&bar_s[1], 1);
         mbar_init(&bar_o, 1);
-        for (int i = 0; i < 2; ++i) { mbar_init(&bar_k[i], 1); mbar_init(&bar_v[i], 1); }
+        mbar_init(&bar_p, 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(&bar_k[i], 1); mbar_init(&bar_v[i], 1); mbar_init(&bar_vfree[i], 1); }
         abort_flag = 0;
         mbar_init_fence();
     }
-    // Q row -> two swizzled tiles (zeros for rows past the last new token)
-    {
+    if (warp < kUmRows / 32) {
+        // Q row -> two swizzled tiles (zeros for rows past the last new token)
         const uint4* src = reinterpret_cast<const uint4*>(
             (const __nv_bfloat16*)p.q + ((int64_t)(q0 + (row_on ? my_tok : 0)) * Hq + my_head) * kHeadDim);
 #pragma unroll
@@ -184,8 +221,9 @@ prefill_umma_kernel(const PrefillUmmaParams p, const __grid_constant__ CUtensorM
             const uint4 v = row_on ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
             *reinterpret_cast<uint4*>(sQ + (c >> 3) * (kUmRows * 128) + swz(tid, c & 7)) = v;
         }
-    }
-    if (warp == 0) {
+        note_positions(0);
+        fence_proxy_async();
+    } else if (issuer) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(&tmem_base_s)), "r"(kUmTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -194,242 +232,231 @@ prefill_umma_kernel(const PrefillUmmaParams p, const __grid_constant__ CUtensorM
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_base_s;
-    const uint32_t my_tmem = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 lanes
-
-    const uint32_t idesc_s = umma_idesc(kUmKeys, false);
-    const uint32_t idesc_o = umma_idesc(kHeadDim, true);
-    float m_run = -INFINITY, m_ref = 0.0f, l_run = 0.0f;   // running max, reference point of the exponentials, row sum
     bool alive = true;
 
-    // K (which = 0) or V (which = 1) of block `blk` -> its buffer blk & 1, issued by one thread: per page two TMA
-    // boxes of 16 rows x 128 B (the two 64-dim halves) into the 128-byte swizzle pattern the tensor cores read.
-    // The V call also notes whether rows of the block will be left without data (a page past the needed ones, an
-    // invalid page id, a page that is not full): those rows of V are cleared before the block is used.
-    auto issue_tma = [&](int blk, int which) {
-        if (blk >= n_blocks) return;
-        const int buf = blk & 1;
-        uint64_t* bar = which ? &bar_v[buf] : &bar_k[buf];
-        uint8_t* dst = sKV + buf * (2 * kUmKBytes) + which * kUmKBytes;
-        int64_t pages[kUmPagesPerBlock];
-        uint32_t bytes = 0;
-        bool holes = false;
+    if (issuer) {
+        if (lane == 0 && n_blocks > 0) {
+            const uint32_t idesc_s = umma_idesc(kUmKeys, false);
+            const uint32_t idesc_o = umma_idesc(kHeadDim, true);
+            // S of block `blk` = Q . K^T into S buffer blk & 1, once its K has landed
+            auto issue_s = [&](int blk) {
+                const int buf = blk & 1;
+                const uint32_t kaddr = smem_u32(sKV + buf * (2 * kUmKBytes));
+                if (!mbar_wait(&bar_k[buf], (blk >> 1) & 1, &abort_flag)) return false;
+                tc_fence_after();
 #pragma unroll
-        for (int pi = 0; pi < kUmPagesPerBlock; ++pi) {
-            const int e = blk * kUmPagesPerBlock + pi;
-            pages[pi] = -1;
-            if (e < n_need) {
-                const int64_t pg = p.kv_indices[sp.start + e];
-                if (pg < 0 || pg >= p.num_pages) {
-                    if (which == 0) report(p.status, KTK_STATUS_BAD_PAGE);
-                } else {
-                    pages[pi] = pg;
-                    bytes += 2u * kPageSize * 128u;
+                for (int s = 0; s < kHeadDim / 16; ++s) {
+                    const uint64_t a = umma_desc(smem_u32(sQ) + (s >> 2) * (kUmRows * 128) + (s & 3) * 32, 0, 1024);
+                    const uint64_t bd = umma_desc(kaddr + (s >> 2) * (kUmKeys * 128) + (s & 3) * 32, 0, 1024);
+                    umma_f16(tmem + kUmColS + buf * kUmKeys, a, bd, idesc_s, s > 0 ? 1u : 0u);
                 }
-                const int ntok = (e == sp.n_pages - 1) ? sp.last_fill : (e == 0 ? sp.first_fill : kPageSize);
-                if (ntok != kPageSize) holes = true;
+                umma_commit(&bar_s[buf]);
+                return true;
+            };
+            bool ok = issue_s(0);
+            for (int j = 0; j < n_blocks && ok; ++j) {
+                const int buf = j & 1;
+                // S of the next block first: its S buffer was read out, and the P in it consumed, a block ago
+                if (j + 1 < n_blocks) ok = issue_s(j + 1);
+                // O += P . V once P is in place and V has landed
+                ok = ok && mbar_wait(&bar_p, j & 1, &abort_flag) && mbar_wait(&bar_v[buf], (j >> 1) & 1, &abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t vaddr = smem_u32(sKV + buf * (2 * kUmKBytes) + kUmKBytes);
+                const uint32_t s_col = kUmColS + buf * kUmKeys;
+#pragma unroll
+                for (int s = 0; s < kUmKeys / 16; ++s) {
+                    const uint64_t bd = umma_desc(vaddr + s * (16 * 128), kUmVLbo, kUmVSbo);
+                    umma_f16_ts(tmem + kUmColO, tmem + s_col + s * 8, bd, idesc_o, (j > 0 || s > 0) ? 1u : 0u);
+                }
+                umma_commit(&bar_o);
+                umma_commit(&bar_vfree[buf]);
             }
-            if (pages[pi] < 0) holes = true;
         }
-        if (which == 1) vholes[buf] = holes ? 1 : 0;
-        if (bytes) mbar_arrive_expect_tx(bar, bytes);
-        else mbar_arrive(bar);
+    } else if (loader) {
+        if (lane == 0 && n_blocks > 0) {
+            // K (which = 0) or V (which = 1) of block `blk` -> its buffer blk & 1: per page two boxes of 16 rows x 128 B
+            auto issue_tma = [&](int blk, int which) {
+                if (blk >= n_blocks) return;
+                const int buf = blk & 1;
+                uint64_t* bar = which ? &bar_v[buf] : &bar_k[buf];
+                uint8_t* dst = sKV + buf * (2 * kUmKBytes) + which * kUmKBytes;
+                int64_t pages[kUmPagesPerBlock];
+                uint32_t bytes = 0;
 #pragma unroll
-        for (int pi = 0; pi < kUmPagesPerBlock; ++pi) {
-            if (pages[pi] < 0) continue;
-            const int z = (int)(pages[pi] * (2 * kPageSize)) + which * kPageSize;    // token row of slot 0
-            tma_load_3d(dst + pi * (kPageSize * 128), &kv_map, bar, 0, h, z);
-            tma_load_3d(dst + kUmKeys * 128 + pi * (kPageSize * 128), &kv_map, bar, 64, h, z);
-        }
-    };
-    // positions of the keys of block `blk` (threads 0..63, one row each)
-    auto note_positions = [&](int blk) {
-        if (blk >= n_blocks || tid >= kUmKeys) return;
-        const int e = blk * kUmPagesPerBlock + (tid >> 4), slot = tid & 15;
-        int pos = 0x7fffffff;
-        if (e < n_need) {
-            const int ntok = (e == sp.n_pages - 1) ? sp.last_fill : (e == 0 ? sp.first_fill : kPageSize);
-            const int64_t pg = p.kv_indices[sp.start + e];
-            if (pg >= 0 && pg < p.num_pages && slot < ntok) pos = page_first_pos(e, sp.first_fill) + slot;
-        }
-        kpos[blk & 1][tid] = pos;
-    };
-    // S of block `blk` = Q . K^T into S buffer blk & 1 (one thread)
-    auto issue_s = [&](int blk) {
-        const int buf = blk & 1;
-        const uint32_t kaddr = smem_u32(sKV + buf * (2 * kUmKBytes));
-        if (!mbar_wait(&bar_k[buf], (blk >> 1) & 1, &abort_flag)) return;      // K of the block has landed
-        tc_fence_after();
+                for (int pi = 0; pi < kUmPagesPerBlock; ++pi) {
+                    const int e = blk * kUmPagesPerBlock + pi;
+                    pages[pi] = -1;
+                    if (e < n_need) {
+                        const int64_t pg = p.kv_indices[sp.start + e];
+                        if (pg < 0 || pg >= p.num_pages) {
+                            if (which == 0) report(p.status, KTK_STATUS_BAD_PAGE);
+                        } else {
+                            pages[pi] = pg;
+                            bytes += 2u * kPageSize * 128u;
+                        }
+                    }
+                }
+                if (bytes) mbar_arrive_expect_tx(bar, bytes);
+                else mbar_arrive(bar);
 #pragma unroll
-        for (int s = 0; s < kHeadDim / 16; ++s) {
-            const uint64_t a = umma_desc(smem_u32(sQ) + (s >> 2) * (kUmRows * 128) + (s & 3) * 32, 0, 1024);
-            const uint64_t bd = umma_desc(kaddr + (s >> 2) * (kUmKeys * 128) + (s & 3) * 32, 0, 1024);
-            umma_f16(tmem + kUmColS + buf * kUmKeys, a, bd, idesc_s, s > 0 ? 1u : 0u);
-        }
-        umma_commit(&bar_s[buf]);
-    };
-    // a block every row of the tile sees in full (no fill-level or diagonal mask): no holes, and its last key lies
-    // before the first row's horizon
-    const int tile_min_vis = base_pos + tok0 + 1;
-    auto block_is_clean = [&](int blk) {
-        const int e1 = blk * kUmPagesPerBlock + kUmPagesPerBlock - 1;
-        return !vholes[blk & 1] && page_first_pos(e1, sp.first_fill) + kPageSize <= tile_min_vis;
-    };
-
-    // Software pipeline, one block ahead: while the threads work on S of block j, the tensor cores already
-    // compute S of block j + 1 and then O += P.V of block j; the loads run two (K) and one (V) blocks ahead.
-    if (n_blocks > 0) {
-        // the copies are issued by lane 0 of warps 1 (K) and 2 (V): warp 0's lane 0 feeds the tensor cores
-        if (tid == 32) {
+                for (int pi = 0; pi < kUmPagesPerBlock; ++pi) {
+                    if (pages[pi] < 0) continue;
+                    const int z = (int)(pages[pi] * (2 * kPageSize)) + which * kPageSize;    // token row of slot 0
+                    tma_load_3d(dst + pi * (kPageSize * 128), &kv_map, bar, 0, h, z);
+                    tma_load_3d(dst + kUmKeys * 128 + pi * (kPageSize * 128), &kv_map, bar, 64, h, z);
+                }
+            };
             prefetch_tensormap(&kv_map);
             issue_tma(0, 0);
             issue_tma(1, 0);
-        }
-        if (tid == 64) issue_tma(0, 1);
-        note_positions(0);
-        __syncthreads();
-        if (tid == 0) issue_s(0);
-    }
-    for (int j = 0; j < n_blocks; ++j) {
-        const int buf = j & 1;
-        const uint32_t s_col = kUmColS + buf * kUmKeys;
-        // ---- S of the next block goes to the tensor cores before this block's softmax (its S buffer and
-        //      its K were released before the barrier that closed the previous iteration) ----
-        if (tid == 0 && j + 1 < n_blocks) issue_s(j + 1);
-        // ---- S of this block ----
-        if (!mbar_wait(&bar_s[buf], (j >> 1) & 1, &abort_flag)) alive = false;
-        tc_fence_after();
-        if (tid == 32) issue_tma(j + 2, 0);         // K of block j + 2 over K of block j, which S no longer needs
-
-        float alpha = 1.0f;
-        uint32_t packed[32];
-        {
-            float s_lo[32], s_hi[32];
-            tmem_ld32(my_tmem + s_col, s_lo);
-            tmem_ld32(my_tmem + s_col + 32, s_hi);
-            // masked columns become -inf; the scale (positive) is applied inside the exponent below
-            if (!block_is_clean(j)) {               // uniform for the CTA
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    s_lo[c] = kpos[buf][c] < vis ? s_lo[c] : -INFINITY;
-                    s_hi[c] = kpos[buf][32 + c] < vis ? s_hi[c] : -INFINITY;
+            issue_tma(0, 1);
+            for (int j = 0; j < n_blocks; ++j) {
+                // K of block j + 2 goes over K of block j once S of block j is complete
+                if (j + 2 < n_blocks) {
+                    if (!mbar_wait(&bar_s[j & 1], (j >> 1) & 1, &abort_flag)) break;
+                    issue_tma(j + 2, 0);
+                }
+                // V of block j + 1 goes over V of block j - 1 once O += P.V of block j - 1 is complete
+                if (j + 1 < n_blocks) {
+                    if (j > 0 && !mbar_wait(&bar_vfree[(j + 1) & 1], ((j - 1) >> 1) & 1, &abort_flag)) break;
+                    issue_tma(j + 1, 1);
                 }
             }
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 32; c += 2) {
-                mx0 = fmaxf(mx0, s_lo[c]);
-                mx1 = fmaxf(mx1, s_lo[c + 1]);
-                mx2 = fmaxf(mx2, s_hi[c]);
-                mx3 = fmaxf(mx3, s_hi[c + 1]);
-            }
-            const float mx = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2);
-            // The reference point of the exponentials follows the running maximum only when that moved by more
-            // than 2^8: P then stays below 256 (exact in fp32, fine in bf16) and the O row in tensor memory is
-            // rescaled rarely instead of at almost every block.  The final division by the row sum, taken against
-            // the same reference point, makes the result independent of it.
-            float m_use;
-            if (mx == -INFINITY) m_use = 0.0f;                     // a row that has seen nothing yet
-            else if (m_run == -INFINITY || mx - m_ref > 8.0f) m_use = mx;
-            else m_use = m_ref;
-            alpha = (m_run == -INFINITY) ? 0.0f : exp2f(m_ref - m_use);
-            m_ref = m_use;
-            float sum = 0.0f;
-#pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                const float p0 = ex2(fmaf(s_lo[2 * c], p.scale_log2, -m_use));
-                const float p1 = ex2(fmaf(s_lo[2 * c + 1], p.scale_log2, -m_use));
-                const float p2 = ex2(fmaf(s_hi[2 * c], p.scale_log2, -m_use));
-                const float p3 = ex2(fmaf(s_hi[2 * c + 1], p.scale_log2, -m_use));
-                sum += (p0 + p1) + (p2 + p3);
-                packed[c] = pack_bf16(p0, p1);      // keys 2c, 2c + 1 -> column c of P
-                packed[16 + c] = pack_bf16(p2, p3); // keys 32 + 2c, 33 + 2c -> column 16 + c
-            }
-            l_run = l_run * alpha + sum;
-            m_run = mx;
         }
-        // ---- O += P.V of the previous block has to be over: O is rescaled, its V buffer reloaded ----
-        if (j > 0) {
-            if (!mbar_wait(&bar_o, (j - 1) & 1, &abort_flag)) alive = false;
+    } else {
+        const uint32_t my_tmem = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 lanes
+        float m_run = -INFINITY, m_ref = 0.0f, l_run = 0.0f;   // running max, reference of the exponentials, row sum
+        const int tile_min_vis = base_pos + tok0 + 1;
+        for (int j = 0; j < n_blocks; ++j) {
+            const int buf = j & 1;
+            const uint32_t s_col = kUmColS + buf * kUmKeys;
+            const bool holes = block_has_holes(j);
+            // every row of the tile sees the whole block: no mask
+            const bool clean = !holes && page_first_pos(j * kUmPagesPerBlock + kUmPagesPerBlock - 1, sp.first_fill) +
+                                                 kPageSize <= tile_min_vis;
+            if (!mbar_wait(&bar_s[buf], (j >> 1) & 1, &abort_flag)) alive = false;
+            tc_fence_after();
+
+            float alpha = 1.0f;
+            uint32_t packed[32];
+            {
+                float s_lo[32], s_hi[32];
+                tmem_ld32(my_tmem + s_col, s_lo);
+                tmem_ld32(my_tmem + s_col + 32, s_hi);
+                // masked columns become -inf; the scale (positive) is applied inside the exponent below
+                if (!clean) {                       // uniform for the CTA
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        s_lo[c] = kpos[buf][c] < vis ? s_lo[c] : -INFINITY;
+                        s_hi[c] = kpos[buf][32 + c] < vis ? s_hi[c] : -INFINITY;
+                    }
+                }
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    mx0 = fmaxf(mx0, s_lo[c]);
+                    mx1 = fmaxf(mx1, s_lo[c + 1]);
+                    mx2 = fmaxf(mx2, s_hi[c]);
+                    mx3 = fmaxf(mx3, s_hi[c + 1]);
+                }
+                const float mx = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2);
+                // The reference point of the exponentials follows the running maximum only when that moved by
+                // more than 2^8: P then stays below 256 (exact in fp32, fine in bf16) and the O row in tensor
+                // memory is rescaled rarely instead of at almost every block.  The final division by the row sum,
+                // taken against the same reference point, makes the result independent of it.
+                float m_use;
+                if (mx == -INFINITY) m_use = 0.0f;                     // a row that has seen nothing yet
+                else if (m_run == -INFINITY || mx - m_ref > 8.0f) m_use = mx;
+                else m_use = m_ref;
+                alpha = (m_run == -INFINITY) ? 0.0f : exp2f(m_ref - m_use);
+                m_ref = m_use;
+                float sum = 0.0f;
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const float p0 = ex2(fmaf(s_lo[2 * c], p.scale_log2, -m_use));
+                    const float p1 = ex2(fmaf(s_lo[2 * c + 1], p.scale_log2, -m_use));
+                    const float p2 = ex2(fmaf(s_hi[2 * c], p.scale_log2, -m_use));
+                    const float p3 = ex2(fmaf(s_hi[2 * c + 1], p.scale_log2, -m_use));
+                    sum += (p0 + p1) + (p2 + p3);
+                    packed[c] = pack_bf16(p0, p1);      // keys 2c, 2c + 1 -> column c of P
+                    packed[16 + c] = pack_bf16(p2, p3); // keys 32 + 2c, 33 + 2c -> column 16 + c
+                }
+                l_run = l_run * alpha + sum;
+                m_run = mx;
+            }
+            // ---- O += P.V of the previous block has to be over before the O row is rescaled ----
+            if (j > 0) {
+                if (!mbar_wait(&bar_o, (j - 1) & 1, &abort_flag)) alive = false;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, alpha != 1.0f)) {      // warp-uniform: tcgen05.ld / st are warp-wide
+#pragma unroll
+                    for (int c = 0; c < kHeadDim; c += 32) {
+                        float o[32];
+                        tmem_ld32(my_tmem + kUmColO + c, o);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] *= alpha;
+                        tmem_st32(my_tmem + kUmColO + c, o);
+                    }
+                }
+            }
+            // P as bf16 pairs over the first 32 columns of this block's S (read into registers above)
+            tmem_st32_u32(my_tmem + s_col, packed);
+            tmem_st_wait();
+            if (holes) {                            // uniform: clear the rows of V that hold no key
+                if (tid < kUmKeys && kpos[buf][tid] == 0x7fffffff) {
+                    if (!mbar_wait(&bar_v[buf], (j >> 1) & 1, &abort_flag)) alive = false;
+                    uint8_t* vrow = sKV + buf * (2 * kUmKBytes) + kUmKBytes;
+#pragma unroll
+                    for (int c = 0; c < 16; ++c)
+                        *reinterpret_cast<uint4*>(vrow + (c >> 3) * (kUmKeys * 128) + swz(tid, c & 7)) =
+                            make_uint4(0u, 0u, 0u, 0u);
+                }
+                fence_proxy_async();
+            }
+            note_positions(j + 1);                  // kpos of the other buffer: block j - 1 is done with it
+            tc_fence_before();
+            // all rows of P in place, V cleared, positions written -- or, for all alike, a wait that ran out
+            if (softmax_sync_or(!alive || abort_flag != 0)) { alive = false; break; }
+            if (tid == 0) mbar_arrive(&bar_p);
+        }
+        if (alive && n_blocks > 0) {
+            if (!mbar_wait(&bar_o, (n_blocks - 1) & 1, &abort_flag)) alive = false;
             tc_fence_after();
         }
-        if (tid == 64) issue_tma(j + 1, 1);         // V of block j + 1 ...
-        note_positions(j + 1);                      // ... and where its keys lie
-        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {     // warp-uniform: tcgen05.ld / st are warp-wide
+        if (alive) {
+            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            __nv_bfloat16* dst = (__nv_bfloat16*)p.o + ((int64_t)(q0 + (row_on ? my_tok : 0)) * Hq + my_head) * kHeadDim;
 #pragma unroll
             for (int c = 0; c < kHeadDim; c += 32) {
                 float o[32];
-                tmem_ld32(my_tmem + kUmColO + c, o);
+                if (n_blocks > 0) {                     // uniform for the CTA (the loads are warp-wide)
+                    tmem_ld32(my_tmem + kUmColO + c, o);
+                } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o[i] *= alpha;
-                tmem_st32(my_tmem + kUmColO + c, o);
-            }
-        }
-        // P as bf16 pairs over the first 32 columns of this block's S (read into registers above)
-        tmem_st32_u32(my_tmem + s_col, packed);
-        tmem_st_wait();
-        if (vholes[buf]) {                          // uniform: clear the rows of V that hold no key
-            if (tid < kUmKeys && kpos[buf][tid] == 0x7fffffff) {
-                if (!mbar_wait(&bar_v[buf], (j >> 1) & 1, &abort_flag)) alive = false;
-                uint8_t* vrow = sKV + buf * (2 * kUmKBytes) + kUmKBytes;
+                    for (int i = 0; i < 32; ++i) o[i] = 0.0f;
+                }
+                if (row_on) {
 #pragma unroll
-                for (int c = 0; c < 16; ++c)
-                    *reinterpret_cast<uint4*>(vrow + (c >> 3) * (kUmKeys * 128) + swz(tid, c & 7)) =
-                        make_uint4(0u, 0u, 0u, 0u);
-            }
-            fence_proxy_async();
-        }
-        tc_fence_before();
-        if (!__syncthreads_and(alive)) { alive = false; break; }
-
-        // ---- O += P . V ----
-        if (tid == 0 && mbar_wait(&bar_v[buf], (j >> 1) & 1, &abort_flag)) {     // V of the block has landed
-            tc_fence_after();
-            const uint32_t vaddr = smem_u32(sKV + buf * (2 * kUmKBytes) + kUmKBytes);
-#pragma unroll
-            for (int s = 0; s < kUmKeys / 16; ++s) {
-                const uint64_t bd = umma_desc(vaddr + s * (16 * 128), kUmVLbo, kUmVSbo);
-                umma_f16_ts(tmem + kUmColO, tmem + s_col + s * 8, bd, idesc_o, (j > 0 || s > 0) ? 1u : 0u);
-            }
-            umma_commit(&bar_o);
-        }
-    }
-    if (alive && n_blocks > 0) {
-        if (!mbar_wait(&bar_o, (n_blocks - 1) & 1, &abort_flag)) alive = false;
-        tc_fence_after();
-    }
-    alive = __syncthreads_and(alive);
-
-    if (alive) {
-        const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-        __nv_bfloat16* dst = (__nv_bfloat16*)p.o + ((int64_t)(q0 + (row_on ? my_tok : 0)) * Hq + my_head) * kHeadDim;
-#pragma unroll
-        for (int c = 0; c < kHeadDim; c += 32) {
-            float o[32];
-            if (n_blocks > 0) {                     // uniform for the CTA (the loads are warp-wide)
-                tmem_ld32(my_tmem + kUmColO + c, o);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[i] = 0.0f;
-            }
-            if (row_on) {
-#pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    uint4 v;
-                    v.x = pack_bf16(o[i] * inv, o[i + 1] * inv);
-                    v.y = pack_bf16(o[i + 2] * inv, o[i + 3] * inv);
-                    v.z = pack_bf16(o[i + 4] * inv, o[i + 5] * inv);
-                    v.w = pack_bf16(o[i + 6] * inv, o[i + 7] * inv);
-                    *reinterpret_cast<uint4*>(dst + c + i) = v;
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 v;
+                        v.x = pack_bf16(o[i] * inv, o[i + 1] * inv);
+                        v.y = pack_bf16(o[i + 2] * inv, o[i + 3] * inv);
+                        v.z = pack_bf16(o[i + 4] * inv, o[i + 5] * inv);
+                        v.w = pack_bf16(o[i + 6] * inv, o[i + 7] * inv);
+                        *reinterpret_cast<uint4*>(dst + c + i) = v;
+                    }
                 }
             }
         }
-    } else if (tid == 0) {
-        report(p.status, KTK_STATUS_TIMEOUT);
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 0)
+    if (abort_flag && tid == 0) report(p.status, KTK_STATUS_TIMEOUT);
+    if (issuer) {
+        __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kUmTmemCols) : "memory");
+    }
 }
 
 int launch_prefill_umma(const PrefillUmmaParams& p, int max_new_tokens, cudaStream_t st) {
@@ -442,7 +469,7 @@ int launch_prefill_umma(const PrefillUmmaParams& p, int max_new_tokens, cudaStre
     CUtensorMap map;
     const int rc = make_kv_tensor_map(&map, d);
     if (rc != KTK_OK) return rc;
-    prefill_umma_kernel<<<grid, kUmRows, kUmSmem, st>>>(p, map);
+    prefill_umma_kernel<<<grid, kUmThreads, kUmSmem, st>>>(p, map);
     KTK_CUDA_TRY(cudaGetLastError(), "ktk_prefill_attention");
     return KTK_OK;
 }
