@@ -819,7 +819,7 @@ def run_micro_select(args):
         wl["batch"] = args.batch
     cfg = kb.get_config(wl["model"])
     B, topk = wl["batch"], wl["topk"]
-    tp = args.one_rank_of or wl.get("tp", 1)
+    tp = args.one_rank_of or wl.get("tp") or 1
     hkv, hq = cfg.num_key_value_heads // tp, cfg.num_attention_heads // tp
     dev = torch.device("cuda", 0)
     torch.manual_seed(args.seed)
@@ -875,7 +875,7 @@ def run_micro_prefill(args):
     import kinetics_b200 as kb
     wl = dict(WORKLOADS[args.workload])
     cfg = kb.get_config(wl["model"])
-    tp = args.one_rank_of or wl.get("tp", 1)
+    tp = args.one_rank_of or wl.get("tp") or 1
     hkv, hq = cfg.num_key_value_heads // tp, cfg.num_attention_heads // tp
     B, n = args.batch or 4, args.prefill_tokens
     dev = torch.device("cuda", 0)
