@@ -133,6 +133,23 @@ __device__ __forceinline__ void tmem_st32_u32(uint32_t taddr, const uint32_t (&v
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// Bounded wait without a suspend-time hint: the barriers of this kernel complete within microseconds, and the
+// waiter should see that at once.  Gives up like mbar_wait (and raises *abort) after about a second of polling.
+__device__ __forceinline__ bool mbar_wait_fast(uint64_t* bar, uint32_t parity, volatile int* abort) {
+    for (uint32_t i = 0; i < (1u << 24); ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((i & 63u) == 63u && *abort) return false;
+    }
+    *abort = 1;
+    return false;
+}
+
 // 2^x on the special-function unit (-inf -> 0)
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -158,10 +175,11 @@ __device__ __forceinline__ bool softmax_sync_or(bool flag) {
 __global__ void __launch_bounds__(kUmThreads, 2)
 prefill_umma_kernel(const PrefillUmmaParams p, const __grid_constant__ CUtensorMap kv_map) {
     extern __shared__ uint8_t um_raw[];
-    // S complete (per S buffer) | O += P.V complete | K, V landed (per buffer) | P in place | V buffer read out
+    // S complete (per S buffer) | K, V landed (per buffer) | P in place | O += P.V of a block complete = its V buffer
+    // read out (per buffer)
     // (per-buffer barriers for the TMA warp: a barrier it waits on cannot run two phases ahead of it, because the next
     // phase needs the very copy it is about to issue)
-    __shared__ __align__(8) uint64_t bar_s[2], bar_o, bar_k[2], bar_v[2], bar_p, bar_vfree[2];
+    __shared__ __align__(8) uint64_t bar_s[2], bar_k[2], bar_v[2], bar_p, bar_vfree[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int kpos[2][kUmKeys];              // position of the key in row c of the block (INT_MAX: none)
     __shared__ int abort_flag;
@@ -218,7 +236,6 @@ prefill_umma_kernel(const PrefillUmmaParams p, const __grid_constant__ CUtensorM
     if (tid == 0) {
         mbar_init(&bar_s[0], 1);
         mbar_init(&bar_s[1], 1);
-        mbar_init(&bar_o, 1);
         mbar_init(&bar_p, 1);
         for (int i = 0; i < 2; ++i) { mbar_init(&bar_k[i], 1); mbar_init(&bar_v[i], 1); mbar_init(&bar_vfree[i], 1); }
         abort_flag = 0;
@@ -254,7 +271,7 @@ prefill_umma_kernel(const PrefillUmmaParams p, const __grid_constant__ CUtensorM
             auto issue_s = [&](int blk) {
                 const int buf = blk & 1;
                 const uint32_t kaddr = smem_u32(sKV + buf * (2 * kUmKBytes));
-                if (!mbar_wait(&bar_k[buf], (blk >> 1) & 1, &abort_flag)) return false;
+                if (!mbar_wait_fast(&bar_k[buf], (blk >> 1) & 1, &abort_flag)) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int s = 0; s < kHeadDim / 16; ++s) {
@@ -271,7 +288,7 @@ prefill_umma_kernel(const PrefillUmmaParams p, const __grid_constant__ CUtensorM
                 // S of the next block first: its S buffer was read out, and the P in it consumed, a block ago
                 if (j + 1 < n_blocks) ok = issue_s(j + 1);
                 // O += P . V once P is in place and V has landed
-                ok = ok && mbar_wait(&bar_p, j & 1, &abort_flag) && mbar_wait(&bar_v[buf], (j >> 1) & 1, &abort_flag);
+                ok = ok && mbar_wait_fast(&bar_p, j & 1, &abort_flag) && mbar_wait_fast(&bar_v[buf], (j >> 1) & 1, &abort_flag);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t vaddr = smem_u32(sKV + buf * (2 * kUmKBytes) + kUmKBytes);
@@ -281,7 +298,6 @@ prefill_umma_kernel(const PrefillUmmaParams p, const __grid_constant__ CUtensorM
                     const uint64_t bd = umma_desc(vaddr + s * (16 * 128), kUmVLbo, kUmVSbo);
                     umma_f16_ts(tmem + kUmColO, tmem + s_col + s * 8, bd, idesc_o, (j > 0 || s > 0) ? 1u : 0u);
                 }
-                umma_commit(&bar_o);
                 umma_commit(&bar_vfree[buf]);
             }
         }
@@ -326,12 +342,12 @@ prefill_umma_kernel(const PrefillUmmaParams p, const __grid_constant__ CUtensorM
             for (int j = 0; j < n_blocks; ++j) {
                 // K of block j + 2 goes over K of block j once S of block j is complete
                 if (j + 2 < n_blocks) {
-                    if (!mbar_wait(&bar_s[j & 1], (j >> 1) & 1, &abort_flag)) break;
+                    if (!mbar_wait_fast(&bar_s[j & 1], (j >> 1) & 1, &abort_flag)) break;
                     issue_tma(j + 2, 0);
                 }
                 // V of block j + 1 goes over V of block j - 1 once O += P.V of block j - 1 is complete
                 if (j + 1 < n_blocks) {
-                    if (j > 0 && !mbar_wait(&bar_vfree[(j + 1) & 1], ((j - 1) >> 1) & 1, &abort_flag)) break;
+                    if (j > 0 && !mbar_wait_fast(&bar_vfree[(j + 1) & 1], ((j - 1) >> 1) & 1, &abort_flag)) break;
                     issue_tma(j + 1, 1);
                 }
             }
@@ -347,7 +363,7 @@ prefill_umma_kernel(const PrefillUmmaParams p, const __grid_constant__ CUtensorM
             // every row of the tile sees the whole block: no mask
             const bool clean = !holes && page_first_pos(j * kUmPagesPerBlock + kUmPagesPerBlock - 1, sp.first_fill) +
                                                  kPageSize <= tile_min_vis;
-            if (!mbar_wait(&bar_s[buf], (j >> 1) & 1, &abort_flag)) alive = false;
+            if (!mbar_wait_fast(&bar_s[buf], (j >> 1) & 1, &abort_flag)) alive = false;
             tc_fence_after();
 
             float alpha = 1.0f;
@@ -396,19 +412,18 @@ prefill_umma_kernel(const PrefillUmmaParams p, const __grid_constant__ CUtensorM
                 l_run = l_run * alpha + sum;
                 m_run = mx;
             }
-            // ---- O += P.V of the previous block has to be over before the O row is rescaled ----
-            if (j > 0) {
-                if (!mbar_wait(&bar_o, (j - 1) & 1, &abort_flag)) alive = false;
+            // ---- the O row is rescaled only when the reference moved, and only then does this warp have to know
+            //      that O += P.V of the previous block is over (per-buffer barrier: it cannot run ahead of us) ----
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {     // warp-uniform: tcgen05.ld / st are warp-wide
+                if (!mbar_wait_fast(&bar_vfree[(j - 1) & 1], ((j - 1) >> 1) & 1, &abort_flag)) alive = false;
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, alpha != 1.0f)) {      // warp-uniform: tcgen05.ld / st are warp-wide
 #pragma unroll
-                    for (int c = 0; c < kHeadDim; c += 32) {
-                        float o[32];
-                        tmem_ld32(my_tmem + kUmColO + c, o);
+                for (int c = 0; c < kHeadDim; c += 32) {
+                    float o[32];
+                    tmem_ld32(my_tmem + kUmColO + c, o);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] *= alpha;
-                        tmem_st32(my_tmem + kUmColO + c, o);
-                    }
+                    for (int i = 0; i < 32; ++i) o[i] *= alpha;
+                    tmem_st32(my_tmem + kUmColO + c, o);
                 }
             }
             // P as bf16 pairs over the first 32 columns of this block's S (read into registers above)
@@ -416,7 +431,7 @@ prefill_umma_kernel(const PrefillUmmaParams p, const __grid_constant__ CUtensorM
             tmem_st_wait();
             if (holes) {                            // uniform: clear the rows of V that hold no key
                 if (tid < kUmKeys && kpos[buf][tid] == 0x7fffffff) {
-                    if (!mbar_wait(&bar_v[buf], (j >> 1) & 1, &abort_flag)) alive = false;
+                    if (!mbar_wait_fast(&bar_v[buf], (j >> 1) & 1, &abort_flag)) alive = false;
                     uint8_t* vrow = sKV + buf * (2 * kUmKBytes) + kUmKBytes;
 #pragma unroll
                     for (int c = 0; c < 16; ++c)
@@ -432,7 +447,7 @@ prefill_umma_kernel(const PrefillUmmaParams p, const __grid_constant__ CUtensorM
             if (tid == 0) mbar_arrive(&bar_p);
         }
         if (alive && n_blocks > 0) {
-            if (!mbar_wait(&bar_o, (n_blocks - 1) & 1, &abort_flag)) alive = false;
+            if (!mbar_wait_fast(&bar_vfree[(n_blocks - 1) & 1], ((n_blocks - 1) >> 1) & 1, &abort_flag)) alive = false;
             tc_fence_after();
         }
         if (alive) {
