@@ -8,6 +8,7 @@
 // up front (LiteSys/litesys/attention/batch_cache.py:32-40, engine.py:51-62).
 #include <cstdint>
 #include <new>
+#include <cstring>
 #include <vector>
 
 #include "ktk_common.cuh"
@@ -165,7 +166,7 @@ extern "C" int64_t ktk_pool_export(const ktk_pool* pool, const int32_t* slots, i
             set_error("ktk_pool_export: kv_indices holds %lld entries, more are needed", (long long)indices_capacity);
             return KTK_ERR_TOO_LARGE;
         }
-        for (size_t j = 0; j < mine.size(); ++j) kv_indices[total + (int64_t)j] = mine[j];
+        if (!mine.empty()) std::memcpy(kv_indices + total, mine.data(), mine.size() * sizeof(int32_t));
         total += (int64_t)mine.size();
         kv_indptr[i + 1] = (int32_t)total;
         const int64_t t = pool->tokens[(size_t)s];

@@ -98,7 +98,11 @@ class PagePool:
         """The same into caller-owned int32 CPU tensors (pinned ones, for a copy that overlaps); returns the
         number of page ids written."""
         n = len(slots)
-        arr = (ctypes.c_int32 * n)(*slots)
+        cached = getattr(self, "_export_slots", None)
+        if cached is None or cached[0] != slots:           # the same batch step after step: build the C array once
+            cached = (list(slots), (ctypes.c_int32 * n)(*slots))
+            self._export_slots = cached
+        arr = cached[1]
         total = self._lib.ktk_pool_export(self._h, arr, n, ctypes.c_void_p(indices.data_ptr()), indices.numel(),
                                           ctypes.c_void_p(indptr.data_ptr()), ctypes.c_void_p(last.data_ptr()))
         if total < 0:
