@@ -90,3 +90,35 @@ def test_prefill_long_prompt_many_sequences(cuda_device):
     torch.testing.assert_close(out.float(), rows.float(), rtol=2e-2, atol=2e-2)
     ref = _reference(q[n:2 * n].float(), k[1].to(cuda_device), v[1].to(cuda_device), G)
     torch.testing.assert_close(out[n:2 * n].float(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("variant", [0, 2])
+@pytest.mark.parametrize("G,sink", [(4, 0), (2, 4), (8, 4)])
+def test_prefill_on_block_and_tile_edges(cuda_device, variant, G, sink):
+    """Histories and chunks that end exactly on the edges the kernels cut at: 16-token pages, the 64-key blocks
+    and the 128 / G-token tiles of the tcgen05 kernel (and one token to either side of them)."""
+    from kinetics_b200 import ops
+    Hkv = 2
+    tile = 128 // G
+    hist = [0, 64 - sink, 64, 128 + sink, 63, 0, 16 * 9]
+    new = [tile, tile, 2 * tile, tile + 1, 1, 64 + sink + 1, tile - 1]
+    B = len(hist)
+    lens = [h + n for h, n in zip(hist, new)]
+    g = torch.Generator().manual_seed(40 + G + sink)
+    L = max(lens)
+    k = torch.randn(B, Hkv, L, 128, generator=g).to(torch.bfloat16).float()
+    v = torch.randn(B, Hkv, L, 128, generator=g).to(torch.bfloat16).float()
+    st = paged_state(k, v, lens, torch.bfloat16, seed=9, sink=sink)           # unused slots hold NaN
+    d = to_dev(st, cuda_device)
+    status = ops.new_status(cuda_device)
+    q_indptr = torch.tensor([sum(new[:i]) for i in range(B + 1)], dtype=torch.int32, device=cuda_device)
+    q = torch.randn(sum(new), Hkv * G, 128, generator=g).to(torch.bfloat16).to(cuda_device)
+    view = ops.PageView(sink_tokens=sink, local_tokens=1) if sink else None
+    out = ops.prefill_attention(q, q_indptr, max(new), d["kv_cache"], d["kv_indices"], d["kv_indptr"],
+                                d["kv_last_page_len"], variant=variant, status=status, view=view)
+    ops.raise_on_status(status)
+    assert torch.isfinite(out.float()).all()
+    for b in range(B):
+        lo, hi = int(q_indptr[b]), int(q_indptr[b + 1])
+        ref = _reference(q[lo:hi].float(), k[b, :, :lens[b]].to(cuda_device), v[b, :, :lens[b]].to(cuda_device), G)
+        torch.testing.assert_close(out[lo:hi].float(), ref, rtol=2e-2, atol=2e-2)
