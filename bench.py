@@ -105,7 +105,9 @@ def parse():
     ap.add_argument("--one-rank-of", type=int, default=0,
                     help="full-model workloads on one GPU: run the compute of ONE rank of this many (heads and MLP "
                          "width divided, no exchange) -- what a step costs without the NVLink exchanges")
-    ap.add_argument("--prefill-tokens", type=int, default=4096, help="--micro prefill: tokens per prompt")
+    ap.add_argument("--prefill-tokens", type=int, default=4096, help="--micro prefill: new tokens per prompt")
+    ap.add_argument("--prefill-history", type=int, default=0,
+                    help="--micro prefill: tokens every prompt already holds in its pages (a later chunk of a long prompt)")
     ap.add_argument("--micro", default="", choices=["", "select", "exchange", "prefill"],
                     help="time one kernel alone on the workload's shapes (select: only the page summaries are "
                          "allocated, so the full batch fits in a few GB; exchange: the NVLink exchange kernels "
@@ -877,19 +879,19 @@ def run_micro_prefill(args):
     cfg = kb.get_config(wl["model"])
     tp = args.one_rank_of or wl.get("tp") or 1
     hkv, hq = cfg.num_key_value_heads // tp, cfg.num_attention_heads // tp
-    B, n = args.batch or 4, args.prefill_tokens
+    B, n, hist = args.batch or 4, args.prefill_tokens, args.prefill_history
     dev = torch.device("cuda", 0)
     torch.manual_seed(args.seed)
-    pages_per = (n + PAGE - 1) // PAGE
+    pages_per = (hist + n + PAGE - 1) // PAGE
     cache = torch.randn(B * pages_per, 2, PAGE, hkv, HEAD_DIM, device=dev).to(torch.bfloat16)
     q = torch.randn(B * n, hq, HEAD_DIM, device=dev).to(torch.bfloat16)
     indptr = torch.arange(B + 1, dtype=torch.int32, device=dev) * pages_per
     table = torch.arange(B * pages_per, dtype=torch.int32, device=dev)
-    last = torch.full((B,), n - (pages_per - 1) * PAGE, dtype=torch.int32, device=dev)
+    last = torch.full((B,), hist + n - (pages_per - 1) * PAGE, dtype=torch.int32, device=dev)
     q_indptr = torch.arange(B + 1, dtype=torch.int32, device=dev) * n
     status = ops.new_status(dev)
-    flop = B * hq * n * (n + 1) / 2 * HEAD_DIM * 4           # QK^T and PV over the causal half
-    out, outs = {"micro": "prefill", "prompts": B, "tokens": n, "kv_heads": hkv, "q_heads": hq, "causal_flop": flop,
+    flop = B * hq * (n * hist + n * (n + 1) / 2) * HEAD_DIM * 4      # QK^T and PV over history + causal half
+    out, outs = {"micro": "prefill", "prompts": B, "tokens": n, "history": hist, "kv_heads": hkv, "q_heads": hq, "causal_flop": flop,
                  "kernels": {}}, {}
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for name, variant in (("prefill_umma_kernel (tcgen05)", _lib.VARIANT_UMMA), ("prefill_mma_kernel (mma.sync)", _lib.VARIANT_MMA)):
