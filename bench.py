@@ -983,7 +983,7 @@ def run_full_model(args):
     kv.assume_filled({s: int(lens[s]) for s in range(B)}, headroom=steps_total)
     # greedy sampling: the argmax is taken over the bf16 logits (identical to the argmax of an fp32 copy)
     model = kb.DecoderStack(cfg, device, dtype, process_group=pg, max_positions=max_seq + 8, decode_batch=B,
-                            seed=args.seed, num_layers=layers, logits_dtype=None)
+                            seed=args.seed, num_layers=layers, logits_dtype=None, shard_vocab=world > 1)
     eng = kb.Engine(model, kv, max_seq, device, temperature=0.0, repeat_check=False)
     slots = list(range(B))
     for s in slots:
@@ -1092,7 +1092,14 @@ def run_full_model(args):
             "gpu_launches_per_step": launches_per_step, "clocks": sampler.summary(),
         })
     if world > 1:
-        leave_group(dist, [eng, model, kv])
+        # the captured step holds a collective of the process group (the ranks' local maxima of the vocabulary
+        # projection): the graph has to be gone before the group is torn down
+        torch.cuda.synchronize()
+        eng._graph = None
+        eng._graph_out = None
+        out = None
+        del eng, model, kv
+        leave_group(dist, [])
 
 
 def run_micro_exchange(args):

@@ -23,10 +23,14 @@ from . import ops, tp
 class DecoderStack:
     def __init__(self, config, device, dtype=torch.bfloat16, process_group=None, max_positions: int = 40960,
                  decode_batch: int = 0, seed: int = 0, num_layers: Optional[int] = None,
-                 logits_dtype=torch.float32):
+                 logits_dtype=torch.float32, shard_vocab: bool = False):
         # logits_dtype: fp32 as the reference returns them (qwen3.py:141); None leaves them in the compute dtype,
         # which greedy sampling can take as they are (the argmax of bf16 logits is the argmax of their fp32 copies)
         self.logits_dtype = logits_dtype
+        # shard_vocab (with a process group): every rank keeps vocab_size / world rows of the vocabulary projection;
+        # `next_tokens` then finds the greedy token from the ranks' local maxima (a few KB exchanged) instead of
+        # every rank multiplying with the whole matrix.  `inference` needs the whole matrix and refuses.
+        self.shard_vocab = bool(shard_vocab)
         self.config, self.device, self.dtype = config, torch.device(device), dtype
         self.group = process_group
         self.world = torch.distributed.get_world_size(process_group) if process_group is not None else 1
@@ -46,6 +50,7 @@ class DecoderStack:
 
         self.embed_tokens = w(config.vocab_size, H)
         self.lm_head = w(config.vocab_size, H)
+        self.vocab_lo = 0
         self.norm_weight = torch.ones(H, device=self.device, dtype=dtype)
         self.layers = []
         for _ in range(self.num_layers):
@@ -73,6 +78,12 @@ class DecoderStack:
             self.ex_o = FusedExchange(process_group, decode_batch, H, dtype, self.device, result="allreduce_norm")
             self.ex_d = FusedExchange(process_group, decode_batch, H, dtype, self.device, result="allreduce_norm")
         self.decode_batch = decode_batch
+        if self.shard_vocab and self.world > 1:
+            if config.vocab_size % self.world:
+                raise ValueError(f"vocab_size {config.vocab_size} does not divide over {self.world} ranks")
+            rows = config.vocab_size // self.world
+            self.vocab_lo = self.rank * rows
+            self.lm_head = self.lm_head[self.vocab_lo:self.vocab_lo + rows].clone()
 
     # -- the sum over ranks of a partial GEMM output, + residual, + RMSNorm with `weight`
     def _reduce_add_norm(self, ex, a, b_t, residual, weight):
@@ -88,6 +99,35 @@ class DecoderStack:
 
     @torch.no_grad()
     def inference(self, input_ids, position_ids, batch_idx, kv):
+        if self.shard_vocab and self.world > 1:
+            raise RuntimeError("inference() returns full logits: build the stack without shard_vocab, or call next_tokens()")
+        bsz, seq_len = input_ids.shape
+        n = self._hidden(input_ids, position_ids, batch_idx, kv)
+        # n is the final RMSNorm of the residual stream (qwen3.py:139)
+        logits = torch.mm(n, self.lm_head.t())
+        if self.logits_dtype is not None:
+            logits = logits.to(self.logits_dtype)
+        return logits.view(bsz, seq_len, -1)
+
+    @torch.no_grad()
+    def next_tokens(self, input_ids, position_ids, batch_idx, kv):
+        """Greedy tokens [rows] of a decode step (the argmax of the logits `inference` would return; among equal
+        maxima the lowest token id).  With shard_vocab every rank multiplies with its rows of the vocabulary
+        projection only and the ranks exchange (maximum, token id) pairs."""
+        n = self._hidden(input_ids, position_ids, batch_idx, kv)
+        logits = torch.mm(n, self.lm_head.t())                         # [rows, vocab or vocab / world]
+        if not (self.shard_vocab and self.world > 1):
+            return logits.argmax(dim=-1)
+        vals, idx = logits.max(dim=-1)
+        pair = torch.stack((vals.float(), (idx + self.vocab_lo).float()), dim=1)       # ids < 2^24: exact in fp32
+        every = torch.empty(self.world, *pair.shape, device=pair.device, dtype=pair.dtype)
+        torch.distributed.all_gather_into_tensor(every, pair, group=self.group)
+        best = every[:, :, 0].max(dim=0).values
+        ids = torch.where(every[:, :, 0] == best, every[:, :, 1], torch.full_like(best, float("inf")))
+        return ids.min(dim=0).values.long()
+
+    def _hidden(self, input_ids, position_ids, batch_idx, kv):
+        """The layer loop: the final RMSNorm of the residual stream, [rows, hidden]."""
         bsz, seq_len = input_ids.shape
         assert bsz == 1 or seq_len == 1, f"Operation Not Supported with input shape {tuple(input_ids.shape)}"
         rows = bsz * seq_len
@@ -109,11 +149,7 @@ class DecoderStack:
             act = ops.silu_mul(gu[:, :half], gu[:, half:])
             nxt = self.layers[i + 1]["input_norm"] if i + 1 < self.num_layers else self.norm_weight
             x, n = self._reduce_add_norm(self.ex_d, act, L["down"].t(), x, nxt)
-        # n is the final RMSNorm of the residual stream (qwen3.py:139)
-        logits = torch.mm(n, self.lm_head.t())
-        if self.logits_dtype is not None:
-            logits = logits.to(self.logits_dtype)
-        return logits.view(bsz, seq_len, -1)
+        return n
 
     def check_status(self):
         for ex in (self.ex_o, self.ex_d):

@@ -479,8 +479,12 @@ class Engine:
     def _decode_device(self, batch_idx: torch.Tensor):
         pos = self.slots_offsets[batch_idx]
         input_ids = self.slots_tokens[batch_idx, pos].unsqueeze(1)
-        logits = self.model.inference(input_ids, pos.unsqueeze(1), batch_idx, self.kv)
-        next_tokens = self._sample(logits).reshape(-1)
+        if self.temperature < 0.02 and hasattr(self.model, "next_tokens"):
+            # greedy: the model may find the token without materialising (or, across ranks, gathering) the logits
+            next_tokens = self.model.next_tokens(input_ids, pos.unsqueeze(1), batch_idx, self.kv).reshape(-1)
+        else:
+            logits = self.model.inference(input_ids, pos.unsqueeze(1), batch_idx, self.kv)
+            next_tokens = self._sample(logits).reshape(-1)
         self.slots_offsets[batch_idx] += 1
         self.slots_tokens[batch_idx, pos + 1] = next_tokens
         return next_tokens

@@ -53,6 +53,35 @@ def stack_logits(dev, group, steps=4):
     return outs
 
 
+def stack_tokens(dev, group, shard_vocab, steps=3):
+    """The same small stack sampling greedily through `next_tokens`, with the vocabulary projection whole on every
+    rank or split by rows over the ranks (the ranks then exchange their local maxima)."""
+    import kinetics_b200 as kb
+    from kinetics_b200.config import LayerConfig
+    cfg = LayerConfig(hidden_size=512, num_attention_heads=16, num_key_value_heads=8, intermediate_size=1024,
+                      num_hidden_layers=2, vocab_size=1024)
+    dtype, B = torch.bfloat16, 8
+    model = kb.DecoderStack(cfg, dev, dtype, process_group=group, max_positions=512, decode_batch=B, seed=5,
+                            shard_vocab=shard_vocab)
+    kv = kb.BatchKVManager(cfg, B, 400, dev, dtype, attn_block_topk=32, attn_local=5, attn_block_size=16)
+    g = torch.Generator().manual_seed(9)
+    outs = []
+    lens = [150, 37, 96, 3, 200, 64, 17, 81]
+    for slot, n in enumerate(lens):
+        ids = torch.randint(0, 1024, (1, n), generator=g).to(dev)
+        pos = torch.arange(n, device=dev).unsqueeze(0)
+        outs.append(model.next_tokens(ids, pos, torch.tensor([slot], device=dev), kv).clone())
+    bi = torch.arange(B, device=dev)
+    for step in range(steps):
+        ids = torch.randint(0, 1024, (B, 1), generator=g).to(dev)
+        pos = torch.tensor([[n + step] for n in lens], device=dev)
+        outs.append(model.next_tokens(ids, pos, bi, kv).clone())
+    torch.cuda.synchronize()
+    kv.check_status()
+    model.check_status()
+    return torch.cat(outs)
+
+
 def main():
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -75,6 +104,16 @@ def main():
         same = a.clone()
         dist.broadcast(same, src=0)
         assert torch.equal(same, a), "ranks disagree on the logits"
+
+    # greedy tokens with the vocabulary projection split over the ranks = with the whole projection on every rank
+    # (the two GEMM shapes may round a logit differently: a near-tie may flip, nothing else)
+    whole = stack_tokens(dev, dist.group.WORLD, False)
+    split = stack_tokens(dev, dist.group.WORLD, True)
+    same_tokens = (whole == split).float().mean().item()
+    assert same_tokens >= 0.99, ("vocabulary-sharded greedy tokens", same_tokens)
+    agreed = split.clone()
+    dist.broadcast(agreed, src=0)
+    assert torch.equal(agreed, split), "ranks disagree on the sampled tokens"
 
     cfg = LayerConfig(hidden_size=1024, num_attention_heads=32, num_key_value_heads=8, intermediate_size=2048,
                       num_hidden_layers=1)
