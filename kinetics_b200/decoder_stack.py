@@ -20,6 +20,14 @@ import torch.nn.functional as F
 from . import ops, tp
 
 
+def merge_rank_maxima(every: torch.Tensor) -> torch.Tensor:
+    """every [ranks, rows, 2] fp32 = each rank's (largest logit, its token id) per row -> the token of the overall
+    largest logit per row; among equal maxima the lowest token id (what an argmax over the whole row gives)."""
+    best = every[:, :, 0].max(dim=0).values
+    ids = torch.where(every[:, :, 0] == best, every[:, :, 1], torch.full_like(best, float("inf")))
+    return ids.min(dim=0).values.long()
+
+
 class DecoderStack:
     def __init__(self, config, device, dtype=torch.bfloat16, process_group=None, max_positions: int = 40960,
                  decode_batch: int = 0, seed: int = 0, num_layers: Optional[int] = None,
@@ -122,9 +130,7 @@ class DecoderStack:
         pair = torch.stack((vals.float(), (idx + self.vocab_lo).float()), dim=1)       # ids < 2^24: exact in fp32
         every = torch.empty(self.world, *pair.shape, device=pair.device, dtype=pair.dtype)
         torch.distributed.all_gather_into_tensor(every, pair, group=self.group)
-        best = every[:, :, 0].max(dim=0).values
-        ids = torch.where(every[:, :, 0] == best, every[:, :, 1], torch.full_like(best, float("inf")))
-        return ids.min(dim=0).values.long()
+        return merge_rank_maxima(every)
 
     def _hidden(self, input_ids, position_ids, batch_idx, kv):
         """The layer loop: the final RMSNorm of the residual stream, [rows, hidden]."""

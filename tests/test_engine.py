@@ -279,3 +279,22 @@ def test_engine_stops_a_repeating_sequence():
     # the check starts once more than 32 tokens exist and trims the last block of 8
     assert len(done) == 1 and 20 < len(done[0]["output_tokens"]) < 60
     assert set(done[0]["output_tokens"]) == {7}
+
+
+def test_merge_of_the_ranks_vocabulary_maxima_is_the_global_argmax():
+    """Greedy sampling over a vocabulary projection split by rows over the ranks: the merge of the ranks'
+    (maximum, token id) pairs equals the argmax over the whole row, ties going to the lowest id."""
+    import torch
+    from kinetics_b200.decoder_stack import merge_rank_maxima
+    g = torch.Generator().manual_seed(3)
+    ranks, rows, vocab = 4, 64, 1024
+    logits = torch.randint(-5, 6, (rows, vocab), generator=g).float()          # many exact ties
+    per = vocab // ranks
+    pairs = []
+    for r in range(ranks):
+        vals, idx = logits[:, r * per:(r + 1) * per].max(dim=-1)
+        first = (logits[:, r * per:(r + 1) * per] == vals[:, None]).float().argmax(dim=-1)   # lowest id of the maximum
+        pairs.append(torch.stack((vals, (first + r * per).float()), dim=1))
+    got = merge_rank_maxima(torch.stack(pairs))
+    want = (logits == logits.max(dim=-1, keepdim=True).values).float().argmax(dim=-1)
+    assert torch.equal(got, want)
