@@ -118,11 +118,14 @@ class DecoderStack:
         return logits.view(bsz, seq_len, -1)
 
     @torch.no_grad()
-    def next_tokens(self, input_ids, position_ids, batch_idx, kv):
+    def next_tokens(self, input_ids, position_ids, batch_idx, kv, last_only: bool = False):
         """Greedy tokens [rows] of a decode step (the argmax of the logits `inference` would return; among equal
-        maxima the lowest token id).  With shard_vocab every rank multiplies with its rows of the vocabulary
-        projection only and the ranks exchange (maximum, token id) pairs."""
+        maxima the lowest token id); last_only: only the token behind the last row (a prompt).  With shard_vocab
+        every rank multiplies with its rows of the vocabulary projection only and the ranks exchange
+        (maximum, token id) pairs."""
         n = self._hidden(input_ids, position_ids, batch_idx, kv)
+        if last_only:
+            n = n[-1:]
         logits = torch.mm(n, self.lm_head.t())                         # [rows, vocab or vocab / world]
         if not (self.shard_vocab and self.world > 1):
             return logits.argmax(dim=-1)

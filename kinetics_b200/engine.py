@@ -456,8 +456,12 @@ class Engine:
         batch_idx = torch.tensor([slot], device=self.device)
         if hasattr(self.kv, "begin_step"):
             self.kv.begin_step([slot])
-        logits = self.model.inference(input_ids, position_ids, batch_idx, self.kv)[:, -1:, :]
-        self.slots_tokens[slot, seq_len] = self._sample(logits).reshape(())
+        if self.temperature < 0.02 and hasattr(self.model, "next_tokens"):
+            self.slots_tokens[slot, seq_len] = self.model.next_tokens(input_ids, position_ids, batch_idx, self.kv,
+                                                                      last_only=True)[-1]
+        else:
+            logits = self.model.inference(input_ids, position_ids, batch_idx, self.kv)[:, -1:, :]
+            self.slots_tokens[slot, seq_len] = self._sample(logits).reshape(())
 
     def decode(self, slots: List[int]) -> torch.Tensor:
         batch_idx = torch.tensor(slots, device=self.device)
@@ -465,8 +469,10 @@ class Engine:
         input_ids = self.slots_tokens[batch_idx].gather(dim=-1, index=offset)
         if hasattr(self.kv, "begin_step"):
             self.kv.begin_step(slots)
-        logits = self.model.inference(input_ids, offset, batch_idx, self.kv)
-        next_tokens = self._sample(logits)
+        if self.temperature < 0.02 and hasattr(self.model, "next_tokens"):
+            next_tokens = self.model.next_tokens(input_ids, offset, batch_idx, self.kv)      # greedy, see _decode_device
+        else:
+            next_tokens = self._sample(self.model.inference(input_ids, offset, batch_idx, self.kv))
         self.slots_offsets[batch_idx] += 1
         for s in slots:
             self._offsets_host[s] += 1
